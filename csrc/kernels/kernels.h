@@ -1,0 +1,154 @@
+// Launch API of the sm_100a kernels.  Plain C++ over raw device pointers and a
+// stream: no torch types here, so the .cu files compile in seconds and the
+// same launchers serve the torch bindings, the task runtime and the C ABI.
+//
+// Every compressing kernel can deliver its payload to up to kMaxWorld
+// destinations at once (`PushTargets`): the local output buffer and/or the
+// receive slots of peer GPUs mapped into this process (NVLink peer memory).
+// After the last CTA has stored its bytes, one thread publishes an epoch-valued
+// flag to every destination with a system-scope release store.  Receivers wait
+// on those flags with `wait_flags` (bounded) and then decode all ranks'
+// payloads in a single pass over the dense tensor (`*_unpack_accum`).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace hipress {
+namespace cuda {
+
+constexpr int kMaxWorld = 8;
+
+// Where a compressing kernel stores its payload.
+//   payload[p]  start of the payload in destination p (local or peer memory)
+//   flag[p]     flag word of destination p to publish `epoch` to; may be null
+//   done        device counter used to elect the last CTA; must be zero on
+//               entry, is reset to zero by the kernel
+struct PushTargets {
+  int world = 0;
+  uint8_t* payload[kMaxWorld] = {};
+  uint32_t* flag[kMaxWorld] = {};
+  uint32_t epoch = 0;
+  unsigned int* done = nullptr;
+};
+
+// Payloads of all ranks as seen by the receiver, in canonical (ascending rank)
+// accumulation order.
+struct UnpackSources {
+  int world = 0;
+  const uint8_t* payload[kMaxWorld] = {};
+  int64_t payload_bytes[kMaxWorld] = {};  // capacity of each slot (bounds checks)
+};
+
+// Optional fused SGD-with-momentum update applied to the decoded, averaged
+// gradient g:  g += wd * p;  buf = mu * buf + g;  p -= lr * buf.
+struct SgdApply {
+  float* param = nullptr;  // null -> no update, only the dense gradient is written
+  float* momentum = nullptr;
+  float lr = 0.f, mu = 0.f, weight_decay = 0.f;
+  int first_step = 0;  // buf = g on the first step (torch.optim.SGD semantics)
+};
+
+// Error codes written to a device status word by bounded waits / bounds checks.
+enum Status : int {
+  kOk = 0,
+  kFlagTimeout = 1,    // a peer's flag did not reach the epoch in time
+  kPayloadBounds = 2,  // a header describes more bytes / elements than the slot holds
+  kBadHeader = 3,
+};
+
+// ---------------------------------------------------------------- TBQ
+// grad and residual hold n floats; each payload destination ceil(n/4) bytes.
+cudaError_t tbq_compress(const float* grad, float* residual, int64_t n, float threshold,
+                         const PushTargets& dst, cudaStream_t stream);
+// out[i] = sum_r decode(payload_r)[i] (+ out[i] if add), times post_scale when != 1.
+cudaError_t tbq_unpack_accum(const UnpackSources& src, float threshold, float* out, int64_t n,
+                             int add, float post_scale, const SgdApply& apply,
+                             cudaStream_t stream);
+
+// ---------------------------------------------------------------- TernGrad
+// Scratch needed by terngrad_compress / ecq_compress (bytes).
+size_t minmax_scratch_bytes();
+// residual may be null.  With a residual, the tensor quantised is grad+residual
+// and residual receives the quantisation error.  scratch must be zero before
+// its first use and is left ready for the next call.
+cudaError_t terngrad_compress(const float* grad, float* residual, int64_t n, int bitwidth,
+                              int enable_random, uint64_t seed, const PushTargets& dst,
+                              void* scratch, cudaStream_t stream);
+// Element count per payload is taken from its header and must equal n.
+cudaError_t terngrad_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
+                                  float post_scale, const SgdApply& apply, int* status,
+                                  cudaStream_t stream);
+
+// ---------------------------------------------------------------- ECQ
+cudaError_t ecq_compress(const float* grad, float* history, int64_t n, float alpha, float beta,
+                         int bitwidth, uint64_t seed, const PushTargets& dst, void* scratch,
+                         cudaStream_t stream);
+cudaError_t ecq_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
+                             float post_scale, int* status, cudaStream_t stream);
+
+// ---------------------------------------------------------------- sparse top-k
+size_t sparse_scratch_bytes(int64_t n);
+// accumulate != 0: R += grad first (GradDrop); else grad is ignored (DGC).
+// Each destination needs 4 + 8*ceil(n*keep_fraction) bytes.
+cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sample_rate,
+                            double keep_fraction, uint64_t seed, int accumulate,
+                            const PushTargets& dst, void* scratch, cudaStream_t stream);
+// add == 0 zero-fills out first.  Payloads are applied one after another in
+// rank order so that the fp32 sum is reproducible on every replica.
+cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
+                                float post_scale, int* status, cudaStream_t stream);
+
+// ---------------------------------------------------------------- flags
+// Spins (one warp) until flag[r] >= epoch for all r < world, or timeout_ns
+// passes; on timeout writes kFlagTimeout to *status and returns normally.
+cudaError_t wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t timeout_ns,
+                       int* status, cudaStream_t stream);
+// Publishes `epoch` to flag[p] of every destination (release, system scope).
+cudaError_t signal_flags(const PushTargets& dst, cudaStream_t stream);
+
+// ---------------------------------------------------------------- dense helpers
+// Fused SGD-momentum over flat buffers (used for 1-D parameters and for the
+// uncompressed baseline path).
+cudaError_t sgd_apply_dense(float* grad, float scale, const SgdApply& apply, int64_t n,
+                            cudaStream_t stream);
+// out = a + b (fp32), n elements.
+cudaError_t add_into(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream);
+// Sum of W dense fp32 buffers (peer pointers) into out: the P2P dense
+// all-reduce used for small PowerSGD factors and 1-D parameters.
+cudaError_t dense_gather_sum(const float* const* srcs, int world, float* out, int64_t n,
+                             float post_scale, cudaStream_t stream);
+
+// ---------------------------------------------------------------- PowerSGD
+// All matrices row-major fp32.  Mat is n x m, P is n x r, Q is m x r, r <= 16.
+// Output rows are split evenly over `world` owners; each row of the product is
+// *added* into its owner's buffer (which has the full output shape and must be
+// zero beforehand).  world == 1 means plain local accumulation.
+struct ReduceTargets {
+  int world = 1;
+  float* dst[kMaxWorld] = {};
+};
+// K extent rounded up to the GEMM's K tile.
+int64_t psgd_kpad(int64_t k);
+// True when Mat can be described by a TMA tensor map (16-byte aligned base and
+// row pitch) so that the tcgen05 path applies.
+bool psgd_tensor_core_eligible(const float* Mat, int64_t n, int64_t m);
+// X[rows x r] -> Xt[16][rows_pad] (transposed, zero padded): the K-major B
+// operand of the tensor-core GEMM.  rows_pad = psgd_kpad(rows).
+cudaError_t psgd_transpose_pad(const float* X, int64_t rows, int r, float* Xt, int64_t rows_pad,
+                               cudaStream_t stream);
+// mode 0: out[n x r] += Mat * X (X = Q, m x r);  mode 1: out[m x r] += Mat^T * X (X = P, n x r).
+// Xt is psgd_transpose_pad(X); when it is null, force_simt is set, or Mat is
+// not TMA-eligible the SIMT kernel runs instead of tcgen05.
+cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const float* X,
+                      const float* Xt, int r, const ReduceTargets& red, int force_simt, int* status,
+                      cudaStream_t stream);
+// In-place modified Gram-Schmidt of the n x r matrix P (r <= 16).
+cudaError_t gram_schmidt(float* P, int64_t n, int r, float eps, cudaStream_t stream);
+// approx = P Q^T.  mode 0 (API parity): Mat = approx; residual = grad - Mat[:N]; grad = Mat[:N].
+// mode 1 (error feedback in place): grad[:N] = post_scale * approx; Mat -= approx.
+cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int64_t m, int r,
+                                 float* Mat, float* residual, float* grad, int64_t N, int mode,
+                                 float post_scale, cudaStream_t stream);
+
+}  // namespace cuda
+}  // namespace hipress

@@ -1,0 +1,100 @@
+// Device-side helpers for kernels that store into peer GPUs' memory and for
+// the flag protocol that tells receivers a payload is complete.
+#pragma once
+#include "kernels.h"
+
+namespace hipress {
+namespace cuda {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Stores of arbitrary alignment: pick the widest store the address allows.
+__device__ __forceinline__ void store_u32_any(uint8_t* p, uint32_t v) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  if ((a & 3) == 0) {
+    *reinterpret_cast<uint32_t*>(p) = v;
+  } else if ((a & 1) == 0) {
+    reinterpret_cast<uint16_t*>(p)[0] = static_cast<uint16_t>(v);
+    reinterpret_cast<uint16_t*>(p)[1] = static_cast<uint16_t>(v >> 16);
+  } else {
+    p[0] = static_cast<uint8_t>(v);
+    p[1] = static_cast<uint8_t>(v >> 8);
+    p[2] = static_cast<uint8_t>(v >> 16);
+    p[3] = static_cast<uint8_t>(v >> 24);
+  }
+}
+
+// The same 4 payload bytes to every destination.
+__device__ __forceinline__ void push_u32(const PushTargets& t, int64_t byte_off, uint32_t v) {
+#pragma unroll
+  for (int p = 0; p < kMaxWorld; ++p)
+    if (p < t.world) store_u32_any(t.payload[p] + byte_off, v);
+}
+__device__ __forceinline__ void push_u8(const PushTargets& t, int64_t byte_off, uint8_t v) {
+#pragma unroll
+  for (int p = 0; p < kMaxWorld; ++p)
+    if (p < t.world) t.payload[p][byte_off] = v;
+}
+__device__ __forceinline__ void push_bytes(const PushTargets& t, int64_t byte_off,
+                                           const uint8_t* src, int count) {
+  for (int p = 0; p < t.world; ++p)
+    for (int i = 0; i < count; ++i) t.payload[p][byte_off + i] = src[i];
+}
+
+// Called by every thread at the end of a compressing kernel.  Makes the CTA's
+// payload stores visible system-wide, elects the last CTA through `done`, and
+// lets that CTA publish the epoch flag to every destination.  The counter is
+// left at zero for the next launch.
+__device__ __forceinline__ void publish_when_grid_done(const PushTargets& t) {
+  if (t.done == nullptr) return;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned int prev = atomicAdd(t.done, 1u);
+    if (prev == total - 1) {
+      __threadfence_system();
+      *t.done = 0u;
+      for (int p = 0; p < t.world; ++p)
+        if (t.flag[p] != nullptr) st_release_sys(t.flag[p], t.epoch);
+    }
+  }
+}
+
+// Combine one byte per lane into 32-bit words: lane 4k ends up with the bytes
+// of lanes 4k..4k+3 (little-endian).  All 32 lanes must call.
+__device__ __forceinline__ uint32_t gather4_bytes(uint32_t b) {
+  uint32_t w = b & 0xffu;
+  w |= (__shfl_down_sync(0xffffffffu, b, 1) & 0xffu) << 8;
+  w |= (__shfl_down_sync(0xffffffffu, b, 2) & 0xffu) << 16;
+  w |= (__shfl_down_sync(0xffffffffu, b, 3) & 0xffu) << 24;
+  return w;
+}
+// Same for one 16-bit half-word per lane: lane 2k gets lanes 2k, 2k+1.
+__device__ __forceinline__ uint32_t gather2_halves(uint32_t h) {
+  return (h & 0xffffu) | ((__shfl_down_sync(0xffffffffu, h, 1) & 0xffffu) << 16);
+}
+
+__device__ __forceinline__ void sgd_update(const SgdApply& a, int64_t i, float g) {
+  // plain fp32 maths; contraction allowed (not part of any payload)
+  float p = a.param[i];
+  g = g + a.weight_decay * p;
+  float buf = a.first_step ? g : a.mu * a.momentum[i] + g;
+  a.momentum[i] = buf;
+  a.param[i] = p - a.lr * buf;
+}
+
+}  // namespace cuda
+}  // namespace hipress

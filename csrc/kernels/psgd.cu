@@ -1,0 +1,514 @@
+// PowerSGD kernels for sm_100a.
+//
+// The two projections of a PowerSGD step,
+//     P[n x r] = Mat[n x m] * Q[m x r]          (mode 0)
+//     Q[m x r] = Mat^T      * P[n x r]          (mode 1)
+// have r <= 16 and are bound by one read of Mat from HBM.  They run as
+// tcgen05 tiles: Mat is streamed by TMA (128-byte swizzle) through a 6-stage
+// shared-memory ring, one thread issues tcgen05.mma.kind::tf32 with a
+// 128 x 16 fp32 accumulator in tensor memory, and four epilogue warps read the
+// accumulator back with tcgen05.ld and reduce their rows into the *owner* of
+// those rows with red.global.add.f32 -- the owner may be a peer GPU (NVLink
+// peer memory), which makes the kernel a fused GEMM + reduce-scatter.  Mode 1
+// consumes Mat through the MN-major operand form, so Mat is never transposed
+// in memory.  The reference computes these with torch::mm (cuBLAS) and leaves
+// the all-reduce to its caller (ref powersgd_body.h:28, 49).
+//
+// Shapes TMA cannot describe (row pitch not a multiple of 16 bytes, unaligned
+// base) take a plain SIMT kernel with the same interface.
+//
+// Also here: the hand-written Gram-Schmidt orthonormalisation (the reference
+// uses geqrf + orgqr, powersgd_body.h:45-46) and the fused
+// expand / residual kernel (ref powersgd_body.h:69-75).
+#include <cuda.h>
+
+#include "kernels.h"
+#include "p2p.cuh"
+
+namespace hipress {
+namespace cuda {
+
+namespace {
+
+constexpr int kBM = 128;     // accumulator rows per CTA (UMMA M)
+constexpr int kBN = 16;      // padded rank (UMMA N)
+constexpr int kBK = 32;      // fp32 elements along K per stage = 128 bytes
+constexpr int kStages = 6;
+constexpr int kStageA = kBM * kBK * 4;  // 16384
+constexpr int kStageB = kBN * kBK * 4;  // 2048
+constexpr int kGemmThreads = 192;       // warp0 TMA, warp1 MMA, warps 2-5 epilogue
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every barrier wait gives up after 2 s
+constexpr int kTmemCols = 32;
+
+struct GemmSmem {
+  // 1024-byte aligned tiles first
+  uint8_t a[kStages][kStageA];
+  uint8_t b[kStages][kStageB];
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t accum;
+  uint32_t tmem_base;
+  int abort;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0u) {
+      if (*abort) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+      __nanosleep(64);
+    }
+  }
+  *abort = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= uint64_t((addr >> 4) & 0x3fffu);
+  d |= uint64_t((lbo >> 4) & 0x3fffu) << 16;
+  d |= uint64_t((sbo >> 4) & 0x3fffu) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+
+struct OwnerTargets {
+  int world;
+  float* dst[kMaxWorld];
+  int64_t rows_per_owner;
+};
+
+// MODE 0: out[n x r] += Mat * X,   A tile K-major  (rows of Mat x K along m)
+// MODE 1: out[m x r] += Mat^T * X, A tile MN-major (columns of Mat x K along n)
+// Xt is X transposed and zero-padded to [16][k_pad] (K-major B operand).
+template <int MODE>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 int64_t out_rows, int r, int total_kb, int kb_per_split, OwnerTargets out,
+                 int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmem& s = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x;
+  const int kb_begin = blockIdx.y * kb_per_split;
+  const int kb_end = min(kb_begin + kb_per_split, total_kb);
+  const int nkb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+    mbar_init(&s.accum, 1);
+    s.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&s.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = s.tmem_base;
+  volatile int* abort = &s.abort;
+
+  if (nkb > 0) {
+    if (warp == 0 && lane == 0) {
+      // ---------------- TMA producer
+      for (int i = 0; i < nkb; ++i) {
+        const int st = i % kStages;
+        const uint32_t round = uint32_t(i / kStages);
+        if (round > 0 && !mbar_wait(&s.empty[st], (round - 1) & 1u, abort)) break;
+        mbar_expect_tx(&s.full[st], kStageA + kStageB);
+        const int k0 = (kb_begin + i) * kBK;
+        if (MODE == 0) {
+          tma_load_2d(s.a[st], &map_a, k0, tile * kBM, &s.full[st]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            tma_load_2d(s.a[st] + j * (kBK * 128), &map_a, tile * kBM + j * 32, k0, &s.full[st]);
+        }
+        tma_load_2d(s.b[st], &map_b, k0, 0, &s.full[st]);
+      }
+    } else if (warp == 1 && lane == 0) {
+      // ---------------- MMA issuer
+      // instruction descriptor: fp32 accumulate, tf32 x tf32, N = 16, M = 128
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(MODE == 1) << 15) |
+                             (uint32_t(kBN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int st = i % kStages;
+        const uint32_t round = uint32_t(i / kStages);
+        ok = mbar_wait(&s.full[st], round & 1u, abort);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a0 = smem_u32(s.a[st]);
+        const uint32_t b0 = smem_u32(s.b[st]);
+#pragma unroll
+        for (int k = 0; k < kBK / 8; ++k) {
+          // K-major: 8 tf32 = 32 bytes further along the swizzled row.
+          // MN-major: next group of 8 K-rows = 1024 bytes further.
+          const uint64_t da = MODE == 0 ? make_desc(a0 + k * 32, 16, 1024)
+                                        : make_desc(a0 + k * 1024, kBK * 128, 1024);
+          const uint64_t db = make_desc(b0 + k * 32, 16, 1024);
+          umma_tf32(tmem, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(&s.empty[st]);  // frees the stage once the MMAs have read it
+      }
+      if (ok) umma_commit(&s.accum);
+    } else if (warp >= 2) {
+      // ---------------- epilogue: TMEM -> registers -> owner's buffer
+      if (mbar_wait(&s.accum, 0, abort)) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int quarter = warp & 3;  // TMEM lanes this warp may touch
+        uint32_t v[16];
+        const uint32_t taddr = tmem + (uint32_t(quarter * 32) << 16);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+            "%12, %13, %14, %15}, [%16];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+              "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+              "=r"(v[14]), "=r"(v[15])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int64_t row = int64_t(tile) * kBM + quarter * 32 + lane;
+        if (row < out_rows) {
+          int owner = int(row / out.rows_per_owner);
+          if (owner >= out.world) owner = out.world - 1;
+          float* dst = out.dst[owner] + row * r;
+#pragma unroll
+          for (int c = 0; c < 16; ++c)
+            if (c < r) atomicAdd(dst + c, __uint_as_float(v[c]));
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (s.abort) {
+    // give copies that may still be in flight time to land before the CTA's
+    // shared memory is released
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    if (threadIdx.x == 0 && status != nullptr) atomicExch(status, int(kFlagTimeout));
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
+                 : "memory");
+  }
+}
+
+// X[rows x r] row-major -> Xt[16][rows_pad], zero padded.
+__global__ void transpose_pad_kernel(const float* __restrict__ X, int64_t rows, int r,
+                                     float* __restrict__ Xt, int64_t rows_pad) {
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < rows_pad; i += stride) {
+#pragma unroll
+    for (int c = 0; c < kBN; ++c) Xt[c * rows_pad + i] = (i < rows && c < r) ? X[i * r + c] : 0.0f;
+  }
+}
+
+// SIMT path, mode 0: one warp per output row.
+__global__ void __launch_bounds__(256)
+simt_gemm_p_kernel(const float* __restrict__ Mat, const float* __restrict__ Q, int64_t n, int64_t m,
+                   int r, OwnerTargets out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= n) return;
+  float acc[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+  for (int64_t k = lane; k < m; k += 32) {
+    const float a = Mat[row * m + k];
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      if (c < r) acc[c] += a * Q[k * r + c];
+  }
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    if (c < r) {
+      float v = acc[c];
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      acc[c] = v;
+    }
+  }
+  if (lane == 0) {
+    int owner = int(row / out.rows_per_owner);
+    if (owner >= out.world) owner = out.world - 1;
+    for (int c = 0; c < r; ++c) atomicAdd(out.dst[owner] + row * r + c, acc[c]);
+  }
+}
+
+// SIMT path, mode 1: thread per Mat column, CTA per (column block, row chunk).
+__global__ void __launch_bounds__(256)
+simt_gemm_q_kernel(const float* __restrict__ Mat, const float* __restrict__ P, int64_t n, int64_t m,
+                   int r, int64_t rows_per_cta, OwnerTargets out) {
+  const int64_t col = int64_t(blockIdx.x) * 256 + threadIdx.x;
+  const int64_t i0 = int64_t(blockIdx.y) * rows_per_cta;
+  const int64_t i1 = min(i0 + rows_per_cta, n);
+  if (col >= m) return;
+  float acc[16];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) acc[c] = 0.f;
+  for (int64_t i = i0; i < i1; ++i) {
+    const float a = Mat[i * m + col];
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      if (c < r) acc[c] += a * P[i * r + c];
+  }
+  int owner = int(col / out.rows_per_owner);
+  if (owner >= out.world) owner = out.world - 1;
+  for (int c = 0; c < r; ++c) atomicAdd(out.dst[owner] + col * r + c, acc[c]);
+}
+
+// ---------------------------------------------------------------- Gram-Schmidt
+constexpr int kGsThreads = 1024;
+
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    v = lane < kGsThreads / 32 ? sh[lane] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) sh[0] = v;
+  }
+  __syncthreads();
+  return sh[0];
+}
+
+// One CTA orthonormalises one n x r matrix in place (modified Gram-Schmidt,
+// columns left to right): col_j /= (|col_j| + eps); col_k -= <col_j, col_k> col_j.
+__global__ void __launch_bounds__(kGsThreads)
+gram_schmidt_kernel(float* __restrict__ P, int64_t n, int r, float eps) {
+  __shared__ float sh[kGsThreads / 32];
+  for (int j = 0; j < r; ++j) {
+    float ss = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += kGsThreads) {
+      const float v = P[i * r + j];
+      ss += v * v;
+    }
+    const float norm = sqrtf(block_sum(ss, sh));
+    const float inv = 1.0f / (norm + eps);
+    for (int64_t i = threadIdx.x; i < n; i += kGsThreads) P[i * r + j] *= inv;
+    __syncthreads();
+    for (int c = j + 1; c < r; ++c) {
+      float dot = 0.f;
+      for (int64_t i = threadIdx.x; i < n; i += kGsThreads) dot += P[i * r + j] * P[i * r + c];
+      dot = block_sum(dot, sh);
+      for (int64_t i = threadIdx.x; i < n; i += kGsThreads) P[i * r + c] -= dot * P[i * r + j];
+      __syncthreads();
+    }
+  }
+}
+
+// ---------------------------------------------------------------- expand
+// approx[i,k] = sum_c P[i,c] Q[k,c].
+//   mode 0: Mat = approx; residual[:N] = grad - Mat[:N]; grad[:N] = Mat[:N]
+//   mode 1: grad[:N] = scale * approx; Mat -= approx      (error feedback kept in Mat)
+template <int MODE>
+__global__ void __launch_bounds__(256)
+expand_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t n, int64_t m, int r,
+              float* __restrict__ Mat, float* __restrict__ residual, float* __restrict__ grad,
+              int64_t N, float scale) {
+  const int64_t total = n * m;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    const int64_t i = e / m, k = e - i * m;
+    float acc = 0.f;
+    for (int c = 0; c < r; ++c) acc += P[i * r + c] * Q[k * r + c];
+    if (MODE == 0) {
+      Mat[e] = acc;
+      if (e < N) {
+        residual[e] = grad[e] - acc;
+        grad[e] = acc;
+      }
+    } else {
+      Mat[e] -= acc;
+      if (e < N) grad[e] = acc * scale;
+    }
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows.
+bool make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int box_inner,
+              int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
+  cuuint64_t strides[1] = {cuuint64_t(inner) * 4};
+  cuuint32_t box[2] = {cuuint32_t(box_inner), cuuint32_t(box_outer)};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+OwnerTargets owners_of(const ReduceTargets& red, int64_t rows) {
+  OwnerTargets o{};
+  o.world = red.world;
+  for (int p = 0; p < red.world; ++p) o.dst[p] = red.dst[p];
+  o.rows_per_owner = (rows + red.world - 1) / red.world;
+  if (o.rows_per_owner < 1) o.rows_per_owner = 1;
+  return o;
+}
+
+}  // namespace
+
+int64_t psgd_kpad(int64_t k) { return (k + kBK - 1) / kBK * kBK; }
+
+bool psgd_tensor_core_eligible(const float* Mat, int64_t n, int64_t m) {
+  return (reinterpret_cast<uintptr_t>(Mat) & 15) == 0 && (m % 4) == 0 && n >= 1 && m >= 1 &&
+         encode_fn() != nullptr;
+}
+
+cudaError_t psgd_transpose_pad(const float* X, int64_t rows, int r, float* Xt, int64_t rows_pad,
+                               cudaStream_t stream) {
+  if (r < 1 || r > kBN || rows_pad < rows) return cudaErrorInvalidValue;
+  int64_t blocks = (rows_pad + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  transpose_pad_kernel<<<int(blocks), 256, 0, stream>>>(X, rows, r, Xt, rows_pad);
+  return cudaGetLastError();
+}
+
+cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const float* X,
+                      const float* Xt, int r, const ReduceTargets& red, int force_simt, int* status,
+                      cudaStream_t stream) {
+  if (r < 1 || r > kBN || red.world < 1 || red.world > kMaxWorld || n < 1 || m < 1)
+    return cudaErrorInvalidValue;
+  const int64_t out_rows = mode == 0 ? n : m;
+  const int64_t K = mode == 0 ? m : n;
+  const OwnerTargets out = owners_of(red, out_rows);
+  if (force_simt || Xt == nullptr || !psgd_tensor_core_eligible(Mat, n, m)) {
+    if (mode == 0) {
+      simt_gemm_p_kernel<<<unsigned((n + 7) / 8), 256, 0, stream>>>(Mat, X, n, m, r, out);
+    } else {
+      const int64_t col_blocks = (m + 255) / 256;
+      int64_t chunks = (148 * 4 + col_blocks - 1) / col_blocks;
+      if (chunks > (n + 15) / 16) chunks = (n + 15) / 16;
+      if (chunks < 1) chunks = 1;
+      const int64_t rows_per = (n + chunks - 1) / chunks;
+      dim3 grid(unsigned(col_blocks), unsigned((n + rows_per - 1) / rows_per));
+      simt_gemm_q_kernel<<<grid, 256, 0, stream>>>(Mat, X, n, m, r, rows_per, out);
+    }
+    return cudaGetLastError();
+  }
+  const int64_t k_pad = psgd_kpad(K);
+  CUtensorMap map_a, map_b;
+  const bool ok_a = mode == 0 ? make_map(&map_a, Mat, m, n, kBK, kBM) : make_map(&map_a, Mat, m, n, 32, kBK);
+  const bool ok_b = make_map(&map_b, Xt, k_pad, kBN, kBK, kBN);
+  if (!ok_a || !ok_b) return cudaErrorInvalidValue;
+  const int tiles = int((out_rows + kBM - 1) / kBM);
+  const int total_kb = int(k_pad / kBK);
+  int splits = (148 * 2 + tiles - 1) / tiles;
+  const int max_splits = total_kb / 4 > 0 ? total_kb / 4 : 1;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  int kbps = (total_kb + splits - 1) / splits;
+  splits = (total_kb + kbps - 1) / kbps;
+  const size_t smem = sizeof(GemmSmem) + 1024;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[mode]) {
+    cudaError_t e = mode == 0 ? cudaFuncSetAttribute(psgd_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
+                              : cudaFuncSetAttribute(psgd_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return e;
+    attr_set[mode] = true;
+  }
+  const dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(splits), 1);
+  if (mode == 0)
+    psgd_gemm_kernel<0><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, out_rows, r, total_kb, kbps, out, status);
+  else
+    psgd_gemm_kernel<1><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, out_rows, r, total_kb, kbps, out, status);
+  return cudaGetLastError();
+}
+
+cudaError_t gram_schmidt(float* P, int64_t n, int r, float eps, cudaStream_t stream) {
+  if (n < 1 || r < 1 || r > kBN) return cudaErrorInvalidValue;
+  gram_schmidt_kernel<<<1, kGsThreads, 0, stream>>>(P, n, r, eps);
+  return cudaGetLastError();
+}
+
+cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int64_t m, int r,
+                                 float* Mat, float* residual, float* grad, int64_t N, int mode,
+                                 float post_scale, cudaStream_t stream) {
+  if (n < 1 || m < 1 || r < 1 || r > kBN || N > n * m) return cudaErrorInvalidValue;
+  int64_t blocks = (n * m + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (mode == 0)
+    expand_kernel<0><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, residual, grad, N, post_scale);
+  else
+    expand_kernel<1><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, residual, grad, N, post_scale);
+  return cudaGetLastError();
+}
+
+}  // namespace cuda
+}  // namespace hipress

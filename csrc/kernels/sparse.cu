@@ -1,0 +1,487 @@
+// Sampled-threshold top-k sparsifier (GradDrop / DGC payloads) for sm_100a,
+// with no host round-trip.
+//
+// The reference pipeline is transform(+) -> for_each(sample) -> sort -> D2H+sync
+// -> copy_if (implicit sync) -> sort + truncate -> H2D+sync -> for_each(gather)
+// (gd_body.h:121-229): four host synchronisations and two sorts.  Here:
+//
+//   sample x3   The k-th largest |value| of the random sample is found by a
+//               3-digit radix select (11+11+10 bits of the order-preserving key).
+//               Samples are *recomputed* from the LCG in every round instead of
+//               being stored and sorted, so no sample buffer exists.
+//   count       One pass: R += G (GradDrop), per-CTA count of |R| > threshold and
+//               first-digit histogram of those candidates.
+//   trim x2     Only when more than ceil(N*keep) candidates qualified (decided on
+//               the device; otherwise the kernels return at once): radix select of
+//               the exact cut among the candidates.
+//   recount     Per-CTA counts against the cut (only when trimming).
+//   scan        One CTA: exclusive offsets per CTA, k, the 4-byte header to every
+//               destination, and clearing of the histograms for the next call.
+//   write       Ordered compaction: indices ascending, values, residual zeroing,
+//               stored into every destination (local and NVLink peers), then the
+//               completion flag.
+//
+// Content rule (identical to the CPU codec): keep |R[i]| > threshold in
+// ascending index order; when over-selected keep the largest magnitudes, ties
+// toward the lower index.
+#include "../common/codec_math.h"
+#include "kernels.h"
+#include "p2p.cuh"
+
+namespace hipress {
+namespace cuda {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kBins = 2048;
+constexpr int kMaxBlocks = 148 * 4;
+constexpr int kTile = kThreads * 4;  // elements per CTA iteration
+
+struct SparseScratch {
+  unsigned int shist[3][kBins];  // sample radix-select rounds
+  unsigned int thist[3][kBins];  // trim radix-select rounds
+  unsigned int cnt_gt[kMaxBlocks], cnt_eq[kMaxBlocks];
+  unsigned int off_gt[kMaxBlocks], off_eq[kMaxBlocks];
+  // state words
+  // Radix-select progress, one slot per round: a kernel reads the slot of the
+  // previous round and writes its own, so no word is read and written by
+  // different CTAs of the same launch.
+  unsigned int s_prefix[3], s_rank[3];  // sample select
+  unsigned int t_prefix[3], t_rank[3];  // trim select
+  unsigned int thr_key;                 // threshold (key of a positive float)
+  unsigned int cand;                    // candidates over the threshold
+  unsigned int cut_key, ties_kept;      // final rule
+  unsigned int k;                       // elements emitted
+  unsigned int pad[3];
+};
+
+__device__ __forceinline__ int digit_of(uint32_t key, int round) {
+  return round == 0 ? int(key >> 21) : round == 1 ? int((key >> 10) & 0x7ffu) : int(key & 0x3ffu);
+}
+__device__ __forceinline__ bool prefix_matches(uint32_t key, int round, uint32_t prefix) {
+  return round == 0 ? true : round == 1 ? (key >> 21) == prefix : (key >> 10) == prefix;
+}
+__device__ __forceinline__ uint32_t extend_prefix(uint32_t prefix, int round, uint32_t digit) {
+  return round == 0 ? digit : round == 1 ? (prefix << 11) | digit : (prefix << 10) | digit;
+}
+
+// Block-wide: find the bin holding the element of 0-indexed `rank` counted from
+// the top bin down.  Every thread returns the same (bin, rank inside bin).
+__device__ void pick_from_top(const unsigned int* hist, unsigned int rank, unsigned int& bin,
+                              unsigned int& rank_in_bin) {
+  __shared__ unsigned int part[kThreads];
+  __shared__ unsigned int res[2];
+  constexpr int PER = kBins / kThreads;  // 8 bins per thread
+  const int t = threadIdx.x;
+  unsigned int local[PER];
+  unsigned int sum = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    local[j] = hist[kBins - 1 - (t * PER + j)];
+    sum += local[j];
+  }
+  part[t] = sum;
+  if (t == 0) {
+    res[0] = 0;
+    res[1] = 0;
+  }
+  __syncthreads();
+  // serial prefix by warp 0 is enough for 256 entries
+  if (t == 0) {
+    unsigned int run = 0;
+    for (int i = 0; i < kThreads; ++i) {
+      const unsigned int v = part[i];
+      part[i] = run;
+      run += v;
+    }
+  }
+  __syncthreads();
+  const unsigned int before = part[t];
+  if (rank >= before && rank < before + sum) {
+    unsigned int run = before;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      if (rank >= run && rank < run + local[j]) {
+        res[0] = kBins - 1 - (t * PER + j);
+        res[1] = rank - run;
+      }
+      run += local[j];
+    }
+  }
+  __syncthreads();
+  bin = res[0];
+  rank_in_bin = res[1];
+  __syncthreads();
+}
+
+__device__ __forceinline__ void hist_flush(unsigned int* sh, unsigned int* gh) {
+  __syncthreads();
+  for (int i = threadIdx.x; i < kBins; i += kThreads) {
+    const unsigned int v = sh[i];
+    if (v) atomicAdd(gh + i, v);
+  }
+}
+
+// ---- sample rounds
+template <int ROUND>
+__global__ void __launch_bounds__(kThreads)
+sample_round_kernel(const float* __restrict__ grad, const float* __restrict__ R, int64_t n,
+                    int64_t sample_cnt, unsigned int rank0, uint64_t seed, int accumulate,
+                    SparseScratch* s) {
+  __shared__ unsigned int sh[kBins];
+  for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
+  uint32_t prefix = 0;
+  if (ROUND > 0) {
+    const unsigned int rank = ROUND == 1 ? rank0 : s->s_rank[ROUND - 1];
+    unsigned int bin, rin;
+    pick_from_top(s->shist[ROUND - 1], rank, bin, rin);
+    prefix = extend_prefix(ROUND == 1 ? 0u : s->s_prefix[ROUND - 1], ROUND - 1, bin);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      // consumed by the next kernel in the stream
+      s->s_prefix[ROUND] = prefix;
+      s->s_rank[ROUND] = rin;
+    }
+  }
+  __syncthreads();
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < sample_cnt; x += stride) {
+    const uint32_t idx = sparse_sample_index(seed, x, uint32_t(n));
+    const float v = accumulate ? hp_add(grad[idx], R[idx]) : R[idx];
+    const uint32_t key = abs_key(v);
+    if (prefix_matches(key, ROUND, prefix)) atomicAdd(&sh[digit_of(key, ROUND)], 1u);
+  }
+  hist_flush(sh, s->shist[ROUND]);
+}
+
+// ---- count pass (also performs R += G)
+__global__ void __launch_bounds__(kThreads)
+count_kernel(const float* __restrict__ grad, float* __restrict__ R, int64_t n, int64_t chunk,
+             int64_t sample_cnt, unsigned int rank0, int accumulate, SparseScratch* s) {
+  __shared__ unsigned int sh[kBins];
+  __shared__ unsigned int blk_cnt;
+  for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
+  if (threadIdx.x == 0) blk_cnt = 0;
+  uint32_t thr_key = 0;
+  if (sample_cnt > 0) {
+    unsigned int bin, rin;
+    pick_from_top(s->shist[2], s->s_rank[2], bin, rin);
+    thr_key = extend_prefix(s->s_prefix[2], 2, bin);
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) s->thr_key = thr_key;
+  const int64_t begin = int64_t(blockIdx.x) * chunk;
+  const int64_t end = begin + chunk < n ? begin + chunk : n;
+  unsigned int mine = 0;
+  for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+    float r = R[i];
+    if (accumulate) {
+      r = hp_add(grad[i], r);
+      R[i] = r;
+    }
+    const uint32_t key = abs_key(r);
+    if (key > thr_key) {
+      ++mine;
+      atomicAdd(&sh[digit_of(key, 0)], 1u);
+    }
+  }
+  atomicAdd(&blk_cnt, mine);
+  hist_flush(sh, s->thist[0]);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s->cnt_gt[blockIdx.x] = blk_cnt;
+    s->cnt_eq[blockIdx.x] = 0;
+    atomicAdd(&s->cand, blk_cnt);
+  }
+}
+
+// ---- trim rounds 1 and 2 (return at once when not over-selected)
+template <int ROUND>
+__global__ void __launch_bounds__(kThreads)
+trim_round_kernel(const float* __restrict__ R, int64_t n, int64_t chunk, unsigned int expected,
+                  SparseScratch* s) {
+  if (s->cand <= expected) return;
+  __shared__ unsigned int sh[kBins];
+  for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
+  const unsigned int rank = ROUND == 1 ? expected - 1 : s->t_rank[ROUND - 1];
+  unsigned int bin, rin;
+  pick_from_top(s->thist[ROUND - 1], rank, bin, rin);
+  const uint32_t prefix = extend_prefix(ROUND == 1 ? 0u : s->t_prefix[ROUND - 1], ROUND - 1, bin);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    s->t_prefix[ROUND] = prefix;
+    s->t_rank[ROUND] = rin;
+  }
+  const uint32_t thr_key = s->thr_key;
+  __syncthreads();
+  const int64_t begin = int64_t(blockIdx.x) * chunk;
+  const int64_t end = begin + chunk < n ? begin + chunk : n;
+  for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+    const uint32_t key = abs_key(R[i]);
+    if (key > thr_key && prefix_matches(key, ROUND, prefix))
+      atomicAdd(&sh[digit_of(key, ROUND)], 1u);
+  }
+  hist_flush(sh, s->thist[ROUND]);
+}
+
+// ---- final rule + per-CTA counts against the cut
+__global__ void __launch_bounds__(kThreads)
+recount_kernel(const float* __restrict__ R, int64_t n, int64_t chunk, unsigned int expected,
+               SparseScratch* s) {
+  if (s->cand <= expected) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      s->cut_key = s->thr_key;
+      s->ties_kept = 0;
+    }
+    return;  // counts of the count pass stand
+  }
+  unsigned int bin, rin;
+  pick_from_top(s->thist[2], s->t_rank[2], bin, rin);
+  const uint32_t cut = extend_prefix(s->t_prefix[2], 2, bin);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    s->cut_key = cut;
+    s->ties_kept = rin + 1;
+  }
+  __shared__ unsigned int c_gt, c_eq;
+  if (threadIdx.x == 0) {
+    c_gt = 0;
+    c_eq = 0;
+  }
+  __syncthreads();
+  const int64_t begin = int64_t(blockIdx.x) * chunk;
+  const int64_t end = begin + chunk < n ? begin + chunk : n;
+  unsigned int g = 0, e = 0;
+  for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+    const uint32_t key = abs_key(R[i]);
+    g += key > cut;
+    e += key == cut;
+  }
+  atomicAdd(&c_gt, g);
+  atomicAdd(&c_eq, e);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s->cnt_gt[blockIdx.x] = c_gt;
+    s->cnt_eq[blockIdx.x] = c_eq;
+  }
+}
+
+// ---- one CTA: offsets, k, header, housekeeping
+__global__ void __launch_bounds__(1024)
+scan_kernel(int blocks, PushTargets dst, SparseScratch* s) {
+  __shared__ unsigned int a[1024], b[1024];
+  const int t = threadIdx.x;
+  a[t] = t < blocks ? s->cnt_gt[t] : 0;
+  b[t] = t < blocks ? s->cnt_eq[t] : 0;
+  __syncthreads();
+  if (t == 0) {
+    unsigned int ra = 0, rb = 0;
+    for (int i = 0; i < blocks; ++i) {
+      const unsigned int va = a[i], vb = b[i];
+      a[i] = ra;
+      b[i] = rb;
+      ra += va;
+      rb += vb;
+    }
+    const unsigned int ties = s->ties_kept;
+    const unsigned int k = ra + (rb < ties ? rb : ties);
+    s->k = k;
+    const uint32_t total = 4u + 8u * k;
+    uint8_t header[4];
+    for (int i = 0; i < 4; ++i) header[i] = uint8_t(total >> (8 * i));
+    push_bytes(dst, 0, header, 4);
+    s->cand = 0;
+  }
+  __syncthreads();
+  if (t < blocks) {
+    s->off_gt[t] = a[t];
+    s->off_eq[t] = b[t];
+  }
+  unsigned int* h = &s->shist[0][0];
+  for (int i = t; i < 6 * kBins; i += 1024) h[i] = 0;
+}
+
+// ---- ordered compaction and delivery
+__global__ void __launch_bounds__(kThreads)
+write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
+             const SparseScratch* s) {
+  __shared__ unsigned int warp_k[kThreads / 32], warp_e[kThreads / 32];
+  __shared__ unsigned int run_k, run_e;
+  const uint32_t cut = s->cut_key;
+  const unsigned int ties = s->ties_kept;
+  const unsigned int k_total = s->k;
+  const unsigned int eq_before_blk = s->off_eq[blockIdx.x];
+  if (threadIdx.x == 0) {
+    // kept elements before this CTA = gt before + kept ties before
+    run_k = s->off_gt[blockIdx.x] + (eq_before_blk < ties ? eq_before_blk : ties);
+    run_e = eq_before_blk;
+  }
+  __syncthreads();
+  const int64_t begin = int64_t(blockIdx.x) * chunk;
+  const int64_t end = begin + chunk < n ? begin + chunk : n;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int64_t base = begin; base < end; base += kTile) {
+    // thread owns 4 consecutive elements so that output order is index order
+    const int64_t e0 = base + int64_t(threadIdx.x) * 4;
+    float v[4];
+    uint32_t key[4];
+    unsigned int n_eq = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = (e0 + j < end) ? R[e0 + j] : 0.0f;
+      key[j] = (e0 + j < end) ? abs_key(v[j]) : 0u;
+      n_eq += (e0 + j < end) && key[j] == cut;
+    }
+    // exclusive scan of tie counts across the CTA (ties decide who is kept)
+    unsigned int inc_e = n_eq;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned int y = __shfl_up_sync(0xffffffffu, inc_e, o);
+      if (lane >= o) inc_e += y;
+    }
+    if (lane == 31) warp_e[warp] = inc_e;
+    __syncthreads();
+    unsigned int eq_rank = run_e + inc_e - n_eq;
+    for (int w = 0; w < warp; ++w) eq_rank += warp_e[w];
+    bool keep[4];
+    unsigned int n_keep = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool in = e0 + j < end;
+      keep[j] = in && key[j] > cut;
+      if (in && ties > 0 && key[j] == cut) {
+        keep[j] = eq_rank < ties;
+        ++eq_rank;
+      }
+      n_keep += keep[j];
+    }
+    unsigned int inc_k = n_keep;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned int y = __shfl_up_sync(0xffffffffu, inc_k, o);
+      if (lane >= o) inc_k += y;
+    }
+    if (lane == 31) warp_k[warp] = inc_k;
+    __syncthreads();
+    unsigned int pos = run_k + inc_k - n_keep;
+    for (int w = 0; w < warp; ++w) pos += warp_k[w];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (keep[j] && pos < k_total) {
+        const uint32_t idx = uint32_t(e0 + j);
+        push_u32(dst, 4 + 4 * int64_t(pos), idx);
+        push_u32(dst, 4 + 4 * int64_t(k_total) + 4 * int64_t(pos), __float_as_uint(v[j]));
+        R[e0 + j] = 0.0f;
+        ++pos;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int tk = 0, te = 0;
+      for (int w = 0; w < kThreads / 32; ++w) {
+        tk += warp_k[w];
+        te += warp_e[w];
+      }
+      run_k += tk;
+      run_e += te;
+    }
+    __syncthreads();
+  }
+  publish_when_grid_done(dst);
+}
+
+__global__ void __launch_bounds__(kThreads)
+scatter_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restrict__ out, int64_t n,
+               float post_scale, int* status) {
+  uint32_t total = 0;
+  for (int k = 0; k < 4; ++k) total |= uint32_t(payload[k]) << (8 * k);
+  if (total < 4 || int64_t(total) > cap) {
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status) atomicExch(status, int(kPayloadBounds));
+    return;
+  }
+  const int64_t k = (int64_t(total) - 4) / 8;
+  const uint32_t* idx = reinterpret_cast<const uint32_t*>(payload + 4);
+  const uint32_t* val = reinterpret_cast<const uint32_t*>(payload + 4 + 4 * k);
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < k; x += stride) {
+    const uint32_t i = idx[x];
+    if (int64_t(i) >= n) {
+      if (status) atomicExch(status, int(kPayloadBounds));
+      continue;
+    }
+    float v = __uint_as_float(val[x]);
+    if (post_scale != 1.0f) v = hp_mul(v, post_scale);
+    // indices are unique inside one payload: a plain read-modify-write is race free
+    out[i] = hp_add(out[i], v);
+  }
+}
+
+struct Plan {
+  int blocks;
+  int64_t chunk;
+};
+inline Plan plan_for(int64_t n) {
+  int64_t blocks = (n + kTile - 1) / kTile;
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  if (blocks < 1) blocks = 1;
+  int64_t chunk = (n + blocks - 1) / blocks;
+  chunk = (chunk + kTile - 1) / kTile * kTile;
+  blocks = (n + chunk - 1) / chunk;
+  return {int(blocks), chunk};
+}
+
+}  // namespace
+
+size_t sparse_scratch_bytes(int64_t) { return sizeof(SparseScratch); }
+
+cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sample_rate,
+                            double keep_fraction, uint64_t seed, int accumulate,
+                            const PushTargets& dst, void* scratch, cudaStream_t stream) {
+  if (n <= 0 || n > 0x7fffffff || scratch == nullptr) return cudaErrorInvalidValue;
+  for (int p = 0; p < dst.world; ++p)
+    if (reinterpret_cast<uintptr_t>(dst.payload[p]) & 3) return cudaErrorInvalidValue;
+  auto* s = static_cast<SparseScratch*>(scratch);
+  const Plan pl = plan_for(n);
+  int64_t expected = sparse_expected_k(n, keep_fraction);
+  if (expected > n) expected = n;
+  const int64_t sample_cnt = sparse_sample_count(n, sample_rate);
+  int64_t rank0 = sparse_threshold_rank(sample_cnt, keep_fraction);
+  if (sample_cnt > 0 && rank0 > sample_cnt - 1) rank0 = sample_cnt - 1;
+  if (sample_cnt > 0) {
+    int64_t sb = (sample_cnt + kThreads - 1) / kThreads;
+    if (sb > kMaxBlocks) sb = kMaxBlocks;
+    sample_round_kernel<0><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s);
+    sample_round_kernel<1><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s);
+    sample_round_kernel<2><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s);
+  }
+  count_kernel<<<pl.blocks, kThreads, 0, stream>>>(grad, R, n, pl.chunk, sample_cnt, unsigned(rank0), accumulate, s);
+  trim_round_kernel<1><<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
+  trim_round_kernel<2><<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
+  recount_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
+  PushTargets hdr = dst;
+  hdr.done = nullptr;
+  scan_kernel<<<1, 1024, 0, stream>>>(pl.blocks, hdr, s);
+  write_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, dst, s);
+  return cudaGetLastError();
+}
+
+cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
+                                float post_scale, int* status, cudaStream_t stream) {
+  if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
+  if (!add) {
+    cudaError_t e = cudaMemsetAsync(out, 0, size_t(n) * sizeof(float), stream);
+    if (e != cudaSuccess) return e;
+  }
+  for (int r = 0; r < src.world; ++r) {
+    if (reinterpret_cast<uintptr_t>(src.payload[r]) & 3) return cudaErrorInvalidValue;
+    // worst-case k is bounded by the slot capacity
+    const int64_t kmax = (src.payload_bytes[r] - 4) / 8;
+    int64_t blocks = (kmax + kThreads - 1) / kThreads;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    scatter_kernel<<<int(blocks), kThreads, 0, stream>>>(src.payload[r], src.payload_bytes[r], out,
+                                                        n, post_scale, status);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace cuda
+}  // namespace hipress

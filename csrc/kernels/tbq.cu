@@ -1,0 +1,168 @@
+// TBQ (threshold quantisation with residual feedback) for sm_100a.
+//
+// Compress: one pass that reads grad and residual with 16-byte loads, updates
+// the residual, packs four 2-bit fields per byte, gathers the bytes of four
+// lanes into one 32-bit word and stores that word into every destination
+// (local buffer and/or NVLink peer slots).  The partial last byte is produced
+// in the same kernel, so there is no host round-trip (the reference finishes
+// the tail on the host: tbq_body.h:114-155).
+//
+// Unpack-accumulate: one pass over the dense tensor that decodes the payloads
+// of all ranks in ascending rank order (the reference launches one full pass
+// per peer payload: hp_cuda_kernel.cu:182-196), optionally scales the sum and
+// applies a fused SGD-momentum update.
+#include "../common/codec_math.h"
+#include "kernels.h"
+#include "p2p.cuh"
+
+namespace hipress {
+namespace cuda {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+tbq_compress_kernel(const float* __restrict__ grad, float* __restrict__ residual, int64_t n,
+                    float thr, PushTargets dst) {
+  const int64_t nquads = n >> 2;                    // full bytes
+  const int64_t nquads_padded = (nquads + 31) & ~int64_t(31);  // whole warps iterate together
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t q = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; q < nquads_padded; q += stride) {
+    uint32_t byte = 0;
+    if (q < nquads) {
+      float g[4], r[4];
+      if (VEC) {
+        const float4 gv = __ldg(reinterpret_cast<const float4*>(grad) + q);
+        const float4 rv = reinterpret_cast<const float4*>(residual)[q];
+        g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+        r[0] = rv.x; r[1] = rv.y; r[2] = rv.z; r[3] = rv.w;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          g[k] = grad[4 * q + k];
+          r[k] = residual[4 * q + k];
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) byte |= tbq_quant(r[k], g[k], thr) << (2 * k);
+      if (VEC) {
+        reinterpret_cast<float4*>(residual)[q] = make_float4(r[0], r[1], r[2], r[3]);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) residual[4 * q + k] = r[k];
+      }
+    }
+    const uint32_t word = gather4_bytes(byte);
+    if ((threadIdx.x & 3) == 0 && q < nquads) {
+      if (q + 3 < nquads) {
+        push_u32(dst, q, word);
+      } else {
+        for (int64_t b = q; b < nquads; ++b) push_u8(dst, b, uint8_t(word >> (8 * (b - q))));
+      }
+    }
+  }
+  // partial last byte: unused fields stay "zero" (01)
+  const int rem = int(n & 3);
+  if (rem && blockIdx.x == 0 && threadIdx.x == 0) {
+    uint32_t byte = kTbqEmptyByte;
+    for (int k = 0; k < rem; ++k) {
+      const int64_t j = (nquads << 2) + k;
+      float r = residual[j];
+      const uint32_t f = tbq_quant(r, grad[j], thr);
+      residual[j] = r;
+      byte = (byte & ~(3u << (2 * k))) | (f << (2 * k));
+    }
+    push_u8(dst, nquads, uint8_t(byte));
+  }
+  publish_when_grid_done(dst);
+}
+
+template <bool VEC, bool APPLY>
+__global__ void __launch_bounds__(kThreads)
+tbq_unpack_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
+                  float post_scale, SgdApply apply) {
+  const int64_t nbytes = (n + 3) >> 2;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t b = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < nbytes; b += stride) {
+    const int64_t e0 = b << 2;
+    const int cnt = (n - e0) >= 4 ? 4 : int(n - e0);
+    float acc[4];
+    const bool vec = VEC && cnt == 4;
+    if (add) {
+      if (vec) {
+        const float4 o = reinterpret_cast<const float4*>(out)[b];
+        acc[0] = o.x; acc[1] = o.y; acc[2] = o.z; acc[3] = o.w;
+      } else {
+        for (int k = 0; k < cnt; ++k) acc[k] = out[e0 + k];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+      if (r < src.world) {
+        const uint32_t byte = src.payload[r][b];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float v = tbq_dequant((byte >> (2 * k)) & 3u, thr);
+          acc[k] = (r == 0 && !add) ? v : hp_add(v, acc[k]);
+        }
+      }
+    }
+    if (post_scale != 1.0f) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[k] = hp_mul(acc[k], post_scale);
+    }
+    if (vec) {
+      reinterpret_cast<float4*>(out)[b] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else {
+      for (int k = 0; k < cnt; ++k) out[e0 + k] = acc[k];
+    }
+    if (APPLY) {
+      for (int k = 0; k < cnt; ++k) sgd_update(apply, e0 + k, acc[k]);
+    }
+  }
+}
+
+inline int grid_for(int64_t items, int threads, int max_blocks) {
+  int64_t blocks = (items + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  if (blocks > max_blocks) blocks = max_blocks;
+  return int(blocks);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+cudaError_t tbq_compress(const float* grad, float* residual, int64_t n, float threshold,
+                         const PushTargets& dst, cudaStream_t stream) {
+  if (n <= 0) return cudaErrorInvalidValue;
+  // 148 SMs x 8 resident CTAs of 256 threads
+  const int grid = grid_for(n >> 2, kThreads, 148 * 8);
+  if (aligned16(grad) && aligned16(residual))
+    tbq_compress_kernel<true><<<grid, kThreads, 0, stream>>>(grad, residual, n, threshold, dst);
+  else
+    tbq_compress_kernel<false><<<grid, kThreads, 0, stream>>>(grad, residual, n, threshold, dst);
+  return cudaGetLastError();
+}
+
+cudaError_t tbq_unpack_accum(const UnpackSources& src, float threshold, float* out, int64_t n,
+                             int add, float post_scale, const SgdApply& apply,
+                             cudaStream_t stream) {
+  if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
+  const int grid = grid_for((n + 3) >> 2, kThreads, 148 * 8);
+  const bool vec = aligned16(out);
+  const bool ap = apply.param != nullptr;
+#define LAUNCH(V, A) \
+  tbq_unpack_kernel<V, A><<<grid, kThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply)
+  if (vec && ap) LAUNCH(true, true);
+  else if (vec) LAUNCH(true, false);
+  else if (ap) LAUNCH(false, true);
+  else LAUNCH(false, false);
+#undef LAUNCH
+  return cudaGetLastError();
+}
+
+}  // namespace cuda
+}  // namespace hipress

@@ -1,0 +1,340 @@
+// Min-max k-bit quantiser ("TernGrad" codec of the reference) for sm_100a.
+//
+// Compress is two kernels and no host synchronisation:
+//   1. minmax_header_kernel  grid reduction of min/max over grad (+ residual);
+//      the last CTA derives gap and 1/(gap+1e-8) (in double, as the reference's
+//      host code does: terngrad_body.h:205-206), stores them for kernel 2 and
+//      writes the 10-byte header into every destination.
+//   2. tern_quant_kernel     quantises with per-byte LCG stochastic rounding
+//      (or round-half-even), packs, stores the bytes into every destination,
+//      optionally writes the error-feedback residual, handles the always
+//      deterministic partial last byte in-kernel, then publishes the flag.
+// The reference needs minmax_element + D2H + sync, a header H2D, a transform,
+// and a second D2H/sync/H2D for the tail (terngrad_body.h:186-298).
+//
+// Unpack-accumulate decodes the payloads of all ranks in one pass, each with
+// its own header, in ascending rank order.
+#include "../common/codec_math.h"
+#include "kernels.h"
+#include "p2p.cuh"
+#include "reduce.cuh"
+
+namespace hipress {
+namespace cuda {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+inline int grid_for(int64_t items, int threads, int max_blocks) {
+  int64_t blocks = (items + threads - 1) / threads;
+  if (blocks < 1) blocks = 1;
+  if (blocks > max_blocks) blocks = max_blocks;
+  return int(blocks);
+}
+
+template <bool VEC, bool EF>
+__global__ void __launch_bounds__(kThreads)
+minmax_header_kernel(const float* __restrict__ grad, const float* __restrict__ residual, int64_t n,
+                     int bw, PushTargets dst, MinMaxScratch* scratch) {
+  float mn = INFINITY, mx = -INFINITY;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (VEC) {
+    const int64_t nv = n >> 2;
+    for (int64_t i = tid; i < nv; i += stride) {
+      float4 g = __ldg(reinterpret_cast<const float4*>(grad) + i);
+      if (EF) {
+        const float4 r = __ldg(reinterpret_cast<const float4*>(residual) + i);
+        g.x = hp_add(g.x, r.x); g.y = hp_add(g.y, r.y);
+        g.z = hp_add(g.z, r.z); g.w = hp_add(g.w, r.w);
+      }
+      mn = fminf(mn, fminf(fminf(g.x, g.y), fminf(g.z, g.w)));
+      mx = fmaxf(mx, fmaxf(fmaxf(g.x, g.y), fmaxf(g.z, g.w)));
+    }
+    for (int64_t i = (nv << 2) + tid; i < n; i += stride) {
+      const float v = EF ? hp_add(grad[i], residual[i]) : grad[i];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+  } else {
+    for (int64_t i = tid; i < n; i += stride) {
+      const float v = EF ? hp_add(grad[i], residual[i]) : grad[i];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+  }
+  float gmn, gmx;
+  if (!grid_minmax_last_block<kThreads>(scratch, mn, mx, gmn, gmx)) return;
+  if (threadIdx.x == 0) {
+    const float gap = tern_gap(gmn, gmx, bw);
+    scratch->mn = gmn;
+    scratch->mx = gmx;
+    scratch->gap = gap;
+    scratch->inv = tern_gap_inverse(gap);
+    uint8_t header[kTernHeaderBytes];
+    header[0] = uint8_t(bw);
+    header[1] = uint8_t(tern_tail(n, bw));
+    const uint32_t a = __float_as_uint(gmn), b = __float_as_uint(gmx);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      header[2 + k] = uint8_t(a >> (8 * k));
+      header[6 + k] = uint8_t(b >> (8 * k));
+    }
+    push_bytes(dst, 0, header, kTernHeaderBytes);
+  }
+}
+
+// Elements handled by one thread and bytes it produces.
+template <int BW> struct Unit {
+  static constexpr int DPB = 8 / BW;
+  static constexpr int EPT = DPB > 4 ? DPB : 4;  // elements per thread
+  static constexpr int BPT = EPT / DPB;          // bytes per thread: 1,1,2,4
+};
+
+template <int BW, bool VEC, bool EF>
+__global__ void __launch_bounds__(kThreads)
+tern_quant_kernel(const float* __restrict__ grad, float* __restrict__ residual, int64_t n,
+                  int random, uint64_t seed, PushTargets dst, const MinMaxScratch* scratch) {
+  constexpr int DPB = Unit<BW>::DPB, EPT = Unit<BW>::EPT, BPT = Unit<BW>::BPT;
+  const float mn = scratch->mn, inv = scratch->inv, gap = scratch->gap;
+  const int64_t units = n / EPT;
+  const int64_t units_padded = (units + 31) & ~int64_t(31);
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t u = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; u < units_padded; u += stride) {
+    uint32_t bytes = 0;
+    if (u < units) {
+      float x[EPT], ef[EPT];
+      const int64_t e0 = u * EPT;
+      if (VEC) {
+#pragma unroll
+        for (int v = 0; v < EPT / 4; ++v) {
+          float4 g = __ldg(reinterpret_cast<const float4*>(grad + e0) + v);
+          if (EF) {
+            const float4 r = reinterpret_cast<const float4*>(residual + e0)[v];
+            g.x = hp_add(g.x, r.x); g.y = hp_add(g.y, r.y);
+            g.z = hp_add(g.z, r.z); g.w = hp_add(g.w, r.w);
+          }
+          x[4 * v] = g.x; x[4 * v + 1] = g.y; x[4 * v + 2] = g.z; x[4 * v + 3] = g.w;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPT; ++k)
+          x[k] = EF ? hp_add(grad[e0 + k], residual[e0 + k]) : grad[e0 + k];
+      }
+#pragma unroll
+      for (int b = 0; b < BPT; ++b) {
+        const int64_t byte_index = u * BPT + b;
+        const uint8_t q = tern_pack_byte<BW>(x + b * DPB, DPB, mn, inv, random != 0,
+                                             tern_byte_seed(seed, byte_index), gap,
+                                             EF ? ef + b * DPB : nullptr);
+        bytes |= uint32_t(q) << (8 * b);
+      }
+      if (EF) {
+        if (VEC) {
+#pragma unroll
+          for (int v = 0; v < EPT / 4; ++v)
+            reinterpret_cast<float4*>(residual + e0)[v] =
+                make_float4(ef[4 * v], ef[4 * v + 1], ef[4 * v + 2], ef[4 * v + 3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < EPT; ++k) residual[e0 + k] = ef[k];
+        }
+      }
+    }
+    // combine lanes into 32-bit words and store them to every destination
+    if (BPT == 1) {
+      const uint32_t word = gather4_bytes(bytes);
+      if ((threadIdx.x & 3) == 0 && u < units) {
+        if (u + 3 < units) {
+          push_u32(dst, kTernHeaderBytes + u, word);
+        } else {
+          for (int64_t b = u; b < units; ++b)
+            push_u8(dst, kTernHeaderBytes + b, uint8_t(word >> (8 * (b - u))));
+        }
+      }
+    } else if (BPT == 2) {
+      const uint32_t word = gather2_halves(bytes);
+      if ((threadIdx.x & 1) == 0 && u < units) {
+        if (u + 1 < units) {
+          push_u32(dst, kTernHeaderBytes + 2 * u, word);
+        } else {
+          push_u8(dst, kTernHeaderBytes + 2 * u, uint8_t(word));
+          push_u8(dst, kTernHeaderBytes + 2 * u + 1, uint8_t(word >> 8));
+        }
+      }
+    } else {
+      if (u < units) push_u32(dst, kTernHeaderBytes + 4 * u, bytes);
+    }
+  }
+  // leftover elements (fewer than EPT): whole bytes keep the requested rounding
+  // mode, the partial last byte is always deterministic
+  const int64_t done_elems = units * EPT;
+  if (done_elems < n && blockIdx.x == 0 && threadIdx.x == 0) {
+    int64_t byte_index = done_elems / DPB;
+    for (int64_t e = done_elems; e < n; e += DPB, ++byte_index) {
+      const int count = (n - e) >= DPB ? DPB : int(n - e);
+      float x[DPB], ef[DPB];
+      for (int j = 0; j < count; ++j)
+        x[j] = EF ? hp_add(grad[e + j], residual[e + j]) : grad[e + j];
+      const bool rnd = random != 0 && count == DPB;
+      const uint8_t q = tern_pack_byte<BW>(x, count, mn, inv, rnd,
+                                           tern_byte_seed(seed, byte_index), gap,
+                                           EF ? ef : nullptr);
+      push_u8(dst, kTernHeaderBytes + byte_index, q);
+      if (EF)
+        for (int j = 0; j < count; ++j) residual[e + j] = ef[j];
+    }
+  }
+  publish_when_grid_done(dst);
+}
+
+struct TernHeader {
+  float mn, gap;
+  int bw, ok;
+};
+
+__device__ __forceinline__ TernHeader read_header(const uint8_t* p, int64_t cap, int64_t n) {
+  TernHeader h;
+  h.bw = p[0];
+  const int tail = p[1];
+  uint32_t a = 0, b = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    a |= uint32_t(p[2 + k]) << (8 * k);
+    b |= uint32_t(p[6 + k]) << (8 * k);
+  }
+  h.mn = __uint_as_float(a);
+  h.ok = tern_bitwidth_ok(h.bw) && tern_payload_bytes(n, h.bw) <= cap && tail == tern_tail(n, h.bw);
+  h.gap = h.ok ? tern_gap(h.mn, __uint_as_float(b), h.bw) : 0.f;
+  return h;
+}
+
+template <bool APPLY>
+__global__ void __launch_bounds__(kThreads)
+tern_unpack_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
+                   float post_scale, SgdApply apply, int* status) {
+  __shared__ TernHeader hdr[kMaxWorld];
+  __shared__ int all_ok;
+  if (threadIdx.x == 0) all_ok = 1;
+  __syncthreads();
+  if (threadIdx.x < src.world) {
+    hdr[threadIdx.x] = read_header(src.payload[threadIdx.x], src.payload_bytes[threadIdx.x], n);
+    if (!hdr[threadIdx.x].ok) all_ok = 0;
+  }
+  __syncthreads();
+  if (!all_ok) {
+    if (blockIdx.x == 0 && threadIdx.x == 0 && status) atomicExch(status, int(kBadHeader));
+    return;
+  }
+  // one thread decodes 8 consecutive elements (1..8 payload bytes per rank)
+  const int64_t groups = (n + 7) >> 3;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  const bool vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  for (int64_t gidx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; gidx < groups; gidx += stride) {
+    const int64_t e0 = gidx << 3;
+    const int cnt = (n - e0) >= 8 ? 8 : int(n - e0);
+    float acc[8];
+    const bool v4 = vec && cnt == 8;
+    if (add) {
+      if (v4) {
+        const float4 a = reinterpret_cast<const float4*>(out + e0)[0];
+        const float4 b = reinterpret_cast<const float4*>(out + e0)[1];
+        acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w;
+        acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+      } else {
+        for (int k = 0; k < cnt; ++k) acc[k] = out[e0 + k];
+      }
+    }
+    for (int r = 0; r < src.world; ++r) {
+      const TernHeader h = hdr[r];
+      const uint8_t* data = src.payload[r] + kTernHeaderBytes;
+      // the 8 elements occupy bw bytes starting at e0*bw/8
+      uint64_t bits = 0;
+      const int64_t first = (e0 * h.bw) >> 3;
+      const int nb = (cnt * h.bw + 7) >> 3;
+      for (int b = 0; b < nb; ++b) bits |= uint64_t(data[first + b]) << (8 * b);
+      const uint32_t mask = (1u << h.bw) - 1u;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float v = tern_dequant(uint32_t(bits >> (k * h.bw)) & mask, h.gap, h.mn);
+        acc[k] = (r == 0 && !add) ? v : hp_add(v, acc[k]);
+      }
+    }
+    if (post_scale != 1.0f) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] = hp_mul(acc[k], post_scale);
+    }
+    if (v4) {
+      reinterpret_cast<float4*>(out + e0)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      reinterpret_cast<float4*>(out + e0)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else {
+      for (int k = 0; k < cnt; ++k) out[e0 + k] = acc[k];
+    }
+    if (APPLY) {
+      for (int k = 0; k < cnt; ++k) sgd_update(apply, e0 + k, acc[k]);
+    }
+  }
+}
+
+}  // namespace
+
+size_t minmax_scratch_bytes() { return sizeof(MinMaxScratch); }
+
+cudaError_t terngrad_compress(const float* grad, float* residual, int64_t n, int bitwidth,
+                              int enable_random, uint64_t seed, const PushTargets& dst,
+                              void* scratch, cudaStream_t stream) {
+  if (n <= 0 || !tern_bitwidth_ok(bitwidth) || scratch == nullptr) return cudaErrorInvalidValue;
+  auto* s = static_cast<MinMaxScratch*>(scratch);
+  const bool ef = residual != nullptr;
+  const bool vec = aligned16(grad) && (!ef || aligned16(residual));
+  PushTargets hdr_dst = dst;
+  hdr_dst.done = nullptr;  // only the quantising kernel publishes
+  {
+    const int grid = grid_for((n + 3) >> 2, kThreads, 148 * 4);
+#define LAUNCH(V, E) \
+  minmax_header_kernel<V, E><<<grid, kThreads, 0, stream>>>(grad, residual, n, bitwidth, hdr_dst, s)
+    if (vec && ef) LAUNCH(true, true);
+    else if (vec) LAUNCH(true, false);
+    else if (ef) LAUNCH(false, true);
+    else LAUNCH(false, false);
+#undef LAUNCH
+  }
+  {
+#define LAUNCH2(BW, V, E)                                                                   \
+  tern_quant_kernel<BW, V, E><<<grid_for(n / Unit<BW>::EPT, kThreads, 148 * 8), kThreads, 0, \
+                                stream>>>(grad, residual, n, enable_random, seed, dst, s)
+#define LAUNCH_BW(BW)                         \
+  do {                                        \
+    if (vec && ef) LAUNCH2(BW, true, true);   \
+    else if (vec) LAUNCH2(BW, true, false);   \
+    else if (ef) LAUNCH2(BW, false, true);    \
+    else LAUNCH2(BW, false, false);           \
+  } while (0)
+    switch (bitwidth) {
+      case 1: LAUNCH_BW(1); break;
+      case 2: LAUNCH_BW(2); break;
+      case 4: LAUNCH_BW(4); break;
+      default: LAUNCH_BW(8); break;
+    }
+#undef LAUNCH_BW
+#undef LAUNCH2
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t terngrad_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
+                                  float post_scale, const SgdApply& apply, int* status,
+                                  cudaStream_t stream) {
+  if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
+  const int grid = grid_for((n + 7) >> 3, kThreads, 148 * 8);
+  if (apply.param)
+    tern_unpack_kernel<true><<<grid, kThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
+  else
+    tern_unpack_kernel<false><<<grid, kThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
+  return cudaGetLastError();
+}
+
+}  // namespace cuda
+}  // namespace hipress

@@ -1,0 +1,78 @@
+// Tensor-level codec operations: the per-algorithm compress / decompress
+// entrypoints of the extension.  Each accepts CUDA tensors (sm_100a kernels on
+// the current stream, no host synchronisation) or CPU tensors (the CPU codec),
+// so the same call is both the product path and its oracle.
+//
+// They correspond to the reference's nine hp_cuda_* entrypoints
+// (ref hp_cuda.cpp:18-102, hp_cuda_kernel.cu:30-301), with two differences:
+// decompression takes the payloads of *all* ranks and makes one pass, and
+// stochastic rounding / sampling take an explicit seed instead of the clock.
+#pragma once
+#include <torch/extension.h>
+
+#include <vector>
+
+namespace hipress {
+namespace ops {
+
+// Payload sizes (bytes) for n fp32 elements.
+int64_t tbq_payload_bytes(int64_t n);
+int64_t terngrad_payload_bytes(int64_t n, int64_t bitwidth);
+int64_t sparse_payload_bytes(int64_t n, double keep_fraction);
+int64_t ecq_payload_bytes(int64_t n, int64_t bitwidth);
+
+void tbq_compress(const torch::Tensor& grad, torch::Tensor residual, torch::Tensor out,
+                  double threshold);
+// payloads: one uint8 tensor per rank, accumulated in list order.
+void tbq_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, double threshold,
+                    bool add, double post_scale);
+
+void terngrad_compress(const torch::Tensor& grad, torch::Tensor out, int64_t bitwidth,
+                       bool enable_random, int64_t seed, c10::optional<torch::Tensor> residual);
+void terngrad_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
+                         double post_scale);
+
+// accumulate: R += grad first (GradDrop).  Otherwise grad may be undefined (DGC).
+void sparse_compress(const c10::optional<torch::Tensor>& grad, torch::Tensor R, torch::Tensor out,
+                     double sample_rate, double keep_fraction, int64_t seed, bool accumulate);
+void sparse_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
+                       double post_scale);
+
+void ecq_compress(const torch::Tensor& grad, torch::Tensor history, torch::Tensor out, double alpha,
+                  double beta, int64_t bitwidth, int64_t seed);
+void ecq_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
+                    double post_scale);
+
+// PowerSGD stages (intended maths of ref powersgd_body.h:10-78; the shipped
+// code copies every result into a temporary and so computes nothing).
+//   encode1: M[:N] = grad + residual;  P = M Q
+//   encode2: P = orthonormalise(P);    Q = M^T P
+//   decode : M = P Q^T; residual = grad - M[:N]; grad = M[:N]
+// CUDA tensors run the tcgen05 GEMMs (TF32 inputs, fp32 accumulation).
+void powersgd_encode1(const torch::Tensor& grad, const torch::Tensor& residual,
+                      const torch::Tensor& Q, torch::Tensor M, torch::Tensor P);
+void powersgd_encode2(torch::Tensor P, const torch::Tensor& M, torch::Tensor Q);
+void powersgd_decode(const torch::Tensor& P, const torch::Tensor& Q, torch::Tensor M,
+                     torch::Tensor residual, torch::Tensor grad);
+// Building blocks of the data-parallel PowerSGD compressor.
+// out (+)= M X  (mode 0, out is n x r, X is m x r)  or  M^T X  (mode 1, out is m x r, X is n x r).
+// `owners`: one tensor per rank with out's shape; each output row is added into
+// the tensor of the rank that owns it (even row split).  zero_first clears the
+// local tensor before accumulating.  simt forces the non-tensor-core kernel.
+void psgd_project(int64_t mode, const torch::Tensor& M, const torch::Tensor& X,
+                  const std::vector<torch::Tensor>& owners, bool simt);
+void gram_schmidt(torch::Tensor P, double eps);
+// grad_out[:N] = post_scale * P Q^T ; M -= P Q^T   (error feedback stays in M)
+void psgd_expand_feedback(const torch::Tensor& P, const torch::Tensor& Q, torch::Tensor M,
+                          torch::Tensor grad_out, double post_scale);
+
+// Device status word of the last bounds / header failure seen by kernels
+// launched through these ops on the tensor's device (0 = none); reading it
+// synchronises the current stream.
+int64_t read_status(const torch::Tensor& like, bool reset);
+// Zero-initialised per-(device, stream) scratch used by kernels that need it.
+void* scratch_for(const torch::Tensor& like, size_t bytes);
+int* status_word_for(const torch::Tensor& like);
+
+}  // namespace ops
+}  // namespace hipress

@@ -1,0 +1,351 @@
+#include "ddp_engine.h"
+
+#include <cstring>
+#include <stdexcept>
+
+#include "../common/codec_math.h"
+
+namespace hipress {
+namespace runtime {
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+  if (e != cudaSuccess)
+    throw std::runtime_error(std::string("hipress engine: ") + what + ": " + cudaGetErrorString(e));
+}
+int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
+
+constexpr size_t kScratchBytes = 256 * 1024;
+
+}  // namespace
+
+int64_t DdpEngine::payload_capacity(int b) const {
+  const int64_t n = buckets_.at(static_cast<size_t>(b)).numel;
+  switch (cfg_.codec) {
+    case Codec::kDense: return n * 4;
+    case Codec::kTbq: return tbq_payload_bytes(n);
+    case Codec::kTernGrad: return tern_payload_bytes(n, cfg_.bitwidth);
+    case Codec::kSparse:
+      return sparse_payload_bytes(std::min<int64_t>(n, sparse_expected_k(n, cfg_.keep_fraction)));
+    case Codec::kEcq: return ecq_payload_bytes(n, cfg_.bitwidth);
+  }
+  return 0;
+}
+
+DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buckets,
+                     const std::vector<int>& param_bucket)
+    : cfg_(cfg), buckets_(buckets), param_bucket_(param_bucket), keep_fraction_(cfg.keep_fraction),
+      pending_params_(buckets.size()), submitted_(buckets.size()) {
+  if (cfg.world < 1 || cfg.world > cuda::kMaxWorld) throw std::invalid_argument("world must be 1..8");
+  if (cfg.rank < 0 || cfg.rank >= cfg.world) throw std::invalid_argument("bad rank");
+  if (cfg.codec == Codec::kTernGrad && !tern_bitwidth_ok(cfg.bitwidth))
+    throw std::invalid_argument("terngrad bitwidth must be 1, 2, 4 or 8");
+  if (cfg.codec == Codec::kEcq && !ecq_bitwidth_ok(cfg.bitwidth))
+    throw std::invalid_argument("ecq bitwidth must be 2, 4 or 8");
+  for (int pb : param_bucket)
+    if (pb < 0 || pb >= static_cast<int>(buckets.size())) throw std::invalid_argument("bad param->bucket map");
+
+  // symmetric layout: [flags of all buckets][slots parity 0][slots parity 1] per bucket
+  int64_t off = 0;
+  layouts_.resize(buckets.size());
+  for (size_t b = 0; b < buckets.size(); ++b) {
+    layouts_[b].flags = off;
+    off += round_up(int64_t(cfg.world) * 4, 128);
+  }
+  off = round_up(off, 1024);
+  for (size_t b = 0; b < buckets.size(); ++b) {
+    BucketLayout& L = layouts_[b];
+    // header-bearing payloads start 6 bytes into the slot so that the data
+    // region after the 10-byte header is 16-byte aligned for vector stores
+    L.shift = (cfg.codec == Codec::kTernGrad || cfg.codec == Codec::kEcq) ? 6 : 0;
+    L.slot_bytes = round_up(payload_capacity(int(b)) + L.shift, 256);
+    for (int p = 0; p < 2; ++p) {
+      L.slots[p] = off;
+      off += L.slot_bytes * cfg.world;
+    }
+  }
+  symmetric_bytes_ = round_up(off, 1024);
+
+  check(cudaSetDevice(cfg.device), "cudaSetDevice");
+  ready_events_.resize(buckets.size());
+  for (auto& e : ready_events_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
+  check(cudaMalloc(reinterpret_cast<void**>(&status_), 64), "cudaMalloc status");
+  check(cudaMemset(status_, 0, 64), "memset status");
+
+  const int nw = cfg.num_workers < 1 ? 1 : cfg.num_workers;
+  workers_.resize(static_cast<size_t>(nw));
+  int lo = 0, hi = 0;
+  check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "priority range");
+  for (auto& w : workers_) {
+    check(cudaStreamCreateWithPriority(&w.push, cudaStreamNonBlocking, hi), "stream");
+    check(cudaStreamCreateWithPriority(&w.recv, cudaStreamNonBlocking, hi), "stream");
+    check(cudaMalloc(&w.scratch, kScratchBytes), "cudaMalloc scratch");
+    check(cudaMemset(w.scratch, 0, kScratchBytes), "memset scratch");
+    check(cudaMalloc(reinterpret_cast<void**>(&w.done), 64), "cudaMalloc counter");
+    check(cudaMemset(w.done, 0, 64), "memset counter");
+    check(cudaEventCreateWithFlags(&w.tail, cudaEventDisableTiming), "event");
+  }
+  check(cudaDeviceSynchronize(), "sync");
+  const int device = cfg.device;
+  pool_ = std::make_unique<WorkerPool>(nw, [device](int) { cudaSetDevice(device); });
+}
+
+DdpEngine::~DdpEngine() {
+  if (pool_) {
+    try {
+      pool_->drain();
+    } catch (...) {
+    }
+    pool_->shutdown();
+  }
+  cudaSetDevice(cfg_.device);
+  cudaDeviceSynchronize();
+  for (auto& w : workers_) {
+    if (w.push) cudaStreamDestroy(w.push);
+    if (w.recv) cudaStreamDestroy(w.recv);
+    if (w.scratch) cudaFree(w.scratch);
+    if (w.done) cudaFree(w.done);
+    if (w.tail) cudaEventDestroy(w.tail);
+  }
+  for (auto& e : ready_events_) cudaEventDestroy(e);
+  if (status_) cudaFree(status_);
+}
+
+void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* momentum) {
+  grad_ = grad;
+  residual_ = residual;
+  param_ = param;
+  momentum_ = momentum;
+}
+
+void DdpEngine::set_symmetric(const std::vector<uint8_t*>& bases) {
+  if (static_cast<int>(bases.size()) != cfg_.world) throw std::invalid_argument("one base pointer per rank");
+  bases_ = bases;
+}
+
+void DdpEngine::set_sgd(float lr, float momentum, float weight_decay, bool fused) {
+  lr_ = lr;
+  sgd_mu_ = momentum;
+  wd_ = weight_decay;
+  fused_sgd_ = fused;
+}
+
+void DdpEngine::set_keep_fraction(double keep_fraction) {
+  if (keep_fraction <= 0.0 || keep_fraction > cfg_.keep_fraction)
+    throw std::invalid_argument("keep_fraction must be in (0, configured maximum]");
+  keep_fraction_ = keep_fraction;
+}
+
+void DdpEngine::begin_step() {
+  if (grad_ == nullptr || bases_.empty()) throw std::runtime_error("hipress engine: buffers not set");
+  ++epoch_;
+  for (size_t b = 0; b < buckets_.size(); ++b) {
+    pending_params_[b].store(buckets_[b].num_params);
+    submitted_[b].store(0);
+  }
+  std::lock_guard<std::mutex> lk(mu_);
+  issued_ = 0;
+  for (auto& w : workers_) w.used = false;
+}
+
+void DdpEngine::grad_ready(int param_index, cudaStream_t producer) {
+  const int b = param_bucket_.at(static_cast<size_t>(param_index));
+  if (pending_params_[static_cast<size_t>(b)].fetch_sub(1) == 1) bucket_ready(b, producer);
+}
+
+void DdpEngine::bucket_ready(int b, cudaStream_t producer) {
+  if (submitted_.at(static_cast<size_t>(b)).exchange(1) != 0) return;
+  check(cudaEventRecord(ready_events_[static_cast<size_t>(b)], producer), "cudaEventRecord");
+  const int worker = b % static_cast<int>(workers_.size());
+  pool_->submit_to(worker, [this, b](int w) {
+    try {
+      issue_bucket(b, w);
+    } catch (...) {
+      {
+        std::lock_guard<std::mutex> lk(mu_);
+        ++issued_;
+      }
+      cv_.notify_all();
+      throw;
+    }
+    {
+      std::lock_guard<std::mutex> lk(mu_);
+      ++issued_;
+    }
+    cv_.notify_all();
+  });
+}
+
+cuda::PushTargets DdpEngine::targets_for(int b, WorkerCtx& w) const {
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int parity = int(epoch_ & 1u);
+  cuda::PushTargets t;
+  t.world = cfg_.world;
+  t.epoch = epoch_;
+  t.done = w.done;
+  for (int p = 0; p < cfg_.world; ++p) {
+    uint8_t* base = bases_[static_cast<size_t>(p)];
+    t.payload[p] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
+    t.flag[p] = reinterpret_cast<uint32_t*>(base + L.flags) + cfg_.rank;
+  }
+  return t;
+}
+
+cuda::UnpackSources DdpEngine::sources_for(int b) const {
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int parity = int(epoch_ & 1u);
+  cuda::UnpackSources s;
+  s.world = cfg_.world;
+  uint8_t* base = bases_[static_cast<size_t>(cfg_.rank)];
+  for (int r = 0; r < cfg_.world; ++r) {
+    s.payload[r] = base + L.slots[parity] + int64_t(r) * L.slot_bytes + L.shift;
+    s.payload_bytes[r] = L.slot_bytes - L.shift;
+  }
+  return s;
+}
+
+void DdpEngine::issue_bucket(int b, int worker) {
+  WorkerCtx& w = workers_[static_cast<size_t>(worker)];
+  const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int64_t n = B.numel;
+  float* g = grad_ + B.offset;
+  float* res = residual_ ? residual_ + B.offset : nullptr;
+  const uint64_t seed = cfg_.seed + uint64_t(epoch_) * 0x9E3779B97F4A7C15ull + uint64_t(b) * 0x632BE59BD9B4E019ull;
+  const float post = cfg_.average ? 1.0f / float(cfg_.world) : 1.0f;
+  cuda::SgdApply apply;
+  if (fused_sgd_) {
+    apply.param = param_ + B.offset;
+    apply.momentum = momentum_ + B.offset;
+    apply.lr = lr_;
+    apply.mu = sgd_mu_;
+    apply.weight_decay = wd_;
+    apply.first_step = steps_ == 0 ? 1 : 0;
+  }
+  cuda::SgdApply none;
+
+  // ---- push stream: compress and deliver
+  check(cudaStreamWaitEvent(w.push, ready_events_[static_cast<size_t>(b)], 0), "wait ready");
+  cuda::PushTargets dst = targets_for(b, w);
+  int launched = 0;
+  switch (cfg_.codec) {
+    case Codec::kTbq:
+      if (!res) throw std::runtime_error("tbq needs a residual buffer");
+      check(cuda::tbq_compress(g, res, n, cfg_.threshold, dst, w.push), "tbq_compress");
+      launched += 1;
+      break;
+    case Codec::kTernGrad:
+      check(cuda::terngrad_compress(g, cfg_.error_feedback ? res : nullptr, n, cfg_.bitwidth,
+                                    cfg_.enable_random, seed, dst, w.scratch, w.push),
+            "terngrad_compress");
+      launched += 2;
+      break;
+    case Codec::kSparse:
+      if (!res) throw std::runtime_error("sparse codecs need a residual buffer");
+      check(cuda::sparse_compress(cfg_.sparse_accumulate ? g : nullptr, res, n, cfg_.sample_rate,
+                                  keep_fraction_, seed, cfg_.sparse_accumulate, dst,
+                                  static_cast<uint8_t*>(w.scratch) + 16384, w.push),
+            "sparse_compress");
+      launched += 9;
+      break;
+    case Codec::kEcq:
+      if (!res) throw std::runtime_error("ecq needs a history buffer");
+      check(cuda::ecq_compress(g, res, n, cfg_.alpha, cfg_.beta, cfg_.bitwidth, seed, dst,
+                               w.scratch, w.push),
+            "ecq_compress");
+      launched += 2;
+      break;
+    case Codec::kDense: {
+      // own slot in local memory; peers pull it
+      uint8_t* slot = bases_[static_cast<size_t>(cfg_.rank)] + L.slots[epoch_ & 1u] +
+                      int64_t(cfg_.rank) * L.slot_bytes;
+      check(cudaMemcpyAsync(slot, g, size_t(n) * 4, cudaMemcpyDeviceToDevice, w.push), "copy");
+      check(cuda::signal_flags(dst, w.push), "signal_flags");
+      launched += 1;
+      break;
+    }
+  }
+
+  // ---- recv stream: wait for all ranks, decode everything in one pass
+  const uint32_t* flags = reinterpret_cast<const uint32_t*>(bases_[static_cast<size_t>(cfg_.rank)] + L.flags);
+  check(cuda::wait_flags(flags, cfg_.world, epoch_, cfg_.flag_timeout_ns, status_, w.recv), "wait_flags");
+  launched += 1;
+  cuda::UnpackSources src = sources_for(b);
+  bool applied = false;
+  switch (cfg_.codec) {
+    case Codec::kTbq:
+      check(cuda::tbq_unpack_accum(src, cfg_.threshold, g, n, 0, post, apply, w.recv), "tbq_unpack");
+      applied = fused_sgd_;
+      launched += 1;
+      break;
+    case Codec::kTernGrad:
+      check(cuda::terngrad_unpack_accum(src, g, n, 0, post, apply, status_, w.recv), "tern_unpack");
+      applied = fused_sgd_;
+      launched += 1;
+      break;
+    case Codec::kSparse:
+      check(cuda::sparse_unpack_accum(src, g, n, 0, post, status_, w.recv), "sparse_unpack");
+      launched += cfg_.world;
+      break;
+    case Codec::kEcq:
+      check(cuda::ecq_unpack_accum(src, g, n, 0, post, status_, w.recv), "ecq_unpack");
+      launched += 1;
+      break;
+    case Codec::kDense: {
+      const float* srcs[cuda::kMaxWorld];
+      for (int r = 0; r < cfg_.world; ++r)
+        srcs[r] = reinterpret_cast<const float*>(bases_[static_cast<size_t>(r)] + L.slots[epoch_ & 1u] +
+                                                 int64_t(r) * L.slot_bytes);
+      check(cuda::dense_gather_sum(srcs, cfg_.world, g, n, post, w.recv), "dense_gather_sum");
+      launched += 1;
+      break;
+    }
+  }
+  if (fused_sgd_ && !applied) {
+    check(cuda::sgd_apply_dense(g, 1.0f, apply, n, w.recv), "sgd_apply_dense");
+    launched += 1;
+  }
+  check(cudaEventRecord(w.tail, w.recv), "record tail");
+  w.used = true;
+  launches_ += launched;
+}
+
+void DdpEngine::finish_step(cudaStream_t consumer) {
+  // flush buckets whose hooks did not all fire (parameters without gradient)
+  for (size_t b = 0; b < buckets_.size(); ++b)
+    if (submitted_[b].load() == 0) bucket_ready(int(b), consumer);
+  {
+    std::unique_lock<std::mutex> lk(mu_);
+    cv_.wait(lk, [&] { return issued_ >= static_cast<int>(buckets_.size()); });
+  }
+  if (pool_->error_count() > 0) {
+    const std::string err = pool_->last_error();
+    throw std::runtime_error("hipress engine: worker failed: " + err);
+  }
+  for (auto& w : workers_)
+    if (w.used) check(cudaStreamWaitEvent(consumer, w.tail, 0), "wait tail");
+  ++steps_;
+}
+
+int DdpEngine::check_status() {
+  int host[4] = {0, 0, 0, 0};
+  check(cudaDeviceSynchronize(), "sync");
+  check(cudaMemcpy(host, status_, sizeof(host), cudaMemcpyDeviceToHost), "read status");
+  if (host[0] != 0) check(cudaMemset(status_, 0, 64), "reset status");
+  return host[0];
+}
+
+int64_t DdpEngine::wire_bytes_per_step() const {
+  int64_t total = 0;
+  for (size_t b = 0; b < buckets_.size(); ++b) total += payload_capacity(int(b));
+  return total * (cfg_.world - 1);
+}
+int64_t DdpEngine::dense_bytes_per_step() const {
+  int64_t total = 0;
+  for (auto& b : buckets_) total += b.numel * 4;
+  return total;
+}
+
+}  // namespace runtime
+}  // namespace hipress

@@ -1,0 +1,152 @@
+// Data-parallel gradient synchronisation engine.
+//
+// Gradients live in one flat fp32 buffer cut into buckets.  Backward hooks
+// report parameters as ready; when the last parameter of a bucket is in, the
+// hook thread records an event on the producing stream and hands the bucket to
+// a worker thread, which issues on its own streams
+//
+//   push stream:  compress bucket -> packed bytes stored straight into every
+//                 rank's receive slot (peer memory over NVLink) -> epoch flag
+//   recv stream:  bounded wait on the W flags of the bucket -> one-pass
+//                 unpack + accumulate of all W payloads (+ optional fused
+//                 SGD-momentum update of the flat parameters)
+//
+// Compress kernels never wait on a peer and all waits sit on the recv stream,
+// so ranks cannot deadlock on bucket order.  Receive slots are double-buffered
+// by epoch parity; flags carry the epoch and are never reset.
+//
+// The reference has no such component: its caller submits per-tensor tasks,
+// polls for completion and moves CPU buffers with an external transport
+// (ref hp_cuda.cpp:904-1060).  This engine is the B200-native replacement for
+// that whole loop; nothing here touches the host except launch calls.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <condition_variable>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../kernels/kernels.h"
+#include "worker_pool.h"
+
+namespace hipress {
+namespace runtime {
+
+enum class Codec : int { kDense = 0, kTbq = 1, kTernGrad = 2, kSparse = 3, kEcq = 4 };
+
+struct EngineConfig {
+  int rank = 0, world = 1, device = 0;
+  Codec codec = Codec::kTernGrad;
+  // codec parameters
+  float threshold = 0.f;                 // tbq
+  int bitwidth = 2, enable_random = 1;   // terngrad / ecq
+  int error_feedback = 1;                // terngrad: keep a residual
+  double sample_rate = 0.01, keep_fraction = 0.001;  // sparse
+  int sparse_accumulate = 1;             // 1: R += g inside the codec (GradDrop)
+  float alpha = 1.f, beta = 1.f;         // ecq
+  uint64_t seed = 1;
+  int average = 1;                       // divide the sum by world
+  uint64_t flag_timeout_ns = 20ull * 1000 * 1000 * 1000;
+  int num_workers = 1;
+};
+
+struct BucketDesc {
+  int64_t offset = 0;   // first element in the flat buffers
+  int64_t numel = 0;
+  int num_params = 0;   // hooks that must fire before the bucket is ready
+};
+
+// Byte layout of one bucket inside the symmetric buffer.
+struct BucketLayout {
+  int64_t slot_bytes = 0;      // capacity of one rank's slot (multiple of 256)
+  int64_t slots[2] = {0, 0};   // offset of slot array [world][slot_bytes] per parity
+  int64_t flags = 0;           // offset of `world` uint32 flags
+  int64_t shift = 0;           // payload starts at slot + shift (aligns the data region)
+};
+
+class DdpEngine {
+ public:
+  DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buckets,
+            const std::vector<int>& param_bucket);
+  ~DdpEngine();
+
+  // Bytes of symmetric memory the buckets need; computed at construction.
+  int64_t symmetric_bytes() const { return symmetric_bytes_; }
+  const BucketLayout& layout(int b) const { return layouts_.at(static_cast<size_t>(b)); }
+  int64_t payload_capacity(int b) const;
+
+  // residual / param / momentum may be null when unused.
+  void set_buffers(float* grad, float* residual, float* param, float* momentum);
+  // bases[r]: rank r's symmetric buffer as mapped in this process.
+  void set_symmetric(const std::vector<uint8_t*>& bases);
+
+  void set_sgd(float lr, float momentum, float weight_decay, bool fused);
+  void set_keep_fraction(double keep_fraction);
+
+  void begin_step();
+  // Called from a backward hook; `producer` is the stream the gradient was
+  // written on.
+  void grad_ready(int param_index, cudaStream_t producer);
+  void bucket_ready(int bucket_index, cudaStream_t producer);
+  // Blocks until every bucket of this step has been issued, then makes
+  // `consumer` wait for the device work.  Buckets whose hooks never fired
+  // (unused parameters) are flushed here.
+  void finish_step(cudaStream_t consumer);
+
+  // Synchronises and returns the device status word (cuda::Status); resets it.
+  int check_status();
+  uint32_t epoch() const { return epoch_; }
+  int64_t steps() const { return steps_; }
+  // kernels launched by the engine since construction
+  int64_t launches() const { return launches_.load(); }
+  // wire bytes (compressed) and dense bytes of one step, for metrics
+  int64_t wire_bytes_per_step() const;
+  int64_t dense_bytes_per_step() const;
+  std::string last_error() { return pool_->last_error(); }
+
+ private:
+  struct WorkerCtx {
+    cudaStream_t push = nullptr, recv = nullptr;
+    void* scratch = nullptr;       // zeroed; minmax + sparse scratch
+    unsigned int* done = nullptr;  // last-CTA counter for publish
+    cudaEvent_t tail = nullptr;    // last recorded event on recv
+    bool used = false;
+  };
+  void issue_bucket(int b, int worker);
+  cuda::PushTargets targets_for(int b, WorkerCtx& w) const;
+  cuda::UnpackSources sources_for(int b) const;
+
+  EngineConfig cfg_;
+  std::vector<BucketDesc> buckets_;
+  std::vector<BucketLayout> layouts_;
+  std::vector<int> param_bucket_;
+  int64_t symmetric_bytes_ = 0;
+
+  float *grad_ = nullptr, *residual_ = nullptr, *param_ = nullptr, *momentum_ = nullptr;
+  std::vector<uint8_t*> bases_;
+  float lr_ = 0.f, sgd_mu_ = 0.f, wd_ = 0.f;
+  bool fused_sgd_ = false;
+  double keep_fraction_;
+
+  uint32_t epoch_ = 0;
+  int64_t steps_ = 0;
+  std::vector<std::atomic<int>> pending_params_;
+  std::vector<std::atomic<int>> submitted_;
+  std::vector<cudaEvent_t> ready_events_;
+  std::vector<WorkerCtx> workers_;
+  int* status_ = nullptr;
+
+  std::mutex mu_;
+  std::condition_variable cv_;
+  int issued_ = 0;
+  std::atomic<int64_t> launches_{0};
+
+  std::unique_ptr<WorkerPool> pool_;
+};
+
+}  // namespace runtime
+}  // namespace hipress

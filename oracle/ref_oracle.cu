@@ -1,0 +1,137 @@
+// Golden-vector harness: runs the reference's own codec headers on the host
+// (thrust::host policy, no GPU needed) so that this library's CPU codec and
+// kernels can be byte-compared against them.  It is a test tool only: it is
+// compiled on demand by tests/test_oracle.py against a checkout of the
+// reference given with -I, and nothing in the product links to it.
+//
+//   ref_oracle tbq_c  grad.bin resid.bin n threshold out.bin     (resid.bin updated in place)
+//   ref_oracle tbq_d  in.bin n threshold dense.bin add           (dense.bin updated in place)
+//   ref_oracle tern_c grad.bin n bitwidth random seed out.bin
+//   ref_oracle tern_d in.bin in_size dense.bin n add
+//   ref_oracle gd_d   in.bin in_size dense.bin n add
+//   ref_oracle lcg    seed count out.bin        (count x {u32 raw via int generator range 2^31, f32 unit})
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <string>
+#include <vector>
+
+
+#include <ZQ_CPP_LIB/gradient_compression_body/gd_body.h>
+#include <ZQ_CPP_LIB/gradient_compression_body/tbq_body.h>
+#include <ZQ_CPP_LIB/gradient_compression_body/terngrad_body.h>
+#include <ZQ_CPP_LIB/naive_random.hpp>
+
+using namespace zq_cpp_lib::gradient_compression_body;
+typedef thrust::detail::host_t policy_t;
+
+template <typename T>
+static std::vector<T> slurp(const char* path, size_t count) {
+  std::vector<T> v(count);
+  FILE* f = fopen(path, "rb");
+  if (!f || fread(v.data(), sizeof(T), count, f) != count) {
+    fprintf(stderr, "cannot read %zu items from %s\n", count, path);
+    exit(2);
+  }
+  fclose(f);
+  return v;
+}
+template <typename T>
+static void dump(const char* path, const std::vector<T>& v) {
+  FILE* f = fopen(path, "wb");
+  if (!f || fwrite(v.data(), sizeof(T), v.size(), f) != v.size()) {
+    fprintf(stderr, "cannot write %s\n", path);
+    exit(2);
+  }
+  fclose(f);
+}
+
+int main(int argc, char** argv) {
+  if (argc < 2) return 1;
+  const std::string cmd = argv[1];
+  policy_t policy = thrust::host;
+  if (cmd == "tbq_c") {
+    const int32_t n = atoi(argv[4]);
+    const float thr = strtof(argv[5], nullptr);
+    auto g = slurp<float>(argv[2], n);
+    auto r = slurp<float>(argv[3], n);
+    std::vector<uint8_t> out((n + 3) / 4, 0);
+    tbq_body<policy_t>(g.data(), n, r.data(), n, out.data(), (int32_t)out.size(), thr, policy,
+                       nullptr);
+    dump(argv[3], r);
+    dump(argv[6], out);
+  } else if (cmd == "tbq_d") {
+    const int32_t n = atoi(argv[3]);
+    const float thr = strtof(argv[4], nullptr);
+    auto in = slurp<uint8_t>(argv[2], (n + 3) / 4);
+    auto d = slurp<float>(argv[5], n);
+    tbq_r_body<policy_t>(d.data(), n, in.data(), (int32_t)in.size(), thr, atoi(argv[6]), policy,
+                         nullptr);
+    dump(argv[5], d);
+  } else if (cmd == "tern_c") {
+    const int32_t n = atoi(argv[3]);
+    const int bw = atoi(argv[4]);
+    const int random = atoi(argv[5]);
+    const unsigned long long seed = strtoull(argv[6], nullptr, 10);
+    auto g = slurp<float>(argv[2], n);
+    const int dpb = 8 / bw;
+    std::vector<uint8_t> out(10 + (n + dpb - 1) / dpb, 0);
+    // deterministic call: gives the header and the (always deterministic) tail byte
+    terngrad_body<policy_t>({g.data()}, {n}, {out.data()}, {(int32_t)out.size()},
+                            {(uint8_t)bw}, {0}, policy, nullptr);
+    if (random) {
+      // the shipped body seeds from the wall clock; its functor takes the seed
+      // as a constructor argument, so drive the functor directly for full bytes
+      float mn, mx;
+      memcpy(&mn, out.data() + 2, 4);
+      memcpy(&mx, out.data() + 6, 4);
+      float gap = (mx - mn) / ((1 << bw) - 1.0f);
+      float gap_inverse = 1. / (gap + 1e-8);
+      uint8_t lg2 = bw == 1 ? 3 : bw == 2 ? 2 : bw == 4 ? 1 : 0;
+      thrust::counting_iterator<int32_t> first(0);
+      thrust::transform(policy, first, first + (n >> lg2), out.data() + 10,
+                        compress_with_random(g.data(), (uint8_t)bw, lg2, mn, gap_inverse, seed));
+    }
+    dump(argv[7], out);
+  } else if (cmd == "tern_d") {
+    const int32_t in_size = atoi(argv[3]);
+    const int32_t n = atoi(argv[5]);
+    auto in = slurp<uint8_t>(argv[2], in_size);
+    auto d = slurp<float>(argv[4], n);
+    terngrad_r_body<policy_t>({d.data()}, {n}, {in.data()}, {in_size}, {atoi(argv[6])}, policy,
+                              nullptr);
+    dump(argv[4], d);
+  } else if (cmd == "gd_d") {
+    const int32_t in_size = atoi(argv[3]);
+    const int32_t n = atoi(argv[5]);
+    auto in = slurp<uint8_t>(argv[2], in_size);
+    auto d = slurp<float>(argv[4], n);
+    std::vector<uint8_t*> ins{in.data()};
+    std::vector<int32_t> in_sizes{in_size};
+    std::vector<float*> outs{d.data()};
+    std::vector<int32_t> out_sizes{n};
+    std::vector<int> adds{atoi(argv[6])};
+    gd_r_body<policy_t>(ins, in_sizes, outs, out_sizes, adds, policy, nullptr);
+    dump(argv[4], d);
+  } else if (cmd == "lcg") {
+    const uint32_t seed = (uint32_t)strtoull(argv[2], nullptr, 10);
+    const int count = atoi(argv[3]);
+    std::vector<uint32_t> out;
+    zq_cpp_lib::naive_int_random<uint32_t> ri(0, 0x7ffffffe);
+    zq_cpp_lib::naive_real_random<float> rr(0.0, 1.0);
+    ri.srand(seed);
+    rr.srand(seed);
+    for (int i = 0; i < count; ++i) {
+      uint32_t a = ri();
+      float f = rr();
+      uint32_t fb;
+      memcpy(&fb, &f, 4);
+      out.push_back(a);
+      out.push_back(fb);
+    }
+    dump(argv[4], out);
+  } else {
+    return 1;
+  }
+  return 0;
+}
