@@ -1,0 +1,321 @@
+"""Headline benchmark: data-parallel ResNet-50 training throughput (samples/s) with TernGrad
+2-bit gradient compression, at N GPUs of one node.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference ...      # the unmodified reference extension
+
+Config (per GPU): ResNet-50 v1.5, 64 images 3x224x224 fp32 ~N(0,1), uniform labels, SGD
+momentum 0.9 lr 0.1, random init, bf16 autocast, fp32 gradients in 25 MB buckets, TernGrad
+2-bit with error feedback.  Weak scaling.  Data is synthetic.
+
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events around exactly K steps,
+barrier + synchronise on both sides, max over ranks) with inputs resident on the device;
+``e2e`` is the same loop through the public API with, every step, the host-to-device copy of
+the step's batch from pinned memory and a device-to-host read of the loss.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL_BATCH = {"resnet50": 64, "vgg19": 64, "bert_large": 32}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="resnet50", choices=list(MODEL_BATCH))
+    ap.add_argument("--algorithm", default=None, help="terngrad | tbq | graddrop | dgc | ecq | dense | powersgd | nccl")
+    ap.add_argument("--batch", type=int, default=None, help="per-GPU batch")
+    return ap.parse_args()
+
+
+def setup_dist(args):
+    import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29500")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier():
+    import torch
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def make_batches(model_name, batch, rank, count=4):
+    from hipress_b200.utils import PinnedBatches, synthetic_images, synthetic_mlm
+    if model_name == "bert_large":
+        return PinnedBatches([synthetic_mlm(batch, 128, seed=1000 * rank + i) for i in range(count)])
+    return PinnedBatches([synthetic_images(batch, seed=1000 * rank + i) for i in range(count)])
+
+
+def default_algorithm(model_name):
+    return {"resnet50": "terngrad", "vgg19": "powersgd", "bert_large": "dgc"}[model_name]
+
+
+# ------------------------------------------------------------------------------------ ours
+class OurTrainer:
+    """Flagship path of this framework through its public API."""
+
+    def __init__(self, args, rank, world, local):
+        import torch
+        from hipress_b200 import models
+        from hipress_b200.parallel import CompressedDataParallel, CompressionConfig
+        self.torch = torch
+        self.dev = torch.device("cuda", local)
+        self.model_name = args.model
+        self.algorithm = args.algorithm or default_algorithm(args.model)
+        torch.manual_seed(0)
+        net = getattr(models, args.model)().to(self.dev)
+        self.is_image = args.model != "bert_large"
+        if self.is_image:
+            net = net.to(memory_format=torch.channels_last)
+        net.train()
+        if self.algorithm == "powersgd":
+            from hipress_b200.parallel.powersgd import PowerSGDDataParallel
+            self.model = PowerSGDDataParallel(net, rank_r=4, lr=0.1 if self.is_image else 1e-4, momentum=0.9)
+        elif self.algorithm == "dgc":
+            from hipress_b200.parallel.dgc import DGCDataParallel
+            self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4)
+        elif self.algorithm == "nccl":
+            from hipress_b200.parallel.baseline import NcclDataParallel
+            self.model = NcclDataParallel(net, lr=0.1, momentum=0.9)
+        else:
+            cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
+                                    threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=25.0)
+            self.model = CompressedDataParallel(net, cfg, lr=0.1, momentum=0.9, weight_decay=0.0, fused_sgd=True)
+
+    def step(self, batch):
+        torch = self.torch
+        if self.is_image:
+            x, y = batch
+            x = x.contiguous(memory_format=torch.channels_last)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = torch.nn.functional.cross_entropy(self.model(x), y)
+        else:
+            ids, labels = batch
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = self.model(ids, labels)
+        loss.backward()
+        self.model.step()
+        return loss
+
+    def launches(self):
+        return int(self.model.metrics().get("kernel_launches", 0))
+
+    def finish(self):
+        self.model.check()
+
+
+# ------------------------------------------------------------------------------------ reference
+class ReferenceTrainer:
+    """The unmodified reference extension (``hp_cuda`` built from its own sources into
+    ``baseline/_ref``) driven through its public API: per-tensor ``submit_task`` /
+    ``getResults`` polling with CPU staging buffers, composed with torch.distributed for the
+    transport the reference leaves to its caller.  Model and optimizer are stock
+    torchvision / torch.optim; nothing of this framework is on the path."""
+
+    def __init__(self, args, rank, world, local):
+        import torch
+        import torchvision
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        import hp_cuda  # the reference's module
+        self.hp = hp_cuda
+        self.torch = torch
+        self.rank, self.world = rank, world
+        self.dev = torch.device("cuda", local)
+        if args.model != "resnet50":
+            raise RuntimeError("reference arm is defined for the headline config (resnet50 + terngrad)")
+        torch.manual_seed(0)
+        self.net = torchvision.models.resnet50(num_classes=1000).to(self.dev).to(memory_format=torch.channels_last)
+        self.net.train()
+        self.opt = torch.optim.SGD(self.net.parameters(), lr=0.1, momentum=0.9)
+        assert hp_cuda.init("terngrad", {"enable_random": 1.0, "bitwidth": 2.0}, local, rank, world)
+        self.params = [(n, p) for n, p in self.net.named_parameters()]
+        self.B, self.C, self.G = {}, {}, {}
+        for n, p in self.params:
+            size = 10 + (p.numel() + 3) // 4
+            self.B[n] = torch.zeros(size, dtype=torch.uint8, device=self.dev)
+            self.C[n] = torch.zeros(size, dtype=torch.uint8).pin_memory()
+            if world > 1:
+                self.G[n] = [torch.zeros(size, dtype=torch.uint8, device=self.dev) for _ in range(world)]
+        self.peerB = {n: [torch.zeros_like(self.B[n]) for _ in range(world)] for n, _ in self.params} if world > 1 else {}
+        self.peerC = {n: [torch.zeros_like(self.C[n]).pin_memory() for _ in range(world)] for n, _ in self.params} if world > 1 else {}
+
+    @staticmethod
+    def _flat(grad):
+        # the reference requires contiguous tensors; a channels-last gradient is contiguous
+        # in NHWC order, which the codec does not care about
+        g = grad if grad.is_contiguous() else grad.permute(0, 2, 3, 1)
+        assert g.is_contiguous()
+        return g
+
+    def _wait(self, task_id, names):
+        pending = set(names)
+        deadline = time.monotonic() + 120
+        while pending:
+            for k in self.hp.getResults(task_id):
+                pending.discard(k)
+            if time.monotonic() > deadline:
+                raise TimeoutError("reference tasks did not finish")
+
+    def step(self, batch):
+        torch = self.torch
+        import torch.distributed as dist
+        x, y = batch
+        x = x.contiguous(memory_format=torch.channels_last)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = torch.nn.functional.cross_entropy(self.net(x), y)
+        self.opt.zero_grad(set_to_none=False)
+        loss.backward()
+        torch.cuda.current_stream().synchronize()  # the reference does not order its streams after ours
+        names = [n for n, _ in self.params]
+        for n, p in self.params:
+            self.hp.submit_task(n, self._flat(p.grad), self.B[n], self.C[n], 0, 10)
+        self._wait(10, names)
+        if self.world == 1:
+            for n, p in self.params:
+                self.hp.submit_task(n, self._flat(p.grad), self.B[n], self.C[n], 0, 20)
+            self._wait(20, names)
+        else:
+            # transport (absent from the reference): all-gather every payload
+            for n, _ in self.params:
+                dist.all_gather(self.G[n], self.C[n].to(self.dev, non_blocking=True))
+            for n, _ in self.params:
+                for r in range(self.world):
+                    self.peerC[n][r].copy_(self.G[n][r], non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            for r in range(self.world):
+                for n, p in self.params:
+                    # is_root doubles as "accumulate": overwrite with rank 0's payload, add the rest
+                    self.hp.submit_task(n, self._flat(p.grad), self.peerB[n][r], self.peerC[n][r], 0 if r == 0 else 1, 20)
+                self._wait(20, names)
+            for _, p in self.params:
+                p.grad.div_(self.world)
+        self.opt.step()
+        return loss
+
+    def launches(self):
+        return None
+
+    def finish(self):
+        self.hp.end()
+
+
+def reference_unavailable_reason():
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not any(f.startswith("hp_cuda") and f.endswith(".so") for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else [])):
+        return "baseline/_ref has no built hp_cuda extension (install the reference first, see DESIGN.md)"
+    return None
+
+
+# ------------------------------------------------------------------------------------ main
+def run(args):
+    import torch
+    rank, world, local = setup_dist(args)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+    batch = args.batch or MODEL_BATCH[args.model]
+    dev = torch.device("cuda", local)
+    trainer = (OurTrainer if args.impl == "ours" else ReferenceTrainer)(args, rank, world, local)
+    from hipress_b200.utils import ClockSampler
+    from hipress_b200.utils.timing import max_over_ranks
+    pinned = make_batches(args.model, batch, rank)
+    resident = [tuple(t.to(dev) for t in b) for b in pinned.batches]
+
+    # ---- warm-up (untimed)
+    for i in range(max(args.warmup, 3)):
+        trainer.step(resident[i % len(resident)])
+    barrier()
+
+    # ---- device-timed region: exactly K steps, inputs resident (per-step working set >> L2)
+    launches0 = trainer.launches()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        start.record()
+        for i in range(args.steps):
+            trainer.step(resident[i % len(resident)])
+        stop.record()
+        barrier()
+    ms = max_over_ranks(start.elapsed_time(stop), dev)
+    launches1 = trainer.launches()
+    clock_summary = clocks.summary()
+
+    # ---- end-to-end region: H2D of each step's batch from pinned memory + loss read back
+    barrier()
+    t0 = time.perf_counter()
+    last = 0.0
+    for i in range(args.steps):
+        b = pinned.next(dev)
+        last = float(trainer.step(b).item())
+    barrier()
+    e2e_s = max_over_ranks(time.perf_counter() - t0, dev)
+    trainer.finish()
+
+    global_batch = batch * world
+    value = global_batch * args.steps / (ms / 1e3)
+    e2e_value = global_batch * args.steps / e2e_s
+    unit = "samples/s"
+    alg = getattr(trainer, "algorithm", "terngrad")
+    out = {
+        "metric": "train samples/sec (ResNet-50 data-parallel, TernGrad 2-bit compressed gradient sync)"
+        if args.model == "resnet50" else f"train samples/sec ({args.model}, {alg})",
+        "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms / args.steps, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": args.impl,
+        "config": {"model": args.model, "global_batch": global_batch, "per_gpu_batch": batch,
+                   "seq_len": 128 if args.model == "bert_large" else None,
+                   "parallelism": f"dp{world}", "algorithm": alg, "bucket_mb": 25,
+                   "optimizer": "sgd momentum 0.9 lr 0.1" if args.model != "bert_large" else "see model wrapper",
+                   "cache": "inputs+activations per step exceed the 126 MB L2; 4 distinct batches rotate"},
+        "clocks": {"sm_mhz": clock_summary["sm_mhz"], "sm_max_mhz": clock_summary["sm_max_mhz"],
+                   "reasons": clock_summary["reasons"]},
+        "e2e": {"value": round(e2e_value, 2), "unit": unit, "h2d_bytes_per_step": pinned.bytes_per_batch,
+                "d2h_bytes_per_step": 4, "last_loss": last},
+        "gpu_launches": (launches1 - launches0) if launches0 is not None else None,
+    }
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        os.environ["HIPRESS_SKIP_NATIVE"] = "1"  # only the pure-Python data/clock helpers are shared
+        why = reference_unavailable_reason()
+        if why:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+            return 0
+    run(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -65,6 +65,10 @@ runtime::EngineConfig config_from(const py::dict& d) {
   c.average = get("average", 1);
   c.flag_timeout_ns = uint64_t(get("flag_timeout_s", 20.0) * 1e9);
   c.num_workers = get("num_workers", 1);
+  c.defer_recv = get("defer_recv", 0);
+  c.momentum_correction = get("momentum_correction", 0);
+  c.dgc_momentum = get("dgc_momentum", 0.9f);
+  c.dgc_clip = get("dgc_clip", 0.0f);
   return c;
 }
 
@@ -143,6 +147,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gram_schmidt", &ops::gram_schmidt, py::arg("P"), py::arg("eps") = 1e-8);
   m.def("psgd_expand_feedback", &ops::psgd_expand_feedback, py::arg("P"), py::arg("Q"), py::arg("M"),
         py::arg("grad_out"), py::arg("post_scale") = 1.0);
+  m.def("psgd_owner_gather", &ops::psgd_owner_gather, py::arg("owners"), py::arg("out"),
+        py::arg("scale") = 1.0);
+  m.def("psgd_expand_sgd", &ops::psgd_expand_sgd, py::arg("P"), py::arg("Q"), py::arg("M"),
+        py::arg("param"), py::arg("momentum"), py::arg("post_scale"), py::arg("lr"), py::arg("mu"),
+        py::arg("weight_decay"), py::arg("first_step"));
   m.def("read_status", &ops::read_status, py::arg("like"), py::arg("reset") = true);
 
   // fused SGD-momentum over flat fp32 buffers
@@ -248,14 +257,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("payload_capacity", &runtime::DdpEngine::payload_capacity)
       .def("set_buffers",
            [](runtime::DdpEngine& e, torch::Tensor grad, c10::optional<torch::Tensor> residual,
-              c10::optional<torch::Tensor> param, c10::optional<torch::Tensor> momentum) {
+              c10::optional<torch::Tensor> param, c10::optional<torch::Tensor> momentum,
+              c10::optional<torch::Tensor> aux, c10::optional<torch::Tensor> second) {
              auto ptr = [](c10::optional<torch::Tensor>& t) -> float* {
                return (t.has_value() && t->defined()) ? t->data_ptr<float>() : nullptr;
              };
-             e.set_buffers(grad.data_ptr<float>(), ptr(residual), ptr(param), ptr(momentum));
+             e.set_buffers(grad.data_ptr<float>(), ptr(residual), ptr(param), ptr(momentum), ptr(aux),
+                           ptr(second));
            },
            py::arg("grad"), py::arg("residual") = py::none(), py::arg("param") = py::none(),
-           py::arg("momentum") = py::none())
+           py::arg("momentum") = py::none(), py::arg("aux") = py::none(), py::arg("second") = py::none())
       .def("set_symmetric",
            [](runtime::DdpEngine& e, comm::SymmetricBuffer& buf) {
              std::vector<uint8_t*> bases;
@@ -264,6 +275,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            })
       .def("set_sgd", &runtime::DdpEngine::set_sgd, py::arg("lr"), py::arg("momentum"),
            py::arg("weight_decay"), py::arg("fused"))
+      .def("set_adamw", &runtime::DdpEngine::set_adamw, py::arg("lr"), py::arg("beta1") = 0.9f,
+           py::arg("beta2") = 0.999f, py::arg("eps") = 1e-8f, py::arg("weight_decay") = 0.0f)
       .def("set_keep_fraction", &runtime::DdpEngine::set_keep_fraction)
       .def("begin_step", &runtime::DdpEngine::begin_step)
       .def("grad_ready",
@@ -278,6 +291,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              py::gil_scoped_release nogil;
              e.finish_step(s);
            })
+      .def("drain", [](runtime::DdpEngine& e) { py::gil_scoped_release nogil; e.drain(); })
       .def("check_status", &runtime::DdpEngine::check_status)
       .def_property_readonly("epoch", &runtime::DdpEngine::epoch)
       .def_property_readonly("steps", &runtime::DdpEngine::steps)

@@ -1,0 +1,127 @@
+// Deep-gradient-compression pre/post-processing and the fused AdamW update.
+//
+// DGC (Lin et al.) wraps a top-k sparsifier with three things the reference
+// does not contain (its dgc_body.h is only the selector):
+//   * momentum correction   u = m*u + g ;  v = v + u ;  send sparse(v)
+//   * momentum factor masking: u and v are cleared at the sent positions
+//   * local gradient clipping: g is scaled by min(1, clip / |g|) per bucket
+//     before it enters u (clip already divided by sqrt(world) by the caller)
+// The selector itself is sparse_compress (sparse.cu) run on v.
+#include "kernels.h"
+#include "p2p.cuh"
+
+namespace hipress {
+namespace cuda {
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(int64_t items, int max_blocks) {
+  int64_t blocks = (items + kThreads - 1) / kThreads;
+  if (blocks < 1) blocks = 1;
+  if (blocks > max_blocks) blocks = max_blocks;
+  return int(blocks);
+}
+
+__global__ void __launch_bounds__(kThreads)
+sumsq_kernel(const float* __restrict__ g, int64_t n, float* __restrict__ out) {
+  __shared__ float sh[kThreads / 32];
+  float acc = 0.f;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) acc += g[i] * g[i];
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    acc = threadIdx.x < kThreads / 32 ? sh[threadIdx.x] : 0.f;
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (threadIdx.x == 0) atomicAdd(out, acc);
+  }
+}
+
+// u = m*u + s*g ; v += u, with s = min(1, clip/|g|) when clip > 0.
+__global__ void __launch_bounds__(kThreads)
+dgc_accumulate_kernel(const float* __restrict__ g, float* __restrict__ u, float* __restrict__ v,
+                      int64_t n, float momentum, float clip, const float* __restrict__ sumsq) {
+  float s = 1.0f;
+  if (clip > 0.f) {
+    const float norm = sqrtf(*sumsq);
+    s = fminf(1.0f, clip / (norm + 1e-6f));
+  }
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float uu = momentum * u[i] + s * g[i];
+    u[i] = uu;
+    v[i] += uu;
+  }
+}
+
+// u[idx] = 0 for every index of a sparse payload; also clears the clip scratch.
+__global__ void __launch_bounds__(kThreads)
+dgc_mask_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restrict__ u, int64_t n,
+                float* __restrict__ sumsq) {
+  uint32_t total = 0;
+  for (int k = 0; k < 4; ++k) total |= uint32_t(payload[k]) << (8 * k);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && sumsq != nullptr) *sumsq = 0.f;
+  if (total < 4 || int64_t(total) > cap) return;
+  const int64_t k = (int64_t(total) - 4) / 8;
+  const uint32_t* idx = reinterpret_cast<const uint32_t*>(payload + 4);
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < k; x += stride) {
+    const uint32_t i = idx[x];
+    if (int64_t(i) < n) u[i] = 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+adamw_kernel(const float* __restrict__ grad, float scale, AdamWApply a, int64_t n) {
+  const float bc1 = 1.0f - powf(a.beta1, float(a.step));
+  const float bc2 = 1.0f - powf(a.beta2, float(a.step));
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float g = grad[i] * scale;
+    float p = a.param[i];
+    p -= a.lr * a.weight_decay * p;  // decoupled weight decay
+    const float m = a.beta1 * a.exp_avg[i] + (1.0f - a.beta1) * g;
+    const float v = a.beta2 * a.exp_avg_sq[i] + (1.0f - a.beta2) * g * g;
+    a.exp_avg[i] = m;
+    a.exp_avg_sq[i] = v;
+    const float denom = sqrtf(v) / sqrtf(bc2) + a.eps;
+    a.param[i] = p - (a.lr / bc1) * (m / denom);
+  }
+}
+
+}  // namespace
+
+cudaError_t dgc_accumulate(const float* grad, float* u, float* v, int64_t n, float momentum,
+                           float clip, float* sumsq_scratch, cudaStream_t stream) {
+  if (n <= 0) return cudaErrorInvalidValue;
+  if (clip > 0.f) {
+    if (sumsq_scratch == nullptr) return cudaErrorInvalidValue;
+    sumsq_kernel<<<grid_for(n, 148 * 4), kThreads, 0, stream>>>(grad, n, sumsq_scratch);
+  }
+  dgc_accumulate_kernel<<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(grad, u, v, n, momentum, clip,
+                                                                       sumsq_scratch);
+  return cudaGetLastError();
+}
+
+cudaError_t dgc_mask(const uint8_t* payload, int64_t payload_capacity, float* u, int64_t n,
+                     float* sumsq_scratch, cudaStream_t stream) {
+  if (n <= 0 || (reinterpret_cast<uintptr_t>(payload) & 3)) return cudaErrorInvalidValue;
+  const int64_t kmax = (payload_capacity - 4) / 8;
+  dgc_mask_kernel<<<grid_for(kmax, 148 * 4), kThreads, 0, stream>>>(payload, payload_capacity, u, n,
+                                                                    sumsq_scratch);
+  return cudaGetLastError();
+}
+
+cudaError_t adamw_apply_dense(const float* grad, float scale, const AdamWApply& apply, int64_t n,
+                              cudaStream_t stream) {
+  if (n <= 0 || !apply.param || !apply.exp_avg || !apply.exp_avg_sq || apply.step < 1)
+    return cudaErrorInvalidValue;
+  adamw_kernel<<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(grad, scale, apply, n);
+  return cudaGetLastError();
+}
+
+}  // namespace cuda
+}  // namespace hipress

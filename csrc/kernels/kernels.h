@@ -118,6 +118,26 @@ cudaError_t add_into(const float* a, const float* b, float* out, int64_t n, cuda
 cudaError_t dense_gather_sum(const float* const* srcs, int world, float* out, int64_t n,
                              float post_scale, cudaStream_t stream);
 
+// ---------------------------------------------------------------- DGC / AdamW
+// Momentum correction: u = momentum*u + s*grad; v += u, where s clips the
+// bucket's gradient to norm `clip` (no clipping when clip <= 0).
+// sumsq_scratch: one float, zero on entry when clip > 0; cleared by dgc_mask.
+cudaError_t dgc_accumulate(const float* grad, float* u, float* v, int64_t n, float momentum,
+                           float clip, float* sumsq_scratch, cudaStream_t stream);
+// Momentum factor masking: u[idx] = 0 for every index in the sparse payload.
+cudaError_t dgc_mask(const uint8_t* payload, int64_t payload_capacity, float* u, int64_t n,
+                     float* sumsq_scratch, cudaStream_t stream);
+struct AdamWApply {
+  float* param = nullptr;
+  float* exp_avg = nullptr;
+  float* exp_avg_sq = nullptr;
+  float lr = 0.f, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0.f;
+  int step = 1;  // 1-based
+};
+// Fused AdamW (decoupled weight decay, bias correction) on g = scale*grad.
+cudaError_t adamw_apply_dense(const float* grad, float scale, const AdamWApply& apply, int64_t n,
+                              cudaStream_t stream);
+
 // ---------------------------------------------------------------- PowerSGD
 // All matrices row-major fp32.  Mat is n x m, P is n x r, Q is m x r, r <= 16.
 // Output rows are split evenly over `world` owners; each row of the product is
@@ -149,6 +169,15 @@ cudaError_t gram_schmidt(float* P, int64_t n, int r, float eps, cudaStream_t str
 cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int64_t m, int r,
                                  float* Mat, float* residual, float* grad, int64_t N, int mode,
                                  float post_scale, cudaStream_t stream);
+
+// Same expansion with the optimizer fused: Mat -= approx and the parameters take
+// an SGD-momentum step with g = post_scale * approx (no dense gradient is written).
+cudaError_t psgd_expand_sgd(const float* P, const float* Q, int64_t n, int64_t m, int r, float* Mat,
+                            int64_t N, float post_scale, const SgdApply& apply, cudaStream_t stream);
+// out[rows x r] = scale * (accumulator of each row's owner); owners[p] has the
+// full output shape and may be peer memory.  Row ownership as in psgd_gemm.
+cudaError_t psgd_owner_gather(const ReduceTargets& owners, int64_t rows, int r, float* out,
+                              float scale, cudaStream_t stream);
 
 }  // namespace cuda
 }  // namespace hipress

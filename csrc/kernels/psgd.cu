@@ -95,14 +95,17 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar))
       : "memory");
 }
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1.
-__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+// Shared-memory matrix descriptor, version 1.  layout: 2 = 128-byte swizzle of
+// 16-byte units (K-major operands), 1 = 128-byte swizzle of 32-byte units, the
+// only layout MN-major 32-bit (tf32) operands may use.
+__device__ __forceinline__ uint64_t make_desc(uint32_t addr, uint32_t lbo, uint32_t sbo,
+                                              uint32_t layout) {
   uint64_t d = 0;
   d |= uint64_t((addr >> 4) & 0x3fffu);
   d |= uint64_t((lbo >> 4) & 0x3fffu) << 16;
   d |= uint64_t((sbo >> 4) & 0x3fffu) << 32;
   d |= uint64_t(1) << 46;
-  d |= uint64_t(2) << 61;
+  d |= uint64_t(layout & 7u) << 61;
   return d;
 }
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
@@ -198,11 +201,14 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t b0 = smem_u32(s.b[st]);
 #pragma unroll
         for (int k = 0; k < kBK / 8; ++k) {
-          // K-major: 8 tf32 = 32 bytes further along the swizzled row.
-          // MN-major: next group of 8 K-rows = 1024 bytes further.
-          const uint64_t da = MODE == 0 ? make_desc(a0 + k * 32, 16, 1024)
-                                        : make_desc(a0 + k * 1024, kBK * 128, 1024);
-          const uint64_t db = make_desc(b0 + k * 32, 16, 1024);
+          // K-major: 8 tf32 = 32 bytes further along the swizzled row; 8-row
+          // groups are 1024 bytes apart.
+          // MN-major: swizzle atoms are 4 K-rows x 128 bytes (512 bytes apart,
+          // SBO); the four 32-column groups of the tile are one TMA box apart
+          // (LBO); one MMA consumes 8 K-rows = 1024 bytes.
+          const uint64_t da = MODE == 0 ? make_desc(a0 + k * 32, 16, 1024, 2)
+                                        : make_desc(a0 + k * 1024, kBK * 128, 512, 1);
+          const uint64_t db = make_desc(b0 + k * 32, 16, 1024, 2);
           umma_tf32(tmem, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&s.empty[st]);  // frees the stage once the MMAs have read it
@@ -359,11 +365,13 @@ gram_schmidt_kernel(float* __restrict__ P, int64_t n, int r, float eps) {
 // approx[i,k] = sum_c P[i,c] Q[k,c].
 //   mode 0: Mat = approx; residual[:N] = grad - Mat[:N]; grad[:N] = Mat[:N]
 //   mode 1: grad[:N] = scale * approx; Mat -= approx      (error feedback kept in Mat)
+//   mode 2: Mat -= approx, and the parameters take a fused SGD-momentum step with
+//           g = scale * approx (residual/grad unused)
 template <int MODE>
 __global__ void __launch_bounds__(256)
 expand_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t n, int64_t m, int r,
               float* __restrict__ Mat, float* __restrict__ residual, float* __restrict__ grad,
-              int64_t N, float scale) {
+              int64_t N, float scale, SgdApply apply) {
   const int64_t total = n * m;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
@@ -376,9 +384,12 @@ expand_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t 
         residual[e] = grad[e] - acc;
         grad[e] = acc;
       }
-    } else {
+    } else if (MODE == 1) {
       Mat[e] -= acc;
       if (e < N) grad[e] = acc * scale;
+    } else {
+      Mat[e] -= acc;
+      if (e < N) sgd_update(apply, e, acc * scale);
     }
   }
 }
@@ -401,7 +412,7 @@ EncodeTiledFn encode_fn() {
 
 // 2-D fp32 tensor map: `inner` contiguous elements per row, `outer` rows.
 bool make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer, int box_inner,
-              int box_outer) {
+              int box_outer, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {cuuint64_t(inner), cuuint64_t(outer)};
@@ -409,7 +420,7 @@ bool make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer,
   cuuint32_t box[2] = {cuuint32_t(box_inner), cuuint32_t(box_outer)};
   cuuint32_t estr[2] = {1, 1};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -464,8 +475,10 @@ cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const fl
   }
   const int64_t k_pad = psgd_kpad(K);
   CUtensorMap map_a, map_b;
-  const bool ok_a = mode == 0 ? make_map(&map_a, Mat, m, n, kBK, kBM) : make_map(&map_a, Mat, m, n, 32, kBK);
-  const bool ok_b = make_map(&map_b, Xt, k_pad, kBN, kBK, kBN);
+  const bool ok_a = mode == 0
+                        ? make_map(&map_a, Mat, m, n, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)
+                        : make_map(&map_a, Mat, m, n, 32, kBK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  const bool ok_b = make_map(&map_b, Xt, k_pad, kBN, kBK, kBN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok_a || !ok_b) return cudaErrorInvalidValue;
   const int tiles = int((out_rows + kBM - 1) / kBM);
   const int total_kb = int(k_pad / kBK);
@@ -504,9 +517,52 @@ cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int6
   int64_t blocks = (n * m + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (mode == 0)
-    expand_kernel<0><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, residual, grad, N, post_scale);
+    expand_kernel<0><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, residual, grad, N, post_scale, SgdApply{});
   else
-    expand_kernel<1><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, residual, grad, N, post_scale);
+    expand_kernel<1><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, residual, grad, N, post_scale, SgdApply{});
+  return cudaGetLastError();
+}
+
+cudaError_t psgd_expand_sgd(const float* P, const float* Q, int64_t n, int64_t m, int r, float* Mat,
+                            int64_t N, float post_scale, const SgdApply& apply, cudaStream_t stream) {
+  if (n < 1 || m < 1 || r < 1 || r > kBN || N > n * m || apply.param == nullptr ||
+      apply.momentum == nullptr)
+    return cudaErrorInvalidValue;
+  int64_t blocks = (n * m + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  expand_kernel<2><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, nullptr, nullptr, N, post_scale, apply);
+  return cudaGetLastError();
+}
+
+namespace {
+struct GatherSrc {
+  const float* p[kMaxWorld];
+};
+// out[row] = scale * (owner of row)'s accumulator[row]: the all-gather half of
+// the factor all-reduce; owners may be peer GPUs (plain peer loads).
+__global__ void __launch_bounds__(256)
+owner_gather_kernel(GatherSrc src, int world, int64_t rows, int r, int64_t rows_per_owner,
+                    float* __restrict__ out, float scale) {
+  const int64_t total = rows * r;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    int owner = int((e / r) / rows_per_owner);
+    if (owner >= world) owner = world - 1;
+    out[e] = src.p[owner][e] * scale;
+  }
+}
+}  // namespace
+
+cudaError_t psgd_owner_gather(const ReduceTargets& owners, int64_t rows, int r, float* out,
+                              float scale, cudaStream_t stream) {
+  if (owners.world < 1 || owners.world > kMaxWorld || rows < 1 || r < 1) return cudaErrorInvalidValue;
+  GatherSrc src{};
+  for (int p = 0; p < owners.world; ++p) src.p[p] = owners.dst[p];
+  int64_t rpo = (rows + owners.world - 1) / owners.world;
+  if (rpo < 1) rpo = 1;
+  int64_t blocks = (rows * r + 255) / 256;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  owner_gather_kernel<<<int(blocks), 256, 0, stream>>>(src, owners.world, rows, r, rpo, out, scale);
   return cudaGetLastError();
 }
 

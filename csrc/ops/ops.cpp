@@ -249,7 +249,8 @@ void sparse_compress(const c10::optional<torch::Tensor>& grad, torch::Tensor R, 
   }
   if (R.is_cuda()) {
     c10::cuda::CUDAGuard guard(R.device());
-    void* scratch = scratch_for(R, cuda::sparse_scratch_bytes(n) + cuda::minmax_scratch_bytes());
+    // the sparse state lives behind the min/max state other codecs keep in the same scratch
+    void* scratch = static_cast<uint8_t*>(scratch_for(R, 16384 + cuda::sparse_scratch_bytes(n))) + 16384;
     HP_CHECK_CUDA(cuda::sparse_compress(g, R.data_ptr<float>(), n, sample_rate, keep_fraction,
                                         uint64_t(seed), accumulate ? 1 : 0, local_target(out),
                                         scratch, at::cuda::getCurrentCUDAStream()));
@@ -435,6 +436,45 @@ void psgd_expand_feedback(const torch::Tensor& P, const torch::Tensor& Q, torch:
     M.sub_(approx);
     grad_out.view(-1).copy_(approx.view(-1).slice(0, 0, N) * post_scale);
   }
+}
+
+void psgd_owner_gather(const std::vector<torch::Tensor>& owners, torch::Tensor out, double scale) {
+  check_f32(out, "out");
+  TORCH_CHECK(out.dim() == 2, "out must be rows x r");
+  TORCH_CHECK(!owners.empty() && owners.size() <= size_t(cuda::kMaxWorld), "1..8 owner tensors expected");
+  TORCH_CHECK(out.is_cuda(), "CUDA tensors expected");
+  cuda::ReduceTargets red;
+  red.world = int(owners.size());
+  for (size_t p = 0; p < owners.size(); ++p) {
+    check_f32(owners[p], "owner");
+    TORCH_CHECK(owners[p].numel() == out.numel(), "owner tensors must have out's shape");
+    red.dst[p] = owners[p].data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  HP_CHECK_CUDA(cuda::psgd_owner_gather(red, out.size(0), int(out.size(1)), out.data_ptr<float>(),
+                                        float(scale), at::cuda::getCurrentCUDAStream()));
+}
+
+void psgd_expand_sgd(const torch::Tensor& P, const torch::Tensor& Q, torch::Tensor M,
+                     torch::Tensor param, torch::Tensor momentum, double post_scale, double lr,
+                     double mu, double weight_decay, bool first_step) {
+  const PsgdShape s = psgd_shape(M, P, Q);
+  TORCH_CHECK(M.is_cuda(), "CUDA tensors expected");
+  TORCH_CHECK(param.scalar_type() == torch::kFloat32 && momentum.scalar_type() == torch::kFloat32,
+              "param and momentum must be float32");
+  const int64_t N = param.numel();
+  TORCH_CHECK(momentum.numel() == N && N <= s.n * s.m, "param/momentum must fit in M");
+  cuda::SgdApply a;
+  a.param = param.data_ptr<float>();
+  a.momentum = momentum.data_ptr<float>();
+  a.lr = float(lr);
+  a.mu = float(mu);
+  a.weight_decay = float(weight_decay);
+  a.first_step = first_step ? 1 : 0;
+  c10::cuda::CUDAGuard guard(M.device());
+  HP_CHECK_CUDA(cuda::psgd_expand_sgd(P.data_ptr<float>(), Q.data_ptr<float>(), s.n, s.m, int(s.r),
+                                      M.data_ptr<float>(), N, float(post_scale), a,
+                                      at::cuda::getCurrentCUDAStream()));
 }
 
 void powersgd_encode1(const torch::Tensor& grad, const torch::Tensor& residual,

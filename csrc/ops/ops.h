@@ -66,6 +66,13 @@ void gram_schmidt(torch::Tensor P, double eps);
 void psgd_expand_feedback(const torch::Tensor& P, const torch::Tensor& Q, torch::Tensor M,
                           torch::Tensor grad_out, double post_scale);
 
+// out = scale * (each row taken from its owner's accumulator); owners as in psgd_project.
+void psgd_owner_gather(const std::vector<torch::Tensor>& owners, torch::Tensor out, double scale);
+// M -= P Q^T and a fused SGD-momentum step of `param` with g = post_scale * P Q^T.
+void psgd_expand_sgd(const torch::Tensor& P, const torch::Tensor& Q, torch::Tensor M,
+                     torch::Tensor param, torch::Tensor momentum, double post_scale, double lr,
+                     double mu, double weight_decay, bool first_step);
+
 // Device status word of the last bounds / header failure seen by kernels
 // launched through these ops on the tensor's device (0 = none); reading it
 // synchronises the current stream.

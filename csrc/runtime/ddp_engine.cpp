@@ -112,11 +112,24 @@ DdpEngine::~DdpEngine() {
   if (status_) cudaFree(status_);
 }
 
-void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* momentum) {
+void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* momentum, float* aux,
+                            float* second) {
   grad_ = grad;
   residual_ = residual;
   param_ = param;
   momentum_ = momentum;
+  aux_ = aux;
+  second_ = second;
+}
+
+void DdpEngine::set_adamw(float lr, float beta1, float beta2, float eps, float weight_decay) {
+  lr_ = lr;
+  beta1_ = beta1;
+  beta2_ = beta2;
+  eps_ = eps;
+  wd_ = weight_decay;
+  adamw_ = true;
+  fused_sgd_ = false;
 }
 
 void DdpEngine::set_symmetric(const std::vector<uint8_t*>& bases) {
@@ -206,6 +219,11 @@ cuda::UnpackSources DdpEngine::sources_for(int b) const {
 }
 
 void DdpEngine::issue_bucket(int b, int worker) {
+  issue_push(b, worker);
+  if (!cfg_.defer_recv) issue_recv(b, worker);
+}
+
+void DdpEngine::issue_push(int b, int worker) {
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
@@ -213,18 +231,6 @@ void DdpEngine::issue_bucket(int b, int worker) {
   float* g = grad_ + B.offset;
   float* res = residual_ ? residual_ + B.offset : nullptr;
   const uint64_t seed = cfg_.seed + uint64_t(epoch_) * 0x9E3779B97F4A7C15ull + uint64_t(b) * 0x632BE59BD9B4E019ull;
-  const float post = cfg_.average ? 1.0f / float(cfg_.world) : 1.0f;
-  cuda::SgdApply apply;
-  if (fused_sgd_) {
-    apply.param = param_ + B.offset;
-    apply.momentum = momentum_ + B.offset;
-    apply.lr = lr_;
-    apply.mu = sgd_mu_;
-    apply.weight_decay = wd_;
-    apply.first_step = steps_ == 0 ? 1 : 0;
-  }
-  cuda::SgdApply none;
-
   // ---- push stream: compress and deliver
   check(cudaStreamWaitEvent(w.push, ready_events_[static_cast<size_t>(b)], 0), "wait ready");
   cuda::PushTargets dst = targets_for(b, w);
@@ -241,14 +247,31 @@ void DdpEngine::issue_bucket(int b, int worker) {
             "terngrad_compress");
       launched += 2;
       break;
-    case Codec::kSparse:
+    case Codec::kSparse: {
       if (!res) throw std::runtime_error("sparse codecs need a residual buffer");
-      check(cuda::sparse_compress(cfg_.sparse_accumulate ? g : nullptr, res, n, cfg_.sample_rate,
-                                  keep_fraction_, seed, cfg_.sparse_accumulate, dst,
-                                  static_cast<uint8_t*>(w.scratch) + 16384, w.push),
+      int accumulate = cfg_.sparse_accumulate;
+      float* sumsq = reinterpret_cast<float*>(static_cast<uint8_t*>(w.scratch) + 12288);
+      if (cfg_.momentum_correction) {
+        if (!aux_) throw std::runtime_error("momentum correction needs the velocity buffer");
+        check(cuda::dgc_accumulate(g, aux_ + B.offset, res, n, cfg_.dgc_momentum, cfg_.dgc_clip, sumsq,
+                                   w.push),
+              "dgc_accumulate");
+        launched += cfg_.dgc_clip > 0.f ? 2 : 1;
+        accumulate = 0;  // v already holds the accumulated velocity
+      }
+      check(cuda::sparse_compress(accumulate ? g : nullptr, res, n, cfg_.sample_rate, keep_fraction_,
+                                  seed, accumulate, dst, static_cast<uint8_t*>(w.scratch) + 16384,
+                                  w.push),
             "sparse_compress");
       launched += 9;
+      if (cfg_.momentum_correction) {
+        check(cuda::dgc_mask(dst.payload[cfg_.rank], L.slot_bytes - L.shift, aux_ + B.offset, n, sumsq,
+                             w.push),
+              "dgc_mask");
+        launched += 1;
+      }
       break;
+    }
     case Codec::kEcq:
       if (!res) throw std::runtime_error("ecq needs a history buffer");
       check(cuda::ecq_compress(g, res, n, cfg_.alpha, cfg_.beta, cfg_.bitwidth, seed, dst,
@@ -267,6 +290,26 @@ void DdpEngine::issue_bucket(int b, int worker) {
     }
   }
 
+  launches_ += launched;
+}
+
+void DdpEngine::issue_recv(int b, int worker) {
+  WorkerCtx& w = workers_[static_cast<size_t>(worker)];
+  const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int64_t n = B.numel;
+  float* g = grad_ + B.offset;
+  const float post = cfg_.average ? 1.0f / float(cfg_.world) : 1.0f;
+  cuda::SgdApply apply;
+  if (fused_sgd_) {
+    apply.param = param_ + B.offset;
+    apply.momentum = momentum_ + B.offset;
+    apply.lr = lr_;
+    apply.mu = sgd_mu_;
+    apply.weight_decay = wd_;
+    apply.first_step = steps_ == 0 ? 1 : 0;
+  }
+  int launched = 0;
   // ---- recv stream: wait for all ranks, decode everything in one pass
   const uint32_t* flags = reinterpret_cast<const uint32_t*>(bases_[static_cast<size_t>(cfg_.rank)] + L.flags);
   check(cuda::wait_flags(flags, cfg_.world, epoch_, cfg_.flag_timeout_ns, status_, w.recv), "wait_flags");
@@ -306,6 +349,21 @@ void DdpEngine::issue_bucket(int b, int worker) {
     check(cuda::sgd_apply_dense(g, 1.0f, apply, n, w.recv), "sgd_apply_dense");
     launched += 1;
   }
+  if (adamw_) {
+    if (!param_ || !momentum_ || !second_) throw std::runtime_error("AdamW needs param and both moment buffers");
+    cuda::AdamWApply aw;
+    aw.param = param_ + B.offset;
+    aw.exp_avg = momentum_ + B.offset;
+    aw.exp_avg_sq = second_ + B.offset;
+    aw.lr = lr_;
+    aw.beta1 = beta1_;
+    aw.beta2 = beta2_;
+    aw.eps = eps_;
+    aw.weight_decay = wd_;
+    aw.step = int(steps_) + 1;
+    check(cuda::adamw_apply_dense(g, 1.0f, aw, n, w.recv), "adamw_apply_dense");
+    launched += 1;
+  }
   check(cudaEventRecord(w.tail, w.recv), "record tail");
   w.used = true;
   launches_ += launched;
@@ -318,6 +376,13 @@ void DdpEngine::finish_step(cudaStream_t consumer) {
   {
     std::unique_lock<std::mutex> lk(mu_);
     cv_.wait(lk, [&] { return issued_ >= static_cast<int>(buckets_.size()); });
+  }
+  if (cfg_.defer_recv) {
+    for (size_t b = 0; b < buckets_.size(); ++b) {
+      const int worker = int(b) % static_cast<int>(workers_.size());
+      pool_->submit_to(worker, [this, b](int w) { issue_recv(int(b), w); });
+    }
+    pool_->drain();
   }
   if (pool_->error_count() > 0) {
     const std::string err = pool_->last_error();

@@ -48,10 +48,19 @@ struct EngineConfig {
   double sample_rate = 0.01, keep_fraction = 0.001;  // sparse
   int sparse_accumulate = 1;             // 1: R += g inside the codec (GradDrop)
   float alpha = 1.f, beta = 1.f;         // ecq
+  // DGC: momentum correction with factor masking and per-bucket local clipping
+  int momentum_correction = 0;
+  float dgc_momentum = 0.9f;
+  float dgc_clip = 0.f;                  // <= 0: off; the caller divides by sqrt(world)
   uint64_t seed = 1;
   int average = 1;                       // divide the sum by world
   uint64_t flag_timeout_ns = 20ull * 1000 * 1000 * 1000;
   int num_workers = 1;
+  // Issue the receive half (flag wait + unpack) of every bucket only in
+  // finish_step().  Used when several ranks are emulated on one device: the
+  // caller lets all ranks push, synchronises, and only then finishes the steps,
+  // so that no kernel ever waits for a kernel that has not been launched yet.
+  int defer_recv = 0;
 };
 
 struct BucketDesc {
@@ -79,12 +88,16 @@ class DdpEngine {
   const BucketLayout& layout(int b) const { return layouts_.at(static_cast<size_t>(b)); }
   int64_t payload_capacity(int b) const;
 
-  // residual / param / momentum may be null when unused.
-  void set_buffers(float* grad, float* residual, float* param, float* momentum);
+  // residual / param / momentum / aux may be null when unused.  `momentum` is
+  // the SGD momentum buffer or AdamW's first moment; `aux` is DGC's velocity u;
+  // `second` is AdamW's second moment.
+  void set_buffers(float* grad, float* residual, float* param, float* momentum,
+                   float* aux = nullptr, float* second = nullptr);
   // bases[r]: rank r's symmetric buffer as mapped in this process.
   void set_symmetric(const std::vector<uint8_t*>& bases);
 
   void set_sgd(float lr, float momentum, float weight_decay, bool fused);
+  void set_adamw(float lr, float beta1, float beta2, float eps, float weight_decay);
   void set_keep_fraction(double keep_fraction);
 
   void begin_step();
@@ -96,6 +109,8 @@ class DdpEngine {
   // `consumer` wait for the device work.  Buckets whose hooks never fired
   // (unused parameters) are flushed here.
   void finish_step(cudaStream_t consumer);
+  // Blocks until every job handed to the workers so far has been issued to the device.
+  void drain() { pool_->drain(); }
 
   // Synchronises and returns the device status word (cuda::Status); resets it.
   int check_status();
@@ -117,6 +132,8 @@ class DdpEngine {
     bool used = false;
   };
   void issue_bucket(int b, int worker);
+  void issue_push(int b, int worker);
+  void issue_recv(int b, int worker);
   cuda::PushTargets targets_for(int b, WorkerCtx& w) const;
   cuda::UnpackSources sources_for(int b) const;
 
@@ -127,6 +144,9 @@ class DdpEngine {
   int64_t symmetric_bytes_ = 0;
 
   float *grad_ = nullptr, *residual_ = nullptr, *param_ = nullptr, *momentum_ = nullptr;
+  float *aux_ = nullptr, *second_ = nullptr;
+  bool adamw_ = false;
+  float beta1_ = 0.9f, beta2_ = 0.999f, eps_ = 1e-8f;
   std::vector<uint8_t*> bases_;
   float lr_ = 0.f, sgd_mu_ = 0.f, wd_ = 0.f;
   bool fused_sgd_ = false;

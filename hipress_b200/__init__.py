@@ -34,9 +34,13 @@ def _load_native():
 
 import torch  # noqa: E402  (must be imported before the extension: it links against libtorch)
 
-_C = _load_native()
-
-from . import ops  # noqa: E402
-from . import hp_cuda  # noqa: E402
+if os.environ.get("HIPRESS_SKIP_NATIVE"):
+    # only the pure-Python helpers (hipress_b200.utils) are wanted, e.g. by the benchmark's
+    # reference arm, which must not load this framework's kernels
+    _C = None
+else:
+    _C = _load_native()
+    from . import ops  # noqa: E402,F401
+    from . import hp_cuda  # noqa: E402,F401
 
 __all__ = ["_C", "ops", "hp_cuda", "__version__"]

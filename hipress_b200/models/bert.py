@@ -1,0 +1,77 @@
+"""BERT for masked-LM pre-training.  ``bert_large`` = 24 layers, hidden 1024, 16 heads,
+FFN 4096, vocabulary 30522 (~340 M parameters with tied output embedding)."""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class BertLayer(nn.Module):
+    def __init__(self, hidden: int, heads: int, ffn: int, dropout: float):
+        super().__init__()
+        self.heads = heads
+        self.qkv = nn.Linear(hidden, 3 * hidden)
+        self.out = nn.Linear(hidden, hidden)
+        self.ln1 = nn.LayerNorm(hidden, eps=1e-12)
+        self.fc1 = nn.Linear(hidden, ffn)
+        self.fc2 = nn.Linear(ffn, hidden)
+        self.ln2 = nn.LayerNorm(hidden, eps=1e-12)
+        self.drop = nn.Dropout(dropout)
+
+    def forward(self, x):
+        b, s, h = x.shape
+        q, k, v = self.qkv(x).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
+        a = F.scaled_dot_product_attention(q, k, v)
+        a = a.transpose(1, 2).reshape(b, s, h)
+        x = self.ln1(x + self.drop(self.out(a)))
+        return self.ln2(x + self.drop(self.fc2(F.gelu(self.fc1(x)))))
+
+
+class BertForMaskedLM(nn.Module):
+    def __init__(self, vocab: int = 30522, hidden: int = 1024, layers: int = 24, heads: int = 16,
+                 ffn: int = 4096, max_pos: int = 512, dropout: float = 0.1):
+        super().__init__()
+        self.tok = nn.Embedding(vocab, hidden)
+        self.pos = nn.Embedding(max_pos, hidden)
+        self.typ = nn.Embedding(2, hidden)
+        self.ln = nn.LayerNorm(hidden, eps=1e-12)
+        self.drop = nn.Dropout(dropout)
+        self.layers = nn.ModuleList(BertLayer(hidden, heads, ffn, dropout) for _ in range(layers))
+        self.head_dense = nn.Linear(hidden, hidden)
+        self.head_ln = nn.LayerNorm(hidden, eps=1e-12)
+        self.head_bias = nn.Parameter(torch.zeros(vocab))
+        self.apply(self._init)
+
+    @staticmethod
+    def _init(m):
+        if isinstance(m, (nn.Linear, nn.Embedding)):
+            nn.init.normal_(m.weight, 0.0, 0.02)
+        if isinstance(m, nn.Linear) and m.bias is not None:
+            nn.init.zeros_(m.bias)
+
+    def forward(self, ids: torch.Tensor, labels: torch.Tensor | None = None):
+        b, s = ids.shape
+        pos = torch.arange(s, device=ids.device)
+        x = self.drop(self.ln(self.tok(ids) + self.pos(pos)[None] + self.typ.weight[0]))
+        for layer in self.layers:
+            x = layer(x)
+        if labels is None:
+            h = self.head_ln(F.gelu(self.head_dense(x)))
+            return F.linear(h, self.tok.weight, self.head_bias)
+        # score only the masked positions (labels == -100 elsewhere)
+        sel = labels.view(-1) >= 0
+        h = x.view(b * s, -1)[sel]
+        h = self.head_ln(F.gelu(self.head_dense(h)))
+        logits = F.linear(h, self.tok.weight, self.head_bias)
+        return F.cross_entropy(logits.float(), labels.view(-1)[sel])
+
+
+def bert_large() -> BertForMaskedLM:
+    return BertForMaskedLM()
+
+
+def bert_tiny() -> BertForMaskedLM:
+    return BertForMaskedLM(vocab=1000, hidden=64, layers=2, heads=4, ffn=128, max_pos=64, dropout=0.0)

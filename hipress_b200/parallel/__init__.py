@@ -1,0 +1,5 @@
+"""Data parallelism: symmetric memory, bucket planning, the DDP wrapper, compressors."""
+from .ddp import BucketPlan, CompressedDataParallel, CompressionConfig, plan_buckets
+from .symmetric import SymmetricMemory
+
+__all__ = ["BucketPlan", "CompressedDataParallel", "CompressionConfig", "SymmetricMemory", "plan_buckets"]

@@ -1,0 +1,278 @@
+"""Data-parallel training with compressed gradient synchronisation.
+
+``CompressedDataParallel`` wraps a module the way ``DistributedDataParallel``
+does, but gradients are synchronised by this framework's engine: parameters and
+gradients are re-homed into flat fp32 buffers cut into buckets (25 MB by
+default), backward hooks tell the C++ engine which parameters are ready, and for
+every full bucket the engine launches, on its own streams and overlapped with
+the rest of backward,
+
+    compress -> packed bytes stored into every rank's receive slot over NVLink
+    -> bounded flag wait -> one-pass unpack + average of all ranks' payloads
+    (-> fused SGD-momentum update of the flat parameters).
+
+Nothing of this exists in the reference, whose caller has to submit per-tensor
+tasks, poll ``getResults`` and move CPU buffers itself (ref hp_cuda.cpp:904-1060).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import _C
+from .symmetric import SymmetricMemory
+
+ALIGN = 4  # elements; keeps every parameter view 16-byte aligned
+
+
+@dataclass
+class CompressionConfig:
+    """Which codec synchronises the gradients, and its parameters.
+
+    algorithm: ``terngrad`` | ``tbq`` | ``graddrop`` | ``dgc`` | ``ecq`` | ``dense``
+    (``dense`` is an uncompressed peer-to-peer all-reduce through the same engine).
+    """
+    algorithm: str = "terngrad"
+    bitwidth: int = 2
+    enable_random: bool = True
+    error_feedback: bool = True
+    threshold: float = 2e-3
+    sample_rate: float = 0.01
+    keep_fraction: float = 0.001
+    alpha: float = 1.0
+    beta: float = 1.0
+    seed: int = 1
+    bucket_mb: float = 25.0
+    average: bool = True
+    flag_timeout_s: float = 20.0
+    num_workers: int = 1
+    # DGC extras (algorithm "dgc"): momentum correction with factor masking, local clipping
+    momentum_correction: bool = False
+    dgc_momentum: float = 0.9
+    clip_norm: float = 0.0
+
+    def engine_dict(self, rank: int, world: int, device: int) -> Dict:
+        return dict(rank=rank, world=world, device=device, codec=self.algorithm, bitwidth=self.bitwidth,
+                    enable_random=int(self.enable_random), error_feedback=int(self.error_feedback),
+                    threshold=float(self.threshold), sample_rate=float(self.sample_rate),
+                    keep_fraction=float(self.keep_fraction), alpha=float(self.alpha), beta=float(self.beta),
+                    seed=int(self.seed), average=int(self.average), flag_timeout_s=float(self.flag_timeout_s),
+                    num_workers=int(self.num_workers), momentum_correction=int(self.momentum_correction),
+                    dgc_momentum=float(self.dgc_momentum),
+                    dgc_clip=float(self.clip_norm) / max(1.0, float(world)) ** 0.5)
+
+    @property
+    def needs_residual(self) -> bool:
+        return self.algorithm in ("tbq", "graddrop", "dgc", "ecq") or (
+            self.algorithm == "terngrad" and self.error_feedback)
+
+
+@dataclass
+class BucketPlan:
+    offsets: List[int] = field(default_factory=list)      # element offset of each parameter
+    buckets: List[tuple] = field(default_factory=list)    # (offset, numel, num_params)
+    param_bucket: List[int] = field(default_factory=list)
+    total: int = 0
+
+
+def plan_buckets(numels: Iterable[int], bucket_elems: int) -> BucketPlan:
+    """Lay parameters out in *reverse* order (the order backward produces gradients), each
+    aligned to 16 bytes, and cut the flat range into buckets of at most ``bucket_elems``."""
+    numels = list(numels)
+    plan = BucketPlan(offsets=[0] * len(numels), param_bucket=[0] * len(numels))
+    cursor, b_start, b_params = 0, 0, 0
+    for i in reversed(range(len(numels))):
+        size = (numels[i] + ALIGN - 1) // ALIGN * ALIGN
+        if b_params > 0 and cursor - b_start + size > bucket_elems:
+            plan.buckets.append((b_start, cursor - b_start, b_params))
+            b_start, b_params = cursor, 0
+        plan.offsets[i] = cursor
+        plan.param_bucket[i] = len(plan.buckets)
+        cursor += size
+        b_params += 1
+    if b_params > 0:
+        plan.buckets.append((b_start, cursor - b_start, b_params))
+    plan.total = cursor
+    return plan
+
+
+def _view_like(flat: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+    """A view of the 1-D slice ``flat`` with ``p``'s shape, keeping a channels-last parameter
+    channels-last (so convolutions do not re-layout their weights every step)."""
+    if p.dim() == 4 and not p.is_contiguous() and p.is_contiguous(memory_format=torch.channels_last):
+        n, c, h, w = p.shape
+        return flat.view(n, h, w, c).permute(0, 3, 1, 2)
+    return flat.view(p.shape)
+
+
+class CompressedDataParallel(nn.Module):
+    """Wrap ``module`` for data-parallel training with compressed gradient exchange.
+
+    Typical step::
+
+        model = CompressedDataParallel(net, CompressionConfig("terngrad"), lr=0.1, momentum=0.9)
+        loss = criterion(model(x), y)
+        loss.backward()          # buckets are compressed and exchanged while backward runs
+        model.step()             # waits for the exchange; parameters are already updated (fused SGD)
+
+    With ``fused_sgd=False`` the averaged gradients are left in ``p.grad`` for any optimizer.
+    """
+
+    def __init__(self, module: nn.Module, config: Optional[CompressionConfig] = None, *, lr: float = 0.1,
+                 momentum: float = 0.9, weight_decay: float = 0.0, fused_sgd: bool = True,
+                 optimizer: str = "sgd", betas=(0.9, 0.999), eps: float = 1e-8,
+                 process_group: Optional[dist.ProcessGroup] = None,
+                 symmetric: Optional[SymmetricMemory] = None, rank: Optional[int] = None,
+                 world: Optional[int] = None):
+        super().__init__()
+        self.module = module
+        self.config = config or CompressionConfig()
+        self.group = process_group
+        if rank is None:
+            rank = dist.get_rank(process_group) if dist.is_initialized() else 0
+        if world is None:
+            world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.rank, self.world = rank, world
+        self.params = [p for p in module.parameters() if p.requires_grad]
+        if not self.params:
+            raise ValueError("module has no trainable parameters")
+        self.device = self.params[0].device
+        if self.device.type != "cuda":
+            raise ValueError("CompressedDataParallel needs the module on a CUDA device")
+        for p in self.params:
+            if p.dtype != torch.float32:
+                raise ValueError("parameters must be float32 (use autocast for bf16 compute)")
+
+        bucket_elems = max(ALIGN, int(self.config.bucket_mb * (1 << 20) / 4) // ALIGN * ALIGN)
+        self.plan = plan_buckets([p.numel() for p in self.params], bucket_elems)
+        n = self.plan.total
+        dev = self.device
+        self.flat_param = torch.zeros(n, device=dev)
+        self.flat_grad = torch.zeros(n, device=dev)
+        self.flat_residual = torch.zeros(n, device=dev) if self.config.needs_residual else None
+        self.optimizer = optimizer
+        if optimizer not in ("sgd", "adamw"):
+            raise ValueError("optimizer must be 'sgd' or 'adamw'")
+        fused = fused_sgd or optimizer == "adamw"
+        self.flat_momentum = torch.zeros(n, device=dev) if fused else None
+        self.flat_second = torch.zeros(n, device=dev) if optimizer == "adamw" else None
+        self.flat_velocity = torch.zeros(n, device=dev) if self.config.momentum_correction else None
+        with torch.no_grad():
+            for p, off in zip(self.params, self.plan.offsets):
+                view = _view_like(self.flat_param[off:off + p.numel()], p)
+                view.copy_(p.data)
+                p.data = view
+                p.grad = _view_like(self.flat_grad[off:off + p.numel()], p)
+
+        if world > 1 and dist.is_initialized():
+            # every replica starts from rank 0's weights
+            dist.broadcast(self.flat_param, src=dist.get_global_rank(process_group, 0)
+                           if process_group is not None else 0, group=process_group)
+
+        self.engine = _C.DdpEngine(self.config.engine_dict(rank, world, dev.index), self.plan.buckets,
+                                   self.plan.param_bucket)
+        self.symmetric = symmetric or SymmetricMemory(self.engine.symmetric_bytes, dev, process_group)
+        if self.symmetric.nbytes < self.engine.symmetric_bytes:
+            raise ValueError("symmetric buffer too small for this model")
+        self.engine.set_buffers(self.flat_grad, self.flat_residual, self.flat_param, self.flat_momentum,
+                                self.flat_velocity, self.flat_second)
+        self.engine.set_symmetric(self.symmetric.buf)
+        self.fused_sgd = fused
+        self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
+        self.betas, self.eps = betas, eps
+        if optimizer == "adamw":
+            self.engine.set_adamw(lr, betas[0], betas[1], eps, weight_decay)
+        else:
+            self.engine.set_sgd(lr, momentum, weight_decay, fused_sgd)
+
+        self._in_step = False
+        self._hooks = []
+        for i, p in enumerate(self.params):
+            self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
+        self._dev_index = dev.index
+
+    # ------------------------------------------------------------------ hooks
+    def _make_hook(self, index: int):
+        def hook(_param):
+            if self._in_step:
+                self.engine.grad_ready(index, self._dev_index)
+        return hook
+
+    def forward(self, *args, **kwargs):
+        if self.training and torch.is_grad_enabled() and not self._in_step:
+            self.begin_step()
+        return self.module(*args, **kwargs)
+
+    def begin_step(self) -> None:
+        """Arm the engine for one backward pass (called automatically by ``forward``)."""
+        self.engine.begin_step()
+        self._in_step = True
+
+    def step(self) -> None:
+        """Wait until every bucket has been exchanged (and, with fused SGD, applied), then clear the
+        gradient buffer for the next backward."""
+        if not self._in_step:
+            raise RuntimeError("step() without a forward/backward since the last step()")
+        self.engine.finish_step(self._dev_index)
+        self._in_step = False
+        if self.fused_sgd:
+            self.flat_grad.zero_()
+
+    def zero_grad(self, set_to_none: bool = False) -> None:  # noqa: D401
+        """Gradients live in the flat buffer and are views: they are zeroed, never dropped."""
+        self.flat_grad.zero_()
+
+    def set_lr(self, lr: float) -> None:
+        self.lr = lr
+        if self.optimizer == "adamw":
+            self.engine.set_adamw(lr, self.betas[0], self.betas[1], self.eps, self.weight_decay)
+        else:
+            self.engine.set_sgd(lr, self.momentum, self.weight_decay, self.fused_sgd)
+
+    def set_keep_fraction(self, keep_fraction: float) -> None:
+        """Per-step sparsity (DGC warm-up); must not exceed the configured maximum."""
+        self.engine.set_keep_fraction(float(keep_fraction))
+
+    def check(self) -> None:
+        """Synchronise and raise if a kernel recorded a flag time-out or a malformed payload."""
+        status = self.engine.check_status()
+        if status != 0:
+            names = {1: "a peer's flag was not published in time", 2: "payload exceeds its slot",
+                     3: "malformed payload header"}
+            raise RuntimeError(f"hipress engine: {names.get(status, status)}")
+
+    # ------------------------------------------------------------------ state
+    def compression_state(self) -> Dict[str, torch.Tensor]:
+        """Residual / momentum state of the synchroniser, for checkpoints."""
+        out = {"steps": torch.tensor(self.engine.steps)}
+        if self.flat_residual is not None:
+            out["residual"] = self.flat_residual.clone()
+        if self.flat_momentum is not None:
+            out["momentum"] = self.flat_momentum.clone()
+        if self.flat_second is not None:
+            out["second_moment"] = self.flat_second.clone()
+        if self.flat_velocity is not None:
+            out["velocity"] = self.flat_velocity.clone()
+        return out
+
+    def load_compression_state(self, state: Dict[str, torch.Tensor]) -> None:
+        if "residual" in state and self.flat_residual is not None:
+            self.flat_residual.copy_(state["residual"])
+        if "momentum" in state and self.flat_momentum is not None:
+            self.flat_momentum.copy_(state["momentum"])
+        if "second_moment" in state and self.flat_second is not None:
+            self.flat_second.copy_(state["second_moment"])
+        if "velocity" in state and self.flat_velocity is not None:
+            self.flat_velocity.copy_(state["velocity"])
+
+    def metrics(self) -> Dict[str, float]:
+        dense = self.engine.dense_bytes_per_step
+        wire = self.engine.wire_bytes_per_step
+        return {"buckets": len(self.plan.buckets), "dense_bytes_per_step": dense,
+                "wire_bytes_per_step": wire,
+                "compression_ratio": dense * max(1, self.world - 1) / wire if wire else float("inf"),
+                "kernel_launches": self.engine.launches, "steps": self.engine.steps}
