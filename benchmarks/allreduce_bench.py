@@ -1,0 +1,163 @@
+"""Compressed all-reduce microbenchmark.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node W --master-addr 127.0.0.1 \
+        --master-port 29511 benchmarks/allreduce_bench.py [--sizes-mb 0.25 4 64 512] [--iters 20]
+
+Per-rank fp32 buffers of 256 KB / 4 MB / 64 MB / 512 MB with values N(0, 1e-3^2) seeded by
+rank are synchronised (sum / W on every rank) by
+
+* ``nccl``      torch.distributed all_reduce (the uncompressed baseline),
+* ``dense``     this framework's peer-to-peer dense path,
+* ``tbq``       threshold 2e-3,
+* ``terngrad``  2-bit, stochastic, error feedback,
+* ``dgc``       top-k 0.1 % with 1 % sample threshold estimation,
+
+each as ONE fused pipeline per step: compress kernels that store the packed payload straight
+into every peer's receive slot over NVLink, a bounded flag wait, and a one-pass unpack +
+accumulate of all W payloads.  Every number is device-timed with CUDA events (one pair per
+iteration, L2 flushed before each, ranks aligned by a barrier) and reported as the max over
+ranks of the median.  Effective GB/s = dense bytes (4 N) / time.  The roofline is the slower
+of the kernels' HBM traffic at the measured copy bandwidth and the bytes a rank must send
+over NVLink at 770 GB/s.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import hipress_b200 as hp  # noqa: E402
+from hipress_b200.parallel import SymmetricMemory  # noqa: E402
+from hipress_b200.utils.timing import flush_l2, max_over_ranks  # noqa: E402
+
+NVLINK_GBS = 770.0
+
+
+def measured_hbm_gbs() -> float:
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def hbm_bytes_per_elem(codec: str, world: int) -> float:
+    """Algorithmic HBM traffic of the fused pipeline per fp32 element."""
+    if codec == "tbq":       # compress: R grad + RW residual + W payload ; unpack: R payloads + W dense
+        return 4 + 8 + 0.25 * world + 0.25 * world + 4
+    if codec == "terngrad":  # min/max pass (grad + residual) then quantise pass
+        return 8 + (8 + 4 + 0.25 * world) + 0.25 * world + 4
+    if codec == "dgc":       # count pass RW, write pass R(+sparse W), zero-fill + scatter
+        return 12 + 4 + 4
+    if codec == "dense":
+        return 4 + 4 + 4 * world + 4
+    return 0.0
+
+
+def wire_bytes(codec: str, n: int, world: int) -> float:
+    per = {"tbq": n / 4, "terngrad": 10 + n / 4, "dgc": 4 + 8 * max(1, int(n * 0.001 + 0.999)),
+           "dense": 0.0}[codec]
+    if codec == "dense":
+        return 4.0 * n * (world - 1)  # pulled: every rank reads every peer's buffer
+    return per * (world - 1)
+
+
+def time_iters(fn, iters: int, warmup: int):
+    times = []
+    for i in range(warmup + iters):
+        flush_l2()
+        if dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(a.elapsed_time(b))
+    return max_over_ranks(statistics.median(times))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes-mb", type=float, nargs="+", default=[0.25, 4, 64, 512])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--codecs", nargs="+", default=["nccl", "dense", "tbq", "terngrad", "dgc"])
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    hbm = measured_hbm_gbs()
+    results = []
+    for mb in args.sizes_mb:
+        n = int(mb * (1 << 20) / 4)
+        gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+        grad0 = torch.randn(n, device=dev, generator=gen) * 1e-3
+        nccl_ms = None
+        for codec in args.codecs:
+            grad = grad0.clone()
+            if codec == "nccl":
+                if world == 1:
+                    continue
+
+                def fn():
+                    dist.all_reduce(grad)
+                    grad.mul_(1.0 / world)
+                ms = time_iters(fn, args.iters, args.warmup)
+                nccl_ms = ms
+                launches = None
+            else:
+                cfg = dict(rank=rank, world=world, device=local, codec=codec, threshold=2e-3, bitwidth=2,
+                           enable_random=1, error_feedback=1, keep_fraction=0.001, sample_rate=0.01, seed=1)
+                eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
+                sym = SymmetricMemory(eng.symmetric_bytes, dev)
+                resid = torch.zeros(n, device=dev)
+                eng.set_buffers(grad, resid, None, None)
+                eng.set_symmetric(sym.buf)
+                eng.set_sgd(0.0, 0.0, 0.0, False)
+                l0 = eng.launches
+
+                def fn():
+                    eng.begin_step()
+                    eng.bucket_ready(0, local)
+                    eng.finish_step(local)
+                ms = time_iters(fn, args.iters, args.warmup)
+                status = eng.check_status()
+                assert status == 0, f"engine status {status}"
+                launches = (eng.launches - l0) // (args.iters + args.warmup)
+                del eng, sym
+            dense_bytes = 4.0 * n
+            row = {"codec": codec, "world": world, "buffer_mb": mb, "n": n, "ms": round(ms, 4),
+                   "effective_gbs": round(dense_bytes / (ms * 1e-3) / 1e9, 2), "launches_per_step": launches}
+            if codec != "nccl":
+                t_hbm = hbm_bytes_per_elem(codec, world) * n / (hbm * 1e9)
+                t_link = wire_bytes(codec, n, world) / (NVLINK_GBS * 1e9)
+                roof = max(t_hbm, t_link)
+                row.update({"roofline_ms": round(roof * 1e3, 4), "roofline_bound": "hbm" if t_hbm >= t_link else "nvlink",
+                            "fraction_of_roofline": round(roof * 1e3 / ms, 3),
+                            "hbm_gbs_measured_peak": hbm})
+                if nccl_ms:
+                    row["speedup_vs_nccl"] = round(nccl_ms / ms, 2)
+            results.append(row)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
