@@ -1,0 +1,122 @@
+"""Run one kernel family on a small, fixed case (for ncu captures and quick event timings).
+
+    python benchmarks/kernel_probe.py --kernel terngrad --mb 64 --iters 3
+
+Inputs are larger than the 126 MB L2 by default (64 MB gradient + 64 MB residual + outputs) but
+hold well under 1 GB on the device, so a ``ncu --set full`` capture of one launch ends quickly.
+Prints device-timed ms per call (CUDA events, L2 flushed between calls) and achieved GB/s of
+algorithmic traffic against the measured copy bandwidth.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+from hipress_b200 import ops  # noqa: E402
+from hipress_b200.utils.timing import flush_l2  # noqa: E402
+
+
+def peak_hbm():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def timed(fn, iters):
+    out = []
+    for _ in range(iters):
+        flush_l2()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    return min(out)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="terngrad",
+                    choices=["terngrad", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q",
+                             "psgd_expand", "sgd"])
+    ap.add_argument("--mb", type=float, default=64.0)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--world", type=int, default=8, help="payload count for the unpack kernels")
+    args = ap.parse_args()
+    n = int(args.mb * (1 << 20) / 4)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    g = torch.randn(n, device=dev) * 1e-3
+    r = torch.zeros(n, device=dev)
+    hbm = peak_hbm()
+    k = args.kernel
+    if k == "terngrad":
+        out = torch.empty(ops.terngrad_payload_bytes(n, 2), dtype=torch.uint8, device=dev)
+        fn = lambda: ops.terngrad_compress(g, 2, True, 1, residual=r, out=out)
+        traffic = n * (8 + 8 + 4 + 0.25)
+    elif k == "terngrad_unpack":
+        pl = [ops.terngrad_compress(torch.randn(n, device=dev) * 1e-3, 2, True, s) for s in range(args.world)]
+        fn = lambda: ops.terngrad_decompress(pl, g, post_scale=1.0 / args.world)
+        traffic = n * (0.25 * args.world + 4)
+    elif k == "tbq":
+        out = torch.empty(ops.tbq_payload_bytes(n), dtype=torch.uint8, device=dev)
+        fn = lambda: ops.tbq_compress(g, r, 2e-3, out=out)
+        traffic = n * (4 + 8 + 0.25)
+    elif k == "tbq_unpack":
+        pl = [ops.tbq_compress(torch.randn(n, device=dev) * 1e-3, torch.zeros(n, device=dev), 2e-3) for _ in range(args.world)]
+        fn = lambda: ops.tbq_decompress(pl, g, 2e-3, post_scale=1.0 / args.world)
+        traffic = n * (0.25 * args.world + 4)
+    elif k == "sparse":
+        out = torch.empty(ops.sparse_payload_bytes(n, 0.001), dtype=torch.uint8, device=dev)
+        seed = [0]
+
+        def fn():
+            seed[0] += 1
+            ops.graddrop_compress(g, r, 0.01, 0.999, seed[0], out=out)
+        traffic = n * (12 + 4)
+    elif k == "ecq":
+        out = torch.empty(ops.ecq_payload_bytes(n, 2), dtype=torch.uint8, device=dev)
+        fn = lambda: ops.ecq_compress(g, r, 1.0, 0.9, 2, 1, out=out)
+        traffic = n * (8 + 8 + 4 + 0.25)
+    elif k in ("psgd_p", "psgd_q", "psgd_expand"):
+        rows = 4096
+        cols = n // rows
+        M = torch.randn(rows, cols, device=dev)
+        Q = torch.randn(cols, 4, device=dev)
+        P = torch.randn(rows, 4, device=dev)
+        if k == "psgd_p":
+            acc = torch.zeros(rows, 4, device=dev)
+            fn = lambda: ops.psgd_project(0, M, Q, [acc])
+            traffic = rows * cols * 4
+        elif k == "psgd_q":
+            acc = torch.zeros(cols, 4, device=dev)
+            fn = lambda: ops.psgd_project(1, M, P, [acc])
+            traffic = rows * cols * 4
+        else:
+            out = torch.zeros(rows * cols, device=dev)
+            fn = lambda: ops.psgd_expand_feedback(P, Q, M, out)
+            traffic = rows * cols * 12
+    else:
+        import hipress_b200 as hp
+        p, m = torch.randn(n, device=dev), torch.zeros(n, device=dev)
+        fn = lambda: hp._C.sgd_apply(g, p, m, 0.5, 0.1, 0.9, 0.0, False)
+        traffic = n * 24
+    fn()
+    torch.cuda.synchronize()
+    ms = timed(fn, args.iters)
+    gbs = traffic / (ms * 1e-3) / 1e9
+    print(json.dumps({"kernel": k, "mb": args.mb, "n": n, "ms": round(ms, 4), "algorithmic_gbs": round(gbs, 1),
+                      "fraction_of_measured_hbm": round(gbs / hbm, 3), "hbm_gbs_measured_peak": hbm}))
+
+
+if __name__ == "__main__":
+    main()

@@ -10,6 +10,8 @@
 //   ref_oracle tern_d in.bin in_size dense.bin n add
 //   ref_oracle gd_d   in.bin in_size dense.bin n add
 //   ref_oracle lcg    seed count out.bin        (count x {u32 raw via int generator range 2^31, f32 unit})
+//   ref_oracle bench  grad.bin n iters          (prints ms/iter of the reference host path: tbq, terngrad)
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -130,6 +132,27 @@ int main(int argc, char** argv) {
       out.push_back(fb);
     }
     dump(argv[4], out);
+  } else if (cmd == "bench") {
+    const int32_t n = atoi(argv[3]);
+    const int iters = atoi(argv[4]);
+    auto g = slurp<float>(argv[2], n);
+    std::vector<float> r(n, 0.f), d(n, 0.f);
+    std::vector<uint8_t> o1((n + 3) / 4), o2(10 + (n + 3) / 4);
+    auto now = [] { return std::chrono::steady_clock::now(); };
+    auto t0 = now();
+    for (int i = 0; i < iters; ++i) {
+      tbq_body<policy_t>(g.data(), n, r.data(), n, o1.data(), (int32_t)o1.size(), 0.01f, policy, nullptr);
+      tbq_r_body<policy_t>(d.data(), n, o1.data(), (int32_t)o1.size(), 0.01f, 0, policy, nullptr);
+    }
+    auto t1 = now();
+    for (int i = 0; i < iters; ++i) {
+      terngrad_body<policy_t>({g.data()}, {n}, {o2.data()}, {(int32_t)o2.size()}, {(uint8_t)2}, {1}, policy, nullptr);
+      terngrad_r_body<policy_t>({d.data()}, {n}, {o2.data()}, {(int32_t)o2.size()}, {0}, policy, nullptr);
+    }
+    auto t2 = now();
+    printf("{\"tbq_ms_per_iter\": %.3f, \"terngrad_ms_per_iter\": %.3f}\n",
+           std::chrono::duration<double, std::milli>(t1 - t0).count() / iters,
+           std::chrono::duration<double, std::milli>(t2 - t1).count() / iters);
   } else {
     return 1;
   }
