@@ -9,6 +9,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <pybind11/stl.h>
 
+#include <cstring>
+
 #include "comm/symm_mem.h"
 #include "common/codec_math.h"
 #include "common/lcg.h"
@@ -179,6 +181,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     Lcg32 a(seed), b(seed);
     for (int i = 0; i < count; ++i) out.emplace_back(a.next_below(0x7fffffffu), b.next_unit());
     return out;
+  });
+
+  // number of raw values in [start, start + count*stride) for which the reciprocal-multiply
+  // form of the unit draw differs from the reference's division form (expected: 0)
+  m.def("lcg_unit_mismatches", [](uint64_t start, uint64_t count, uint64_t stride) {
+    uint64_t bad = 0;
+    for (uint64_t i = 0; i < count; ++i) {
+      const uint32_t raw = uint32_t(start + i * stride);
+      const float a = Lcg32::unit_from_raw(raw), b = Lcg32::unit_from_raw_by_division(raw);
+      bad += std::memcmp(&a, &b, 4) != 0;
+    }
+    return bad;
   });
 
   // ---------------------------------------------------------------- probes

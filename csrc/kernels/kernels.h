@@ -74,10 +74,13 @@ size_t minmax_scratch_bytes();
 cudaError_t terngrad_compress(const float* grad, float* residual, int64_t n, int bitwidth,
                               int enable_random, uint64_t seed, const PushTargets& dst,
                               void* scratch, cudaStream_t stream);
-// Element count per payload is taken from its header and must equal n.
+// Element count per payload is taken from its header and must equal n; all
+// payloads must carry the same bitwidth (kBadHeader otherwise).  bitwidth_hint
+// (0 = unknown) lets the launcher size the decode table for that bitwidth; a
+// payload with another bitwidth is then rejected.
 cudaError_t terngrad_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
                                   float post_scale, const SgdApply& apply, int* status,
-                                  cudaStream_t stream);
+                                  cudaStream_t stream, int bitwidth_hint = 0);
 
 // ---------------------------------------------------------------- ECQ
 cudaError_t ecq_compress(const float* grad, float* history, int64_t n, float alpha, float beta,

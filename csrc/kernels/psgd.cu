@@ -482,7 +482,10 @@ cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const fl
   if (!ok_a || !ok_b) return cudaErrorInvalidValue;
   const int tiles = int((out_rows + kBM - 1) / kBM);
   const int total_kb = int(k_pad / kBK);
-  int splits = (148 * 2 + tiles - 1) / tiles;
+  // Two CTAs fit on an SM (110 KB of shared memory each): aim for one full wave of
+  // 148 x 2 CTAs, never more, so that no partial second wave runs at half occupancy.
+  constexpr int kResident = 148 * 2;
+  int splits = kResident / tiles;
   const int max_splits = total_kb / 4 > 0 ? total_kb / 4 : 1;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;

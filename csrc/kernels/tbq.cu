@@ -8,12 +8,13 @@
 // the tail on the host: tbq_body.h:114-155).
 //
 // Unpack-accumulate: one pass over the dense tensor that decodes the payloads
-// of all ranks in ascending rank order (the reference launches one full pass
-// per peer payload: hp_cuda_kernel.cu:182-196), optionally scales the sum and
-// applies a fused SGD-momentum update.
+// of all ranks in ascending rank order through a shared-memory byte table (the
+// reference launches one full pass per peer payload: hp_cuda_kernel.cu:182-196),
+// optionally scales the sum and applies a fused SGD-momentum update.
 #include "../common/codec_math.h"
 #include "kernels.h"
 #include "p2p.cuh"
+#include "unpack_lut.cuh"
 
 namespace hipress {
 namespace cuda {
@@ -79,49 +80,18 @@ tbq_compress_kernel(const float* __restrict__ grad, float* __restrict__ residual
   publish_when_grid_done(dst);
 }
 
-template <bool VEC, bool APPLY>
-__global__ void __launch_bounds__(kThreads)
-tbq_unpack_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
-                  float post_scale, SgdApply apply) {
-  const int64_t nbytes = (n + 3) >> 2;
-  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t b = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; b < nbytes; b += stride) {
-    const int64_t e0 = b << 2;
-    const int cnt = (n - e0) >= 4 ? 4 : int(n - e0);
-    float acc[4];
-    const bool vec = VEC && cnt == 4;
-    if (add) {
-      if (vec) {
-        const float4 o = reinterpret_cast<const float4*>(out)[b];
-        acc[0] = o.x; acc[1] = o.y; acc[2] = o.z; acc[3] = o.w;
-      } else {
-        for (int k = 0; k < cnt; ++k) acc[k] = out[e0 + k];
-      }
-    }
+// Table-driven unpack (see unpack_lut.cuh): one 256 x 4 table shared by all ranks.
+template <bool APPLY>
+__global__ void __launch_bounds__(kUnpackThreads)
+tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
+                      float post_scale, SgdApply apply) {
+  __shared__ __align__(16) float lut[256 * 4];
+  for (int v = threadIdx.x; v < 256; v += blockDim.x) {
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r < src.world) {
-        const uint32_t byte = src.payload[r][b];
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float v = tbq_dequant((byte >> (2 * k)) & 3u, thr);
-          acc[k] = (r == 0 && !add) ? v : hp_add(v, acc[k]);
-        }
-      }
-    }
-    if (post_scale != 1.0f) {
-#pragma unroll
-      for (int k = 0; k < 4; ++k) acc[k] = hp_mul(acc[k], post_scale);
-    }
-    if (vec) {
-      reinterpret_cast<float4*>(out)[b] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    } else {
-      for (int k = 0; k < cnt; ++k) out[e0 + k] = acc[k];
-    }
-    if (APPLY) {
-      for (int k = 0; k < cnt; ++k) sgd_update(apply, e0 + k, acc[k]);
-    }
+    for (int j = 0; j < 4; ++j) lut[v * 4 + j] = tbq_dequant((uint32_t(v) >> (2 * j)) & 3u, thr);
   }
+  __syncthreads();
+  unpack_lut_body<4, APPLY>(lut, 0, src, 0, out, n, add, post_scale, apply);
 }
 
 inline int grid_for(int64_t items, int threads, int max_blocks) {
@@ -151,16 +121,11 @@ cudaError_t tbq_unpack_accum(const UnpackSources& src, float threshold, float* o
                              int add, float post_scale, const SgdApply& apply,
                              cudaStream_t stream) {
   if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
-  const int grid = grid_for((n + 3) >> 2, kThreads, 148 * 8);
-  const bool vec = aligned16(out);
-  const bool ap = apply.param != nullptr;
-#define LAUNCH(V, A) \
-  tbq_unpack_kernel<V, A><<<grid, kThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply)
-  if (vec && ap) LAUNCH(true, true);
-  else if (vec) LAUNCH(true, false);
-  else if (ap) LAUNCH(false, true);
-  else LAUNCH(false, false);
-#undef LAUNCH
+  const int grid = grid_for((n + 3) >> 2, kUnpackThreads * 4, 148 * 4);
+  if (apply.param != nullptr)
+    tbq_unpack_lut_kernel<true><<<grid, kUnpackThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply);
+  else
+    tbq_unpack_lut_kernel<false><<<grid, kUnpackThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply);
   return cudaGetLastError();
 }
 

@@ -18,6 +18,7 @@
 #include "kernels.h"
 #include "p2p.cuh"
 #include "reduce.cuh"
+#include "unpack_lut.cuh"
 
 namespace hipress {
 namespace cuda {
@@ -211,10 +212,14 @@ __device__ __forceinline__ TernHeader read_header(const uint8_t* p, int64_t cap,
   return h;
 }
 
+// Table-driven unpack (see unpack_lut.cuh).  All payloads of one call must
+// carry the same bitwidth; it is read from the headers, so the host never has
+// to look at a payload.
 template <bool APPLY>
-__global__ void __launch_bounds__(kThreads)
-tern_unpack_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
-                   float post_scale, SgdApply apply, int* status) {
+__global__ void __launch_bounds__(kUnpackThreads)
+tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
+                       float post_scale, SgdApply apply, int* status, int bw_expected) {
+  extern __shared__ __align__(16) float lut[];  // [world][256][dpb]
   __shared__ TernHeader hdr[kMaxWorld];
   __shared__ int all_ok;
   if (threadIdx.x == 0) all_ok = 1;
@@ -224,57 +229,30 @@ tern_unpack_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int ad
     if (!hdr[threadIdx.x].ok) all_ok = 0;
   }
   __syncthreads();
+  const int bw = hdr[0].bw;
+  if (all_ok) {
+    for (int r = 1; r < src.world; ++r)
+      if (hdr[r].bw != bw) all_ok = 0;  // every thread computes the same verdict
+    if (bw_expected != 0 && bw != bw_expected) all_ok = 0;
+  }
+  __syncthreads();
   if (!all_ok) {
     if (blockIdx.x == 0 && threadIdx.x == 0 && status) atomicExch(status, int(kBadHeader));
     return;
   }
-  // one thread decodes 8 consecutive elements (1..8 payload bytes per rank)
-  const int64_t groups = (n + 7) >> 3;
-  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  const bool vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-  for (int64_t gidx = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; gidx < groups; gidx += stride) {
-    const int64_t e0 = gidx << 3;
-    const int cnt = (n - e0) >= 8 ? 8 : int(n - e0);
-    float acc[8];
-    const bool v4 = vec && cnt == 8;
-    if (add) {
-      if (v4) {
-        const float4 a = reinterpret_cast<const float4*>(out + e0)[0];
-        const float4 b = reinterpret_cast<const float4*>(out + e0)[1];
-        acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w;
-        acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
-      } else {
-        for (int k = 0; k < cnt; ++k) acc[k] = out[e0 + k];
-      }
-    }
-    for (int r = 0; r < src.world; ++r) {
-      const TernHeader h = hdr[r];
-      const uint8_t* data = src.payload[r] + kTernHeaderBytes;
-      // the 8 elements occupy bw bytes starting at e0*bw/8
-      uint64_t bits = 0;
-      const int64_t first = (e0 * h.bw) >> 3;
-      const int nb = (cnt * h.bw + 7) >> 3;
-      for (int b = 0; b < nb; ++b) bits |= uint64_t(data[first + b]) << (8 * b);
-      const uint32_t mask = (1u << h.bw) - 1u;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float v = tern_dequant(uint32_t(bits >> (k * h.bw)) & mask, h.gap, h.mn);
-        acc[k] = (r == 0 && !add) ? v : hp_add(v, acc[k]);
-      }
-    }
-    if (post_scale != 1.0f) {
-#pragma unroll
-      for (int k = 0; k < 8; ++k) acc[k] = hp_mul(acc[k], post_scale);
-    }
-    if (v4) {
-      reinterpret_cast<float4*>(out + e0)[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      reinterpret_cast<float4*>(out + e0)[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-    } else {
-      for (int k = 0; k < cnt; ++k) out[e0 + k] = acc[k];
-    }
-    if (APPLY) {
-      for (int k = 0; k < cnt; ++k) sgd_update(apply, e0 + k, acc[k]);
-    }
+  const int dpb = 8 / bw;
+  const uint32_t mask = (1u << bw) - 1u;
+  for (int i = threadIdx.x; i < src.world * 256; i += blockDim.x) {
+    const int r = i >> 8, v = i & 255;
+    for (int j = 0; j < dpb; ++j)
+      lut[i * dpb + j] = tern_dequant((uint32_t(v) >> (bw * j)) & mask, hdr[r].gap, hdr[r].mn);
+  }
+  __syncthreads();
+  switch (bw) {
+    case 1: unpack_lut_body<8, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+    case 2: unpack_lut_body<4, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+    case 4: unpack_lut_body<2, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+    default: unpack_lut_body<1, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
   }
 }
 
@@ -326,13 +304,28 @@ cudaError_t terngrad_compress(const float* grad, float* residual, int64_t n, int
 
 cudaError_t terngrad_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
                                   float post_scale, const SgdApply& apply, int* status,
-                                  cudaStream_t stream) {
+                                  cudaStream_t stream, int bitwidth_hint) {
   if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
-  const int grid = grid_for((n + 7) >> 3, kThreads, 148 * 8);
+  if (bitwidth_hint != 0 && !tern_bitwidth_ok(bitwidth_hint)) return cudaErrorInvalidValue;
+  // table size: world x 256 x dpb floats; without a hint, room for 1-bit payloads (dpb = 8)
+  const int dpb = bitwidth_hint ? 8 / bitwidth_hint : 8;
+  const size_t smem = size_t(src.world) * 256 * dpb * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(tern_unpack_lut_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 256 * 8 * 4);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tern_unpack_lut_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 256 * 8 * 4);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  // one thread decodes 4 payload bytes per rank and iteration; CTAs are sized so that the
+  // table build (world x 256 x dpb dequantisations) stays small against the decode work
+  const int64_t groups = (n + 3) / 4;
+  int grid = grid_for(groups, kUnpackThreads * 4, 148 * 4);
   if (apply.param)
-    tern_unpack_kernel<true><<<grid, kThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
+    tern_unpack_lut_kernel<true><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status, bitwidth_hint);
   else
-    tern_unpack_kernel<false><<<grid, kThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
+    tern_unpack_lut_kernel<false><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status, bitwidth_hint);
   return cudaGetLastError();
 }
 

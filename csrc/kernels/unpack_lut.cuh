@@ -1,0 +1,132 @@
+// One-pass decode + accumulate of up to 8 packed payloads through a
+// shared-memory byte table.
+//
+// A payload byte holds DPB = 8/bitwidth quantised elements.  Instead of
+// extracting and dequantising every field with integer and floating-point
+// instructions (which made the first version of these kernels issue-bound at
+// ~136 instructions per element for 8 ranks), each CTA first builds, per rank,
+// a table  byte value -> DPB decoded floats  (256 x DPB entries, computed with
+// the same contraction-free arithmetic as the CPU codec), and the main loop
+// then needs one 32-bit payload load per 4 bytes and one vector shared-memory
+// load per byte, plus the adds.  Accumulation order is the canonical one
+// (ascending rank, acc = decoded + acc), so results are bit-identical to
+// decoding the payloads one after another.
+#pragma once
+#include "../common/codec_math.h"
+#include "kernels.h"
+#include "p2p.cuh"
+
+namespace hipress {
+namespace cuda {
+
+constexpr int kUnpackThreads = 256;
+
+__device__ __forceinline__ uint32_t load_u32_any(const uint8_t* p) {
+  if ((reinterpret_cast<uintptr_t>(p) & 3) == 0) return *reinterpret_cast<const uint32_t*>(p);
+  return uint32_t(p[0]) | (uint32_t(p[1]) << 8) | (uint32_t(p[2]) << 16) | (uint32_t(p[3]) << 24);
+}
+
+__device__ __forceinline__ void sgd_update4(const SgdApply& a, int64_t i, const float* g) {
+  const float4 p4 = *reinterpret_cast<const float4*>(a.param + i);
+  float4 b4 = a.first_step ? make_float4(0, 0, 0, 0) : *reinterpret_cast<const float4*>(a.momentum + i);
+  float p[4] = {p4.x, p4.y, p4.z, p4.w};
+  float b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float d = g[k] + a.weight_decay * p[k];
+    b[k] = a.first_step ? d : a.mu * b[k] + d;
+    p[k] -= a.lr * b[k];
+  }
+  *reinterpret_cast<float4*>(a.momentum + i) = make_float4(b[0], b[1], b[2], b[3]);
+  *reinterpret_cast<float4*>(a.param + i) = make_float4(p[0], p[1], p[2], p[3]);
+}
+
+// lut: shared memory, entry (rank r, byte v, slot j) at lut[(r*rank_stride + v)*DPB + j];
+// rank_stride is 256 for per-rank tables and 0 when all ranks share one table.
+// data_offset: bytes to skip at the start of each payload (header size).
+template <int DPB, bool APPLY>
+__device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_stride,
+                                                const UnpackSources& src, int data_offset,
+                                                float* __restrict__ out, int64_t n, int add,
+                                                float post_scale, const SgdApply& apply) {
+  constexpr int EPG = 4 * DPB;  // elements per group of 4 payload bytes
+  const int64_t full_groups = n / EPG;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  const bool out_vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const bool apply_vec = APPLY && ((reinterpret_cast<uintptr_t>(apply.param) |
+                                    reinterpret_cast<uintptr_t>(apply.momentum)) & 15) == 0;
+  for (int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; grp < full_groups; grp += stride) {
+    const int64_t e0 = grp * EPG;
+    float acc[EPG];
+    if (add) {
+#pragma unroll
+      for (int k = 0; k < EPG; ++k) acc[k] = out[e0 + k];
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+      if (r < src.world) {
+        const uint32_t w = load_u32_any(src.payload[r] + data_offset + grp * 4);
+        const float* table = lut + size_t(r) * rank_stride * DPB;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const float* e = table + ((w >> (8 * b)) & 255u) * DPB;
+          float v[DPB];
+          if (DPB % 4 == 0) {
+#pragma unroll
+            for (int q = 0; q < DPB / 4; ++q) {
+              const float4 t = reinterpret_cast<const float4*>(e)[q];
+              v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+            }
+          } else if (DPB == 2) {
+            const float2 t = *reinterpret_cast<const float2*>(e);
+            v[0] = t.x; v[1] = t.y;
+          } else {
+            v[0] = e[0];
+          }
+#pragma unroll
+          for (int j = 0; j < DPB; ++j)
+            acc[b * DPB + j] = (r == 0 && !add) ? v[j] : hp_add(v[j], acc[b * DPB + j]);
+        }
+      }
+    }
+    if (post_scale != 1.0f) {
+#pragma unroll
+      for (int k = 0; k < EPG; ++k) acc[k] = hp_mul(acc[k], post_scale);
+    }
+    if (out_vec) {
+#pragma unroll
+      for (int q = 0; q < EPG / 4; ++q)
+        reinterpret_cast<float4*>(out + e0)[q] =
+            make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < EPG; ++k) out[e0 + k] = acc[k];
+    }
+    if (APPLY) {
+      if (apply_vec) {
+#pragma unroll
+        for (int q = 0; q < EPG / 4; ++q) sgd_update4(apply, e0 + 4 * q, acc + 4 * q);
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPG; ++k) sgd_update(apply, e0 + k, acc[k]);
+      }
+    }
+  }
+  // fewer than EPG leftover elements: one thread, element by element
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    for (int64_t e = full_groups * EPG; e < n; ++e) {
+      float acc = add ? out[e] : 0.f;
+      for (int r = 0; r < src.world; ++r) {
+        const uint32_t byte = src.payload[r][data_offset + e / DPB];
+        const float v = lut[(size_t(r) * rank_stride + byte) * DPB + int(e % DPB)];
+        acc = (r == 0 && !add) ? v : hp_add(v, acc);
+      }
+      if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
+      out[e] = acc;
+      if (APPLY) sgd_update(apply, e, acc);
+    }
+  }
+}
+
+}  // namespace cuda
+}  // namespace hipress

@@ -88,7 +88,9 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   }
   check(cudaDeviceSynchronize(), "sync");
   const int device = cfg.device;
-  pool_ = std::make_unique<WorkerPool>(nw, [device](int) { cudaSetDevice(device); });
+  // num_workers == 0: no threads; the thread that reports a bucket ready issues its kernels
+  if (cfg.num_workers >= 1)
+    pool_ = std::make_unique<WorkerPool>(nw, [device](int) { cudaSetDevice(device); });
 }
 
 DdpEngine::~DdpEngine() {
@@ -171,6 +173,12 @@ void DdpEngine::bucket_ready(int b, cudaStream_t producer) {
   if (submitted_.at(static_cast<size_t>(b)).exchange(1) != 0) return;
   check(cudaEventRecord(ready_events_[static_cast<size_t>(b)], producer), "cudaEventRecord");
   const int worker = b % static_cast<int>(workers_.size());
+  if (!pool_) {
+    issue_bucket(b, worker);
+    std::lock_guard<std::mutex> lk(mu_);
+    ++issued_;
+    return;
+  }
   pool_->submit_to(worker, [this, b](int w) {
     try {
       issue_bucket(b, w);
@@ -323,7 +331,7 @@ void DdpEngine::issue_recv(int b, int worker) {
       launched += 1;
       break;
     case Codec::kTernGrad:
-      check(cuda::terngrad_unpack_accum(src, g, n, 0, post, apply, status_, w.recv), "tern_unpack");
+      check(cuda::terngrad_unpack_accum(src, g, n, 0, post, apply, status_, w.recv, cfg_.bitwidth), "tern_unpack");
       applied = fused_sgd_;
       launched += 1;
       break;
@@ -380,11 +388,12 @@ void DdpEngine::finish_step(cudaStream_t consumer) {
   if (cfg_.defer_recv) {
     for (size_t b = 0; b < buckets_.size(); ++b) {
       const int worker = int(b) % static_cast<int>(workers_.size());
-      pool_->submit_to(worker, [this, b](int w) { issue_recv(int(b), w); });
+      if (pool_) pool_->submit_to(worker, [this, b](int w) { issue_recv(int(b), w); });
+      else issue_recv(int(b), worker);
     }
-    pool_->drain();
+    if (pool_) pool_->drain();
   }
-  if (pool_->error_count() > 0) {
+  if (pool_ && pool_->error_count() > 0) {
     const std::string err = pool_->last_error();
     throw std::runtime_error("hipress engine: worker failed: " + err);
   }

@@ -110,7 +110,7 @@ class DdpEngine {
   // (unused parameters) are flushed here.
   void finish_step(cudaStream_t consumer);
   // Blocks until every job handed to the workers so far has been issued to the device.
-  void drain() { pool_->drain(); }
+  void drain() { if (pool_) pool_->drain(); }
 
   // Synchronises and returns the device status word (cuda::Status); resets it.
   int check_status();
@@ -121,7 +121,7 @@ class DdpEngine {
   // wire bytes (compressed) and dense bytes of one step, for metrics
   int64_t wire_bytes_per_step() const;
   int64_t dense_bytes_per_step() const;
-  std::string last_error() { return pool_->last_error(); }
+  std::string last_error() { return pool_ ? pool_->last_error() : std::string(); }
 
  private:
   struct WorkerCtx {

@@ -42,3 +42,53 @@ class PinnedBatches:
         b = self.batches[self.i % len(self.batches)]
         self.i += 1
         return tuple(t.to(device, non_blocking=True) for t in b)
+
+
+class Prefetcher:
+    """Stages the *next* batch host-to-device on a side stream while the current step computes.
+
+    ``next()`` returns device tensors of one batch.  Every batch is copied from pinned memory
+    (each step's input does cross PCIe), but on a copy stream that runs alongside the previous
+    step's kernels instead of in front of this step's.  The device buffers are a fixed ring
+    allocated once: a slot is overwritten only after the consumer stream has passed the point
+    where the batch it held was last used, which the ring learns at the following ``next()``.
+    No allocator call happens per step (a per-step allocation would stall the pipeline: the
+    host runs several steps ahead of the device).
+    """
+
+    def __init__(self, pinned: PinnedBatches, device, depth: int = 3):
+        self.pinned = pinned
+        self.device = torch.device(device)
+        self.stream = torch.cuda.Stream(device=self.device)
+        proto = pinned.batches[0]
+        self.ring = [tuple(torch.empty(t.shape, dtype=t.dtype, device=self.device) for t in proto)
+                     for _ in range(depth)]
+        self.copied = [torch.cuda.Event() for _ in range(depth)]
+        self.released = [None] * depth
+        self.head = 0          # slot handed out by the next call
+        self.last = None       # slot handed out by the previous call
+        self._issue(self.head)
+
+    def _issue(self, slot: int) -> None:
+        b = self.pinned.batches[self.pinned.i % len(self.pinned.batches)]
+        self.pinned.i += 1
+        if self.released[slot] is not None:
+            self.stream.wait_event(self.released[slot])
+        with torch.cuda.stream(self.stream):
+            for dst, src in zip(self.ring[slot], b):
+                dst.copy_(src, non_blocking=True)
+            self.copied[slot].record(self.stream)
+
+    def next(self) -> Tuple[torch.Tensor, ...]:
+        cur = torch.cuda.current_stream(self.device)
+        if self.last is not None:
+            # everything that used the previous batch has been enqueued by now
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            self.released[self.last] = ev
+        slot = self.head
+        cur.wait_event(self.copied[slot])
+        self.last = slot
+        self.head = (slot + 1) % len(self.ring)
+        self._issue(self.head)
+        return self.ring[slot]

@@ -28,6 +28,16 @@ def test_lcg_matches_recurrence():
         assert 0.0 <= unit <= 1.0
 
 
+def test_lcg_unit_draw_multiply_equals_division():
+    # the codecs convert raw draws with a double multiply; the reference divides.  Equal for all
+    # 2^32 raw values (exhaustive check done offline); here: a strided sweep plus both ends.
+    C = hp._C
+    assert C.lcg_unit_mismatches(0, 1 << 24, 251) == 0
+    assert C.lcg_unit_mismatches(0, 1 << 16, 1) == 0
+    assert C.lcg_unit_mismatches((1 << 32) - (1 << 16), 1 << 16, 1) == 0
+    assert C.lcg_unit_mismatches((1 << 31) - (1 << 15), 1 << 16, 1) == 0
+
+
 # ----------------------------------------------------------------------------- TBQ
 def test_tbq_hand_vector():
     # g[i] = (i-5)*0.004, t = 0.01, N = 10 -> bytes 40 55 5a (hand-derived from tbq_body.h:70-87)
