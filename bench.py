@@ -38,6 +38,8 @@ def parse():
     ap.add_argument("--model", default="resnet50", choices=list(MODEL_BATCH))
     ap.add_argument("--algorithm", default=None, help="terngrad | tbq | graddrop | dgc | ecq | dense | powersgd | nccl")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch")
+    ap.add_argument("--dgc-start-step", type=int, default=400,
+                    help="position in DGC's 400-step sparsity warm-up at which the run starts (400 = steady state)")
     return ap.parse_args()
 
 
@@ -92,19 +94,23 @@ class OurTrainer:
         if self.is_image:
             net = net.to(memory_format=torch.channels_last)
         net.train()
+        # VGG without normalisation layers diverges at 0.1 on random data
+        self.lr = {"resnet50": 0.1, "vgg19": 0.01, "bert_large": 1e-4}[args.model]
         if self.algorithm == "powersgd":
             from hipress_b200.parallel.powersgd import PowerSGDDataParallel
-            self.model = PowerSGDDataParallel(net, rank_r=4, lr=0.1 if self.is_image else 1e-4, momentum=0.9)
+            self.model = PowerSGDDataParallel(net, rank_r=4, lr=self.lr, momentum=0.9)
         elif self.algorithm == "dgc":
             from hipress_b200.parallel.dgc import DGCDataParallel
-            self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4)
+            # measured in the steady state: the 400-step sparsity warm-up is skipped, not shortened
+            self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4,
+                                         start_step=args.dgc_start_step)
         elif self.algorithm == "nccl":
             from hipress_b200.parallel.baseline import NcclDataParallel
-            self.model = NcclDataParallel(net, lr=0.1, momentum=0.9)
+            self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9)
         else:
             cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
                                     threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=25.0)
-            self.model = CompressedDataParallel(net, cfg, lr=0.1, momentum=0.9, weight_decay=0.0, fused_sgd=True)
+            self.model = CompressedDataParallel(net, cfg, lr=self.lr, momentum=0.9, weight_decay=0.0, fused_sgd=True)
 
     def step(self, batch):
         torch = self.torch
@@ -303,7 +309,8 @@ def run(args):
         "config": {"model": args.model, "global_batch": global_batch, "per_gpu_batch": batch,
                    "seq_len": 128 if args.model == "bert_large" else None,
                    "parallelism": f"dp{world}", "algorithm": alg, "bucket_mb": 25,
-                   "optimizer": "sgd momentum 0.9 lr 0.1" if args.model != "bert_large" else "see model wrapper",
+                   "optimizer": {"resnet50": "sgd momentum 0.9 lr 0.1", "vgg19": "sgd momentum 0.9 lr 0.01",
+                                 "bert_large": "adamw lr 1e-4 (fused)"}[args.model],
                    "cache": "inputs+activations per step exceed the 126 MB L2; 4 distinct batches rotate"},
         "clocks": {"sm_mhz": clock_summary["sm_mhz"], "sm_max_mhz": clock_summary["sm_max_mhz"],
                    "reasons": clock_summary["reasons"]},

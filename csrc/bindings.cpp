@@ -13,6 +13,7 @@
 
 #include "comm/symm_mem.h"
 #include "common/codec_math.h"
+#include "common/host_utils.h"
 #include "common/lcg.h"
 #include "kernels/kernels.h"
 #include "ops/ops.h"
@@ -194,6 +195,20 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     }
     return bad;
   });
+
+  // support-layer utilities (branch-free abs, wall-clock checkpoint timer)
+  m.def("fast_abs_i32", [](int32_t v) { return fast_abs(v); });
+  m.def("fast_abs_i64", [](int64_t v) { return fast_abs(v); });
+  m.def("fast_abs_f32", [](float v) { return fast_abs(v); });
+  m.def("fast_abs_f64", [](double v) { return fast_abs(v); });
+  py::class_<TimeCost>(m, "TimeCost")
+      .def(py::init<>())
+      .def("start", &TimeCost::start)
+      .def("record", &TimeCost::record)
+      .def("intervals", &TimeCost::intervals, py::arg("per_second") = 1e6)
+      .def("print_by_us", &TimeCost::print_by_us)
+      .def("print_by_ms", &TimeCost::print_by_ms)
+      .def("print_by_s", &TimeCost::print_by_s);
 
   // ---------------------------------------------------------------- probes
   m.def("can_access_peer", &comm::can_access_peer);

@@ -53,19 +53,26 @@ __device__ __forceinline__ void push_bytes(const PushTargets& t, int64_t byte_of
     for (int i = 0; i < count; ++i) t.payload[p][byte_off + i] = src[i];
 }
 
-// Called by every thread at the end of a compressing kernel.  Makes the CTA's
-// payload stores visible system-wide, elects the last CTA through `done`, and
-// lets that CTA publish the epoch flag to every destination.  The counter is
-// left at zero for the next launch.
+// Called by every thread at the end of a compressing kernel.  Elects the last
+// CTA through `done` and lets it publish the epoch flag to every destination.
+// Ordering: the CTA barrier orders all of the CTA's payload stores before
+// thread 0's fence, and fences are cumulative, so one fence per CTA (not one per
+// thread: a system-scope fence is expensive, more so while a host-to-device
+// copy is in flight) makes the whole CTA's stores visible before the counter
+// is bumped; the last CTA fences again after observing every other CTA's bump
+// and only then releases the flags.  With a single local destination the
+// consumer is on this GPU and device scope is enough.  The counter is left at
+// zero for the next launch.
 __device__ __forceinline__ void publish_when_grid_done(const PushTargets& t) {
   if (t.done == nullptr) return;
-  __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) {
+    const bool remote = t.world > 1;
+    if (remote) __threadfence_system(); else __threadfence();
     const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
     const unsigned int prev = atomicAdd(t.done, 1u);
     if (prev == total - 1) {
-      __threadfence_system();
+      if (remote) __threadfence_system(); else __threadfence();
       *t.done = 0u;
       for (int p = 0; p < t.world; ++p)
         if (t.flag[p] != nullptr) st_release_sys(t.flag[p], t.epoch);

@@ -7,6 +7,7 @@
 
 #include <cmath>
 
+#include "../common/host_utils.h"
 #include "../ops/ops.h"
 
 namespace hipress {
@@ -122,7 +123,7 @@ bool TaskRuntime::submit_without_residual(const std::string& name, torch::Tensor
   check_input(tensor, "tensor");
   check_input(B, "B");
   check_input(C, "C");
-  if (is_root != 0 && is_root != 1) return false;
+  if (HP_UNLIKELY(is_root != 0 && is_root != 1)) return false;
   if (task_id != kCompTask && task_id != kDecompTask && task_id != kRootDecompCompTask) return false;
   Task t;
   t.tensor_name = name;
@@ -141,7 +142,7 @@ bool TaskRuntime::submit_with_residual(const std::string& name, torch::Tensor te
   check_input(residual, "residual");
   check_input(B, "B");
   check_input(C, "C");
-  if (is_root != 0 && is_root != 1) return false;
+  if (HP_UNLIKELY(is_root != 0 && is_root != 1)) return false;
   if (task_id != kCompTask && task_id != kDecompTask && task_id != kRootDecompCompTask) return false;
   Task t;
   t.tensor_name = name;

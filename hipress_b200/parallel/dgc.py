@@ -35,7 +35,10 @@ class DGCDataParallel(CompressedDataParallel):
     def __init__(self, module: nn.Module, keep_fraction: float = 0.001, *, sample_rate: float = 0.01,
                  warmup_steps: int = 400, momentum_correction: float = 0.9, clip_norm: float = 1.0,
                  lr: float = 1e-4, weight_decay: float = 0.01, optimizer: str = "adamw",
-                 bucket_mb: float = 25.0, seed: int = 1, **kw):
+                 bucket_mb: float = 25.0, seed: int = 1, start_step: int = 0, **kw):
+        # start_step: position in the warm-up schedule of the first step (resuming a run, or
+        # measuring the steady state without running the warm-up first)
+        self.start_step = int(start_step)
         self.schedule = warmup_schedule(keep_fraction, warmup_steps)
         max_keep = max(k for _, k in self.schedule)
         cfg = CompressionConfig("dgc", keep_fraction=max_keep, sample_rate=sample_rate, bucket_mb=bucket_mb,
@@ -44,7 +47,7 @@ class DGCDataParallel(CompressedDataParallel):
         super().__init__(module, cfg, lr=lr, momentum=0.0, weight_decay=weight_decay, fused_sgd=True,
                          optimizer=optimizer, **kw)
         self.target_keep = keep_fraction
-        self._apply_schedule(0)
+        self._apply_schedule(self.start_step)
 
     def keep_fraction_at(self, step: int) -> float:
         keep = self.schedule[0][1]
@@ -57,5 +60,5 @@ class DGCDataParallel(CompressedDataParallel):
         self.engine.set_keep_fraction(self.keep_fraction_at(step))
 
     def begin_step(self) -> None:
-        self._apply_schedule(self.engine.steps)
+        self._apply_schedule(self.start_step + self.engine.steps)
         super().begin_step()
