@@ -88,7 +88,7 @@ tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int
   __shared__ __align__(16) float lut[256 * 4];
   for (int v = threadIdx.x; v < 256; v += blockDim.x) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) lut[v * 4 + j] = tbq_dequant((uint32_t(v) >> (2 * j)) & 3u, thr);
+    for (int j = 0; j < 4; ++j) lut[lut_row(uint32_t(v)) * 4 + j] = tbq_dequant((uint32_t(v) >> (2 * j)) & 3u, thr);
   }
   __syncthreads();
   unpack_lut_body<4, APPLY>(lut, 0, src, 0, out, n, add, post_scale, apply);

@@ -245,7 +245,7 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
   for (int i = threadIdx.x; i < src.world * 256; i += blockDim.x) {
     const int r = i >> 8, v = i & 255;
     for (int j = 0; j < dpb; ++j)
-      lut[i * dpb + j] = tern_dequant((uint32_t(v) >> (bw * j)) & mask, hdr[r].gap, hdr[r].mn);
+      lut[(r * 256 + int(lut_row(uint32_t(v)))) * dpb + j] = tern_dequant((uint32_t(v) >> (bw * j)) & mask, hdr[r].gap, hdr[r].mn);
   }
   __syncthreads();
   switch (bw) {

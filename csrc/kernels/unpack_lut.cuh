@@ -41,7 +41,13 @@ __device__ __forceinline__ void sgd_update4(const SgdApply& a, int64_t i, const 
   *reinterpret_cast<float4*>(a.param + i) = make_float4(p[0], p[1], p[2], p[3]);
 }
 
-// lut: shared memory, entry (rank r, byte v, slot j) at lut[(r*rank_stride + v)*DPB + j];
+// Table row of byte value v.  Gradient payloads are dominated by a few byte values (fields
+// near the middle levels); with rows stored in natural order those values fall on only four
+// of the eight 16-byte bank groups and every table read is a multi-way bank conflict.  XOR-ing
+// two higher bits into the low bits spreads them over all eight groups (a bijection on 0..255).
+__device__ __forceinline__ uint32_t lut_row(uint32_t v) { return v ^ ((v >> 3) & 5u); }
+
+// lut: shared memory, entry (rank r, byte v, slot j) at lut[(r*rank_stride + lut_row(v))*DPB + j];
 // rank_stride is 256 for per-rank tables and 0 when all ranks share one table.
 // data_offset: bytes to skip at the start of each payload (header size).
 template <int DPB, bool APPLY>
@@ -55,8 +61,20 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
   const bool out_vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   const bool apply_vec = APPLY && ((reinterpret_cast<uintptr_t>(apply.param) |
                                     reinterpret_cast<uintptr_t>(apply.momentum)) & 15) == 0;
-  for (int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; grp < full_groups; grp += stride) {
+  int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  // payload words of the group being decoded; the next group's words are requested before
+  // the current ones are used, so their latency hides behind the decode
+  uint32_t w[kMaxWorld];
+#pragma unroll
+  for (int r = 0; r < kMaxWorld; ++r)
+    w[r] = (r < src.world && grp < full_groups) ? load_u32_any(src.payload[r] + data_offset + grp * 4) : 0u;
+  for (; grp < full_groups; grp += stride) {
     const int64_t e0 = grp * EPG;
+    const int64_t nxt = grp + stride;
+    uint32_t wn[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      wn[r] = (r < src.world && nxt < full_groups) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
     float acc[EPG];
     if (add) {
 #pragma unroll
@@ -65,11 +83,10 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r) {
       if (r < src.world) {
-        const uint32_t w = load_u32_any(src.payload[r] + data_offset + grp * 4);
         const float* table = lut + size_t(r) * rank_stride * DPB;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const float* e = table + ((w >> (8 * b)) & 255u) * DPB;
+          const float* e = table + lut_row((w[r] >> (8 * b)) & 255u) * DPB;
           float v[DPB];
           if (DPB % 4 == 0) {
 #pragma unroll
@@ -111,6 +128,8 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
         for (int k = 0; k < EPG; ++k) sgd_update(apply, e0 + k, acc[k]);
       }
     }
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) w[r] = wn[r];
   }
   // fewer than EPG leftover elements: one thread, element by element
   if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -118,7 +137,7 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
       float acc = add ? out[e] : 0.f;
       for (int r = 0; r < src.world; ++r) {
         const uint32_t byte = src.payload[r][data_offset + e / DPB];
-        const float v = lut[(size_t(r) * rank_stride + byte) * DPB + int(e % DPB)];
+        const float v = lut[(size_t(r) * rank_stride + lut_row(byte)) * DPB + int(e % DPB)];
         acc = (r == 0 && !add) ? v : hp_add(v, acc);
       }
       if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
