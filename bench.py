@@ -38,6 +38,8 @@ def parse():
     ap.add_argument("--model", default="resnet50", choices=list(MODEL_BATCH))
     ap.add_argument("--algorithm", default=None, help="terngrad | tbq | graddrop | dgc | ecq | dense | powersgd | nccl")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch")
+    ap.add_argument("--engine-workers", type=int, default=1,
+                    help="engine worker threads (0 = the hook thread issues the kernels itself)")
     ap.add_argument("--dgc-start-step", type=int, default=400,
                     help="position in DGC's 400-step sparsity warm-up at which the run starts (400 = steady state)")
     return ap.parse_args()
@@ -109,7 +111,8 @@ class OurTrainer:
             self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9)
         else:
             cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
-                                    threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=25.0)
+                                    threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=25.0,
+                                    num_workers=args.engine_workers)
             self.model = CompressedDataParallel(net, cfg, lr=self.lr, momentum=0.9, weight_decay=0.0, fused_sgd=True)
 
     def step(self, batch):

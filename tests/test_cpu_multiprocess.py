@@ -79,7 +79,10 @@ def _heartbeat_worker(rank, world, port, results):
     dist.all_reduce(t)
     hb.beat(0)
     assert hb.missing(0, timeout_s=10.0) == []
+    store.set(f"checked0/{rank}", "1")
     if rank == world - 1:
+        # leave only after everyone has seen step 0 complete
+        store.wait([f"checked0/{r}" for r in range(world)])
         hb.leave()                      # orderly exit between steps; no collective in flight
         results[rank] = "left"
     else:
