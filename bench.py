@@ -38,8 +38,8 @@ def parse():
     ap.add_argument("--model", default="resnet50", choices=list(MODEL_BATCH))
     ap.add_argument("--algorithm", default=None, help="terngrad | tbq | graddrop | dgc | ecq | dense | powersgd | nccl")
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch")
-    ap.add_argument("--engine-workers", type=int, default=1,
-                    help="engine worker threads (0 = the hook thread issues the kernels itself)")
+    ap.add_argument("--engine-workers", type=int, default=-1,
+                    help="engine worker threads (0 = the hook thread issues the kernels itself, -1 = auto)")
     ap.add_argument("--dgc-start-step", type=int, default=400,
                     help="position in DGC's 400-step sparsity warm-up at which the run starts (400 = steady state)")
     return ap.parse_args()

@@ -65,7 +65,7 @@ def main():
         traffic = n * (8 + 8 + 4 + 0.25)
     elif k == "terngrad_unpack":
         pl = [ops.terngrad_compress(torch.randn(n, device=dev) * 1e-3, 2, True, s) for s in range(args.world)]
-        fn = lambda: ops.terngrad_decompress(pl, g, post_scale=1.0 / args.world)
+        fn = lambda: ops.terngrad_decompress(pl, g, post_scale=1.0 / args.world, bitwidth=2)
         traffic = n * (0.25 * args.world + 4)
     elif k == "tbq":
         out = torch.empty(ops.tbq_payload_bytes(n), dtype=torch.uint8, device=dev)

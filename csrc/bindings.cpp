@@ -133,7 +133,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("bitwidth"), py::arg("enable_random"), py::arg("seed"),
         py::arg("residual") = py::none());
   m.def("terngrad_decompress", &ops::terngrad_decompress, py::arg("payloads"), py::arg("out"),
-        py::arg("add") = false, py::arg("post_scale") = 1.0);
+        py::arg("add") = false, py::arg("post_scale") = 1.0, py::arg("bitwidth") = 0);
   m.def("sparse_compress", &ops::sparse_compress, py::arg("grad"), py::arg("R"), py::arg("out"),
         py::arg("sample_rate"), py::arg("keep_fraction"), py::arg("seed"), py::arg("accumulate"));
   m.def("sparse_decompress", &ops::sparse_decompress, py::arg("payloads"), py::arg("out"),

@@ -24,6 +24,7 @@
 
 #include "kernels.h"
 #include "p2p.cuh"
+#include "unpack_lut.cuh"
 
 namespace hipress {
 namespace cuda {
@@ -394,6 +395,101 @@ expand_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t 
   }
 }
 
+// Vectorised form of the expansion for 16-byte aligned matrices with m % 4 == 0: a CTA owns a
+// 1024-column strip and walks down a band of rows; each thread keeps the Q rows of its four
+// columns in registers, reads P rows as broadcasts, and touches Mat / grad / param / momentum
+// with 16-byte accesses only (no per-element division).
+template <int MODE, int R>
+__global__ void __launch_bounds__(256)
+expand_rows_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t n, int64_t m,
+                   float* __restrict__ Mat, float* __restrict__ residual, float* __restrict__ grad,
+                   int64_t N, float scale, SgdApply apply, int rows_per_cta) {
+  const int64_t col = (int64_t(blockIdx.x) * 256 + threadIdx.x) * 4;
+  if (col >= m) return;
+  float q[4][R];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int c = 0; c < R; ++c) q[j][c] = Q[(col + j) * R + c];
+  const int64_t r0 = int64_t(blockIdx.y) * rows_per_cta;
+  const int64_t r1 = min(r0 + rows_per_cta, n);
+  for (int64_t i = r0; i < r1; ++i) {
+    float p[R];
+#pragma unroll
+    for (int c = 0; c < R; ++c) p[c] = __ldg(P + i * R + c);
+    float a[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float acc = 0.f;
+#pragma unroll
+      for (int c = 0; c < R; ++c) acc += p[c] * q[j][c];
+      a[j] = acc;
+    }
+    const int64_t e = i * m + col;
+    float4* mp = reinterpret_cast<float4*>(Mat + e);
+    if (MODE == 0) {
+      *mp = make_float4(a[0], a[1], a[2], a[3]);
+      if (e + 3 < N) {
+        const float4 g = *reinterpret_cast<const float4*>(grad + e);
+        *reinterpret_cast<float4*>(residual + e) = make_float4(g.x - a[0], g.y - a[1], g.z - a[2], g.w - a[3]);
+        *reinterpret_cast<float4*>(grad + e) = make_float4(a[0], a[1], a[2], a[3]);
+      } else {
+        for (int j = 0; j < 4; ++j)
+          if (e + j < N) {
+            residual[e + j] = grad[e + j] - a[j];
+            grad[e + j] = a[j];
+          }
+      }
+    } else {
+      const float4 mv = *mp;
+      *mp = make_float4(mv.x - a[0], mv.y - a[1], mv.z - a[2], mv.w - a[3]);
+      float g[4] = {a[0] * scale, a[1] * scale, a[2] * scale, a[3] * scale};
+      if (MODE == 1) {
+        if (e + 3 < N) {
+          *reinterpret_cast<float4*>(grad + e) = make_float4(g[0], g[1], g[2], g[3]);
+        } else {
+          for (int j = 0; j < 4; ++j)
+            if (e + j < N) grad[e + j] = g[j];
+        }
+      } else {
+        if (e + 3 < N) {
+          sgd_update4(apply, e, g);
+        } else {
+          for (int j = 0; j < 4; ++j)
+            if (e + j < N) sgd_update(apply, e + j, g[j]);
+        }
+      }
+    }
+  }
+}
+
+template <int MODE>
+bool launch_expand_rows(const float* P, const float* Q, int64_t n, int64_t m, int r, float* Mat,
+                        float* residual, float* grad, int64_t N, float scale, const SgdApply& apply,
+                        cudaStream_t stream) {
+  auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  if ((m & 3) != 0 || !al(Mat) || !al(residual) || !al(grad) || !al(apply.param) || !al(apply.momentum))
+    return false;
+  const unsigned col_blocks = unsigned((m / 4 + 255) / 256);
+  // enough CTAs for ~8 per SM, at least 8 rows each
+  int64_t row_blocks = (148 * 8 + col_blocks - 1) / col_blocks;
+  if (row_blocks > (n + 7) / 8) row_blocks = (n + 7) / 8;
+  if (row_blocks < 1) row_blocks = 1;
+  const int rows_per = int((n + row_blocks - 1) / row_blocks);
+  const dim3 grid(col_blocks, unsigned((n + rows_per - 1) / rows_per), 1);
+#define HP_EXPAND(RR) \
+  expand_rows_kernel<MODE, RR><<<grid, 256, 0, stream>>>(P, Q, n, m, Mat, residual, grad, N, scale, apply, rows_per)
+  switch (r) {
+    case 1: HP_EXPAND(1); break;
+    case 2: HP_EXPAND(2); break;
+    case 4: HP_EXPAND(4); break;
+    case 8: HP_EXPAND(8); break;
+    default: return false;
+  }
+#undef HP_EXPAND
+  return true;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -517,6 +613,9 @@ cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int6
                                  float* Mat, float* residual, float* grad, int64_t N, int mode,
                                  float post_scale, cudaStream_t stream) {
   if (n < 1 || m < 1 || r < 1 || r > kBN || N > n * m) return cudaErrorInvalidValue;
+  if (mode == 0 ? launch_expand_rows<0>(P, Q, n, m, r, Mat, residual, grad, N, post_scale, SgdApply{}, stream)
+                : launch_expand_rows<1>(P, Q, n, m, r, Mat, residual, grad, N, post_scale, SgdApply{}, stream))
+    return cudaGetLastError();
   int64_t blocks = (n * m + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (mode == 0)
@@ -531,6 +630,8 @@ cudaError_t psgd_expand_sgd(const float* P, const float* Q, int64_t n, int64_t m
   if (n < 1 || m < 1 || r < 1 || r > kBN || N > n * m || apply.param == nullptr ||
       apply.momentum == nullptr)
     return cudaErrorInvalidValue;
+  if (launch_expand_rows<2>(P, Q, n, m, r, Mat, nullptr, nullptr, N, post_scale, apply, stream))
+    return cudaGetLastError();
   int64_t blocks = (n * m + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   expand_kernel<2><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, nullptr, nullptr, N, post_scale, apply);

@@ -323,13 +323,23 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
     const int64_t e0 = base + int64_t(threadIdx.x) * 4;
     float v[4];
     uint32_t key[4];
-    unsigned int n_eq = 0;
+    unsigned int n_eq = 0, n_hit = 0;
+    if (e0 + 3 < end && (reinterpret_cast<uintptr_t>(R + e0) & 15) == 0) {
+      const float4 q = *reinterpret_cast<const float4*>(R + e0);
+      v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = (e0 + j < end) ? R[e0 + j] : 0.0f;
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      v[j] = (e0 + j < end) ? R[e0 + j] : 0.0f;
       key[j] = (e0 + j < end) ? abs_key(v[j]) : 0u;
       n_eq += (e0 + j < end) && key[j] == cut;
+      n_hit += (e0 + j < end) && key[j] >= cut;
     }
+    // almost every tile holds nothing at or above the cut (0.1 % is kept): those tiles
+    // cost one barrier and no scan.  Ties only matter while some are still to be kept.
+    if (!__syncthreads_or(int(n_hit))) continue;
     // exclusive scan of tie counts across the CTA (ties decide who is kept)
     unsigned int inc_e = n_eq;
 #pragma unroll

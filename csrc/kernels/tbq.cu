@@ -121,7 +121,8 @@ cudaError_t tbq_unpack_accum(const UnpackSources& src, float threshold, float* o
                              int add, float post_scale, const SgdApply& apply,
                              cudaStream_t stream) {
   if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
-  const int grid = grid_for((n + 3) >> 2, kUnpackThreads * 4, 148 * 4);
+  // one thread decodes 16 elements per iteration
+  const int grid = grid_for((n + 15) >> 4, kUnpackThreads, 148 * 8);
   if (apply.param != nullptr)
     tbq_unpack_lut_kernel<true><<<grid, kUnpackThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply);
   else

@@ -214,11 +214,13 @@ __device__ __forceinline__ TernHeader read_header(const uint8_t* p, int64_t cap,
 
 // Table-driven unpack (see unpack_lut.cuh).  All payloads of one call must
 // carry the same bitwidth; it is read from the headers, so the host never has
-// to look at a payload.
-template <bool APPLY>
+// to look at a payload.  BW > 0 compiles the decode loop for that bitwidth only
+// (fewer registers, more resident CTAs); BW == 0 dispatches on the header at
+// run time for callers that do not know the bitwidth.
+template <int BW, bool APPLY>
 __global__ void __launch_bounds__(kUnpackThreads)
 tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
-                       float post_scale, SgdApply apply, int* status, int bw_expected) {
+                       float post_scale, SgdApply apply, int* status) {
   extern __shared__ __align__(16) float lut[];  // [world][256][dpb]
   __shared__ TernHeader hdr[kMaxWorld];
   __shared__ int all_ok;
@@ -229,11 +231,10 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
     if (!hdr[threadIdx.x].ok) all_ok = 0;
   }
   __syncthreads();
-  const int bw = hdr[0].bw;
+  const int bw = BW > 0 ? BW : hdr[0].bw;
   if (all_ok) {
-    for (int r = 1; r < src.world; ++r)
+    for (int r = 0; r < src.world; ++r)
       if (hdr[r].bw != bw) all_ok = 0;  // every thread computes the same verdict
-    if (bw_expected != 0 && bw != bw_expected) all_ok = 0;
   }
   __syncthreads();
   if (!all_ok) {
@@ -245,15 +246,41 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
   for (int i = threadIdx.x; i < src.world * 256; i += blockDim.x) {
     const int r = i >> 8, v = i & 255;
     for (int j = 0; j < dpb; ++j)
-      lut[(r * 256 + int(lut_row(uint32_t(v)))) * dpb + j] = tern_dequant((uint32_t(v) >> (bw * j)) & mask, hdr[r].gap, hdr[r].mn);
+      lut[(r * 256 + int(lut_row(uint32_t(v)))) * dpb + j] =
+          tern_dequant((uint32_t(v) >> (bw * j)) & mask, hdr[r].gap, hdr[r].mn);
   }
   __syncthreads();
-  switch (bw) {
-    case 1: unpack_lut_body<8, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
-    case 2: unpack_lut_body<4, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
-    case 4: unpack_lut_body<2, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
-    default: unpack_lut_body<1, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+  if (BW > 0) {
+    unpack_lut_body<8 / (BW > 0 ? BW : 1), APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply);
+  } else {
+    switch (bw) {
+      case 1: unpack_lut_body<8, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+      case 2: unpack_lut_body<4, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+      case 4: unpack_lut_body<2, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+      default: unpack_lut_body<1, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+    }
   }
+}
+
+template <int BW, bool APPLY>
+cudaError_t launch_tern_unpack(const UnpackSources& src, float* out, int64_t n, int add, float post_scale,
+                               const SgdApply& apply, int* status, cudaStream_t stream) {
+  // table size: world x 256 x dpb floats; without a known bitwidth, room for 1-bit payloads (dpb = 8)
+  const int dpb = BW > 0 ? 8 / BW : 8;
+  const size_t smem = size_t(src.world) * 256 * dpb * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(tern_unpack_lut_kernel<BW, APPLY>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 256 * 8 * 4);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  // one thread decodes 4 payload bytes per rank and iteration; a CTA covers at least 4 K
+  // elements so that building the table stays small against the decode work
+  const int64_t groups = (n + 4 * dpb - 1) / (4 * dpb);
+  const int grid = grid_for(groups, kUnpackThreads, 148 * 8);
+  tern_unpack_lut_kernel<BW, APPLY><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status);
+  return cudaGetLastError();
 }
 
 }  // namespace
@@ -307,26 +334,18 @@ cudaError_t terngrad_unpack_accum(const UnpackSources& src, float* out, int64_t 
                                   cudaStream_t stream, int bitwidth_hint) {
   if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
   if (bitwidth_hint != 0 && !tern_bitwidth_ok(bitwidth_hint)) return cudaErrorInvalidValue;
-  // table size: world x 256 x dpb floats; without a hint, room for 1-bit payloads (dpb = 8)
-  const int dpb = bitwidth_hint ? 8 / bitwidth_hint : 8;
-  const size_t smem = size_t(src.world) * 256 * dpb * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tern_unpack_lut_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 256 * 8 * 4);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(tern_unpack_lut_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 256 * 8 * 4);
-    if (e != cudaSuccess) return e;
-    attr_set = true;
+  const bool ap = apply.param != nullptr;
+#define HP_UNPACK(BW) \
+  (ap ? launch_tern_unpack<BW, true>(src, out, n, add, post_scale, apply, status, stream) \
+      : launch_tern_unpack<BW, false>(src, out, n, add, post_scale, apply, status, stream))
+  switch (bitwidth_hint) {
+    case 1: return HP_UNPACK(1);
+    case 2: return HP_UNPACK(2);
+    case 4: return HP_UNPACK(4);
+    case 8: return HP_UNPACK(8);
+    default: return HP_UNPACK(0);
   }
-  // one thread decodes 4 payload bytes per rank and iteration; CTAs are sized so that the
-  // table build (world x 256 x dpb dequantisations) stays small against the decode work
-  const int64_t groups = (n + 3) / 4;
-  int grid = grid_for(groups, kUnpackThreads * 4, 148 * 4);
-  if (apply.param)
-    tern_unpack_lut_kernel<true><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status, bitwidth_hint);
-  else
-    tern_unpack_lut_kernel<false><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status, bitwidth_hint);
-  return cudaGetLastError();
+#undef HP_UNPACK
 }
 
 }  // namespace cuda

@@ -201,7 +201,7 @@ void terngrad_compress(const torch::Tensor& grad, torch::Tensor out, int64_t bit
 }
 
 void terngrad_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
-                         double post_scale) {
+                         double post_scale, int64_t bitwidth) {
   check_f32(out, "out");
   const int64_t n = out.numel();
   TORCH_CHECK(n > 0, "empty tensor");
@@ -210,7 +210,7 @@ void terngrad_decompress(const std::vector<torch::Tensor>& payloads, torch::Tens
     HP_CHECK_CUDA(cuda::terngrad_unpack_accum(sources_of(payloads, out), out.data_ptr<float>(), n,
                                               add ? 1 : 0, float(post_scale), cuda::SgdApply{},
                                               status_word_for(out),
-                                              at::cuda::getCurrentCUDAStream()));
+                                              at::cuda::getCurrentCUDAStream(), int(bitwidth)));
   } else {
     TORCH_CHECK(!payloads.empty(), "at least one payload expected");
     for (size_t r = 0; r < payloads.size(); ++r) {

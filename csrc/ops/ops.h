@@ -29,8 +29,10 @@ void tbq_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor ou
 
 void terngrad_compress(const torch::Tensor& grad, torch::Tensor out, int64_t bitwidth,
                        bool enable_random, int64_t seed, c10::optional<torch::Tensor> residual);
+// bitwidth: 0 = read it from the payload headers on the device; a known bitwidth selects a kernel
+// compiled for it (payloads with another bitwidth are then rejected through the status word).
 void terngrad_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
-                         double post_scale);
+                         double post_scale, int64_t bitwidth);
 
 // accumulate: R += grad first (GradDrop).  Otherwise grad may be undefined (DGC).
 void sparse_compress(const c10::optional<torch::Tensor>& grad, torch::Tensor R, torch::Tensor out,

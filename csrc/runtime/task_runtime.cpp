@@ -254,7 +254,7 @@ void TaskRuntime::run_decompress(Task& t) {
   auto out = t.tensor.view(-1);
   const bool add = t.is_root != 0;  // is_root doubles as "accumulate" (ref hp_cuda.cpp:236, 417, 567)
   if (a.name == "terngrad") {
-    ops::terngrad_decompress({t.B}, out, add, 1.0);
+    ops::terngrad_decompress({t.B}, out, add, 1.0, alg_.bitwidth);
   } else if (a.name == "tbq") {
     ops::tbq_decompress({t.B}, out, a.threshold, add, 1.0);
   } else if (a.name == "graddrop") {
@@ -289,7 +289,7 @@ void TaskRuntime::run_root(Task& t) {
   auto out = t.tensor.view(-1);
   const bool add = t.is_root != 0;
   if (!peers.empty()) {
-    if (a.name == "terngrad") ops::terngrad_decompress(peers, out, add, 1.0);
+    if (a.name == "terngrad") ops::terngrad_decompress(peers, out, add, 1.0, alg_.bitwidth);
     else if (a.name == "tbq") ops::tbq_decompress(peers, out, a.threshold, add, 1.0);
     else if (a.name == "graddrop") ops::sparse_decompress(peers, out, add, 1.0);
     else TORCH_CHECK(false, "task 30 is not valid for algorithm ", a.name);

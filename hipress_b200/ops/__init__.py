@@ -96,9 +96,12 @@ def terngrad_compress(grad: torch.Tensor, bitwidth: int = 2, enable_random: bool
 
 
 def terngrad_decompress(payloads, out: torch.Tensor, add: bool = False,
-                        post_scale: float = 1.0) -> torch.Tensor:
-    """Decode payload(s); each carries its own header (ref terngrad_body.h:309-409)."""
-    _C.terngrad_decompress(_as_list(payloads), out.view(-1), bool(add), float(post_scale))
+                        post_scale: float = 1.0, bitwidth: int = 0) -> torch.Tensor:
+    """Decode payload(s); each carries its own header (ref terngrad_body.h:309-409).
+
+    ``bitwidth`` (optional) names the bitwidth all payloads are known to have, which selects a
+    kernel compiled for it; 0 reads it from the headers on the device."""
+    _C.terngrad_decompress(_as_list(payloads), out.view(-1), bool(add), float(post_scale), int(bitwidth))
     return out
 
 

@@ -49,7 +49,10 @@ class CompressionConfig:
     bucket_mb: float = 25.0
     average: bool = True
     flag_timeout_s: float = 20.0
-    num_workers: int = 1
+    # engine threads that issue the buckets' kernels: 0 = the backward-hook thread launches them
+    # itself; -1 = choose (a worker thread once a step has enough launches to be worth moving
+    # off the autograd thread, none for a handful of buckets where the hand-off costs more)
+    num_workers: int = -1
     # DGC extras (algorithm "dgc"): momentum correction with factor masking, local clipping
     momentum_correction: bool = False
     dgc_momentum: float = 0.9
@@ -173,8 +176,11 @@ class CompressedDataParallel(nn.Module):
             dist.broadcast(self.flat_param, src=dist.get_global_rank(process_group, 0)
                            if process_group is not None else 0, group=process_group)
 
-        self.engine = _C.DdpEngine(self.config.engine_dict(rank, world, dev.index), self.plan.buckets,
-                                   self.plan.param_bucket)
+        cfg_dict = self.config.engine_dict(rank, world, dev.index)
+        if self.config.num_workers < 0:
+            per_bucket = {"dgc": 12 + world, "graddrop": 10 + world}.get(self.config.algorithm, 4)
+            cfg_dict["num_workers"] = 1 if len(self.plan.buckets) * per_bucket > 200 else 0
+        self.engine = _C.DdpEngine(cfg_dict, self.plan.buckets, self.plan.param_bucket)
         self.symmetric = symmetric or SymmetricMemory(self.engine.symmetric_bytes, dev, process_group)
         if self.symmetric.nbytes < self.engine.symmetric_bytes:
             raise ValueError("symmetric buffer too small for this model")

@@ -318,3 +318,29 @@ def test_sgd_apply_matches_torch():
         opt.step()
         hp._C.sgd_apply(g.clone(), p, mom, 0.5, 0.1, 0.9, 1e-4, step == 0)
         torch.testing.assert_close(p, ref_p.data, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("n,m,r", [(128, 512, 4), (300, 1024, 2), (64, 4608, 8), (100, 333, 4)])
+def test_psgd_expand_paths_match_torch(n, m, r):
+    """Vectorised (m % 4 == 0) and generic expand kernels: feedback form and fused-SGD form."""
+    torch.manual_seed(n + m)
+    P, Q = torch.randn(n, r, device="cuda"), torch.randn(m, r, device="cuda")
+    M0 = torch.randn(n, m, device="cuda")
+    approx = P @ Q.T
+    M = M0.clone()
+    out = torch.zeros(n * m, device="cuda")
+    ops.psgd_expand_feedback(P, Q, M, out, post_scale=0.25)
+    torch.testing.assert_close(M, M0 - approx, atol=1e-4, rtol=1e-5)
+    torch.testing.assert_close(out.view(n, m), approx * 0.25, atol=1e-4, rtol=1e-5)
+    # fused SGD: two steps against torch.optim.SGD fed with the same approximations
+    M = M0.clone()
+    param = torch.randn(n * m, device="cuda")
+    ref = torch.nn.Parameter(param.clone())
+    opt = torch.optim.SGD([ref], lr=0.1, momentum=0.9, weight_decay=1e-4)
+    mom = torch.zeros(n * m, device="cuda")
+    for step in range(2):
+        ref.grad = approx.reshape(-1).clone()
+        opt.step()
+        hp._C.psgd_expand_sgd(P, Q, M, param, mom, 1.0, 0.1, 0.9, 1e-4, step == 0)
+        torch.testing.assert_close(param, ref.data, atol=1e-4, rtol=1e-5)
+    torch.testing.assert_close(M, M0 - 2 * approx, atol=2e-4, rtol=1e-5)
