@@ -108,7 +108,9 @@ class OurTrainer:
                                          start_step=args.dgc_start_step)
         elif self.algorithm == "nccl":
             from hipress_b200.parallel.baseline import NcclDataParallel
-            self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9)
+            self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9,
+                                          optimizer="adamw" if args.model == "bert_large" else "sgd",
+                                          weight_decay=0.01 if args.model == "bert_large" else 0.0)
         else:
             cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
                                     threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=25.0,
@@ -273,25 +275,33 @@ def run(args):
     clock_summary = clocks.summary()
 
     # ---- end-to-end region: H2D of each step's batch from pinned memory + loss read back
+    # One-time set-up (staging ring, pinned loss buffers) and two untimed steps through the same
+    # path come first; the timed region is exactly K steps, each with its own H2D copy of the
+    # batch and D2H read of the loss.
     from hipress_b200.utils import Prefetcher
-    barrier()
-    t0 = time.perf_counter()
-    last = 0.0
-    feed = Prefetcher(pinned, dev)     # first copy is issued inside the timed region
-    # every step's loss is read back to the host; the read of step i is collected after step i+1
-    # has been launched, so the device never idles waiting for the host
+    feed = Prefetcher(pinned, dev)
     host_loss = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
     ready = [torch.cuda.Event(), torch.cuda.Event()]
-    losses = []
-    for i in range(args.steps):
-        loss = trainer.step(feed.next())
-        host_loss[i & 1].copy_(loss.detach().float().view(1), non_blocking=True)
-        ready[i & 1].record()
-        if i > 0:
-            ready[(i - 1) & 1].synchronize()
-            losses.append(float(host_loss[(i - 1) & 1]))
-    ready[(args.steps - 1) & 1].synchronize()
-    losses.append(float(host_loss[(args.steps - 1) & 1]))
+
+    def e2e_steps(count):
+        # the loss of step i is collected after step i+1 has been launched, so the device never
+        # idles waiting for the host; all `count` losses are read before the function returns
+        got = []
+        for i in range(count):
+            loss = trainer.step(feed.next())
+            host_loss[i & 1].copy_(loss.detach().float().view(1), non_blocking=True)
+            ready[i & 1].record()
+            if i > 0:
+                ready[(i - 1) & 1].synchronize()
+                got.append(float(host_loss[(i - 1) & 1]))
+        ready[(count - 1) & 1].synchronize()
+        got.append(float(host_loss[(count - 1) & 1]))
+        return got
+
+    e2e_steps(2)
+    barrier()
+    t0 = time.perf_counter()
+    losses = e2e_steps(args.steps)
     last = losses[-1]
     barrier()
     e2e_s = max_over_ranks(time.perf_counter() - t0, dev)

@@ -176,6 +176,30 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
         });
 
+  // fused AdamW (decoupled weight decay, bias correction) over flat fp32 buffers; step is 1-based
+  m.def("adamw_apply",
+        [](torch::Tensor grad, torch::Tensor param, torch::Tensor exp_avg, torch::Tensor exp_avg_sq,
+           double scale, double lr, double beta1, double beta2, double eps, double wd, int64_t step) {
+          TORCH_CHECK(grad.is_cuda() && param.is_cuda() && exp_avg.is_cuda() && exp_avg_sq.is_cuda(),
+                      "CUDA tensors expected");
+          TORCH_CHECK(grad.numel() == param.numel() && grad.numel() == exp_avg.numel() &&
+                      grad.numel() == exp_avg_sq.numel(), "size mismatch");
+          c10::cuda::CUDAGuard guard(grad.device());
+          cuda::AdamWApply a;
+          a.param = param.data_ptr<float>();
+          a.exp_avg = exp_avg.data_ptr<float>();
+          a.exp_avg_sq = exp_avg_sq.data_ptr<float>();
+          a.lr = float(lr);
+          a.beta1 = float(beta1);
+          a.beta2 = float(beta2);
+          a.eps = float(eps);
+          a.weight_decay = float(wd);
+          a.step = int(step);
+          cudaError_t e = cuda::adamw_apply_dense(grad.data_ptr<float>(), float(scale), a, grad.numel(),
+                                                  current_stream(grad.get_device()));
+          TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+        });
+
   // LCG draws, for checking the generator against the reference's
   m.def("lcg_draws", [](uint32_t seed, int count) {
     std::vector<std::pair<uint32_t, float>> out;

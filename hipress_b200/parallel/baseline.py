@@ -16,7 +16,8 @@ from .ddp import _view_like, plan_buckets, ALIGN
 
 class NcclDataParallel(nn.Module):
     def __init__(self, module: nn.Module, *, lr: float = 0.1, momentum: float = 0.9,
-                 weight_decay: float = 0.0, bucket_mb: float = 25.0,
+                 weight_decay: float = 0.0, bucket_mb: float = 25.0, optimizer: str = "sgd",
+                 betas=(0.9, 0.999), eps: float = 1e-8,
                  process_group: Optional[dist.ProcessGroup] = None):
         super().__init__()
         self.module = module
@@ -30,6 +31,8 @@ class NcclDataParallel(nn.Module):
         self.flat_param = torch.zeros(n, device=self.device)
         self.flat_grad = torch.zeros(n, device=self.device)
         self.flat_momentum = torch.zeros(n, device=self.device)
+        self.optimizer, self.betas, self.eps = optimizer, betas, eps
+        self.flat_second = torch.zeros(n, device=self.device) if optimizer == "adamw" else None
         with torch.no_grad():
             for p, off in zip(self.params, self.plan.offsets):
                 view = _view_like(self.flat_param[off:off + p.numel()], p)
@@ -62,8 +65,13 @@ class NcclDataParallel(nn.Module):
         with torch.cuda.stream(self.comm_stream):
             if self.world > 1:
                 dist.all_reduce(g, group=self.group)
-            _C.sgd_apply(g, self.flat_param[off:off + numel], self.flat_momentum[off:off + numel],
-                         1.0 / self.world, self.lr, self.momentum, self.weight_decay, self.steps == 0)
+            if self.optimizer == "adamw":
+                _C.adamw_apply(g, self.flat_param[off:off + numel], self.flat_momentum[off:off + numel],
+                               self.flat_second[off:off + numel], 1.0 / self.world, self.lr, self.betas[0],
+                               self.betas[1], self.eps, self.weight_decay, self.steps + 1)
+            else:
+                _C.sgd_apply(g, self.flat_param[off:off + numel], self.flat_momentum[off:off + numel],
+                             1.0 / self.world, self.lr, self.momentum, self.weight_decay, self.steps == 0)
             self.launches += 1
 
     def forward(self, *args, **kwargs):

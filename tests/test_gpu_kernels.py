@@ -344,3 +344,18 @@ def test_psgd_expand_paths_match_torch(n, m, r):
         hp._C.psgd_expand_sgd(P, Q, M, param, mom, 1.0, 0.1, 0.9, 1e-4, step == 0)
         torch.testing.assert_close(param, ref.data, atol=1e-4, rtol=1e-5)
     torch.testing.assert_close(M, M0 - 2 * approx, atol=2e-4, rtol=1e-5)
+
+
+def test_adamw_apply_matches_torch():
+    torch.manual_seed(0)
+    n = 50001
+    p = torch.randn(n, device="cuda")
+    ref = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    for step in range(1, 4):
+        g = torch.randn(n, device="cuda")
+        ref.grad = (g * 0.5).clone()
+        opt.step()
+        hp._C.adamw_apply(g, p, m, v, 0.5, 1e-2, 0.9, 0.999, 1e-8, 0.01, step)
+        torch.testing.assert_close(p, ref.data, atol=1e-5, rtol=1e-5)
