@@ -18,7 +18,14 @@
 #include "kernels/kernels.h"
 #include "ops/ops.h"
 #include "runtime/ddp_engine.h"
+#include "runtime/psgd_engine.h"
 #include "runtime/task_runtime.h"
+
+#define HP_CHECK_CUDA(e)                                                                      \
+  do {                                                                                        \
+    cudaError_t _e = (e);                                                                     \
+    TORCH_CHECK(_e == cudaSuccess, "hipress kernel launch failed: ", cudaGetErrorString(_e)); \
+  } while (0)
 
 namespace py = pybind11;
 using namespace hipress;
@@ -147,6 +154,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("powersgd_decode", &ops::powersgd_decode);
   m.def("psgd_project", &ops::psgd_project, py::arg("mode"), py::arg("M"), py::arg("X"),
         py::arg("owners"), py::arg("simt") = false);
+  m.def("psgd_kpad", &cuda::psgd_kpad, py::arg("k"));
   m.def("gram_schmidt", &ops::gram_schmidt, py::arg("P"), py::arg("eps") = 1e-8);
   m.def("psgd_expand_feedback", &ops::psgd_expand_feedback, py::arg("P"), py::arg("Q"), py::arg("M"),
         py::arg("grad_out"), py::arg("post_scale") = 1.0);
@@ -283,6 +291,76 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
                                            ops::status_word_for(like), current_stream(like.get_device()));
           TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
         });
+
+  // ---------------------------------------------------------------- PowerSGD step driver
+  py::class_<runtime::PsgdEngine>(m, "PsgdEngine")
+      .def(py::init([](int world, int r, const torch::Tensor& like) {
+             TORCH_CHECK(like.is_cuda(), "PsgdEngine needs a CUDA tensor to pick its device");
+             return std::make_unique<runtime::PsgdEngine>(world, r, ops::status_word_for(like));
+           }),
+           py::arg("world"), py::arg("rank_r"), py::arg("like"))
+      .def("add_matrix",
+           [](runtime::PsgdEngine& e, torch::Tensor M, torch::Tensor param, torch::Tensor momentum,
+              torch::Tensor P, torch::Tensor Q, c10::optional<torch::Tensor> Pt,
+              c10::optional<torch::Tensor> Qt, const std::vector<std::vector<torch::Tensor>>& accP,
+              const std::vector<std::vector<torch::Tensor>>& accQ) {
+             auto f32 = [](const torch::Tensor& t, const char* what) {
+               TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(), what,
+                           " must be a contiguous float32 CUDA tensor");
+               return t.data_ptr<float>();
+             };
+             TORCH_CHECK(M.dim() == 2 && P.dim() == 2 && Q.dim() == 2, "M, P, Q must be matrices");
+             runtime::PsgdMatrix d;
+             d.M = f32(M, "M");
+             d.n = M.size(0);
+             d.m = M.size(1);
+             d.param = f32(param, "param");
+             d.momentum = f32(momentum, "momentum");
+             d.numel = param.numel();
+             TORCH_CHECK(momentum.numel() == d.numel && d.numel <= d.n * d.m, "param/momentum must fit in M");
+             d.P = f32(P, "P");
+             d.Q = f32(Q, "Q");
+             TORCH_CHECK(P.size(0) == d.n && Q.size(0) == d.m && P.size(1) == Q.size(1), "P[n,r], Q[m,r] expected");
+             if (Pt) {
+               TORCH_CHECK(Pt->numel() >= 16 * cuda::psgd_kpad(d.n), "Pt too small");
+               d.Pt = f32(*Pt, "Pt");
+             }
+             if (Qt) {
+               TORCH_CHECK(Qt->numel() >= 16 * cuda::psgd_kpad(d.m), "Qt too small");
+               d.Qt = f32(*Qt, "Qt");
+             }
+             TORCH_CHECK(accP.size() == 2 && accQ.size() == 2, "accumulators are given per epoch parity");
+             for (int par = 0; par < 2; ++par) {
+               TORCH_CHECK(accP[par].size() == accQ[par].size() && accP[par].size() <= size_t(cuda::kMaxWorld),
+                           "one accumulator per rank expected");
+               for (size_t p = 0; p < accP[par].size(); ++p) {
+                 TORCH_CHECK(accP[par][p].numel() == P.numel() && accQ[par][p].numel() == Q.numel(),
+                             "accumulators must have the factors' shapes");
+                 d.accP[par][p] = f32(accP[par][p], "accP");
+                 d.accQ[par][p] = f32(accQ[par][p], "accQ");
+               }
+             }
+             return e.add_matrix(d);
+           },
+           py::arg("M"), py::arg("param"), py::arg("momentum"), py::arg("P"), py::arg("Q"), py::arg("Pt"),
+           py::arg("Qt"), py::arg("accP"), py::arg("accQ"))
+      .def("project_p",
+           [](runtime::PsgdEngine& e, int parity, int device) {
+             c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+             HP_CHECK_CUDA(e.project_p(parity, at::cuda::getCurrentCUDAStream()));
+           })
+      .def("project_q",
+           [](runtime::PsgdEngine& e, int parity, int device) {
+             c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+             HP_CHECK_CUDA(e.project_q(parity, at::cuda::getCurrentCUDAStream()));
+           })
+      .def("apply",
+           [](runtime::PsgdEngine& e, int parity, double lr, double mu, double wd, bool first, int device) {
+             c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+             HP_CHECK_CUDA(e.apply(parity, float(lr), float(mu), float(wd), first, at::cuda::getCurrentCUDAStream()));
+           })
+      .def_property_readonly("launches", &runtime::PsgdEngine::launches)
+      .def_property_readonly("matrices", &runtime::PsgdEngine::matrices);
 
   // ---------------------------------------------------------------- DDP engine
   py::class_<runtime::BucketLayout>(m, "BucketLayout")

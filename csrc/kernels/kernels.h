@@ -173,6 +173,30 @@ cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int6
                                  float* Mat, float* residual, float* grad, int64_t N, int mode,
                                  float post_scale, cudaStream_t stream);
 
+// Batched forms of the small per-matrix kernels: one launch per kPsgdBatch matrices.
+constexpr int kPsgdBatch = 32;
+struct PsgdTransposeItem {
+  const float* X;    // rows x r
+  float* Xt;         // 16 x rows_pad
+  int64_t rows, rows_pad;
+  int r;
+};
+struct PsgdGatherItem {
+  const float* src[kMaxWorld];  // every owner's accumulator (full output shape)
+  float* out;                   // rows x r
+  int64_t rows;
+  int r;
+};
+struct PsgdGsItem {
+  float* P;  // n x r, orthonormalised in place
+  int64_t n;
+  int r;
+};
+cudaError_t psgd_transpose_pad_batched(const PsgdTransposeItem* items, int count, cudaStream_t stream);
+cudaError_t psgd_owner_gather_batched(const PsgdGatherItem* items, int count, int world, float scale,
+                                      cudaStream_t stream);
+cudaError_t gram_schmidt_batched(const PsgdGsItem* items, int count, float eps, cudaStream_t stream);
+
 // Same expansion with the optimizer fused: Mat -= approx and the parameters take
 // an SGD-momentum step with g = post_scale * approx (no dense gradient is written).
 cudaError_t psgd_expand_sgd(const float* P, const float* Q, int64_t n, int64_t m, int r, float* Mat,

@@ -603,6 +603,132 @@ cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const fl
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------- batched small kernels
+// A model has tens of matrices and each needs the same handful of tiny kernels per step
+// (operand transposes, factor gathers, orthonormalisation).  Launched one by one they cost a
+// few microseconds each with the device idle in between; here one launch covers up to
+// kPsgdBatch matrices, their descriptors travelling in the kernel's parameter space.
+namespace {
+
+struct TransposeBatch {
+  int count;
+  PsgdTransposeItem item[kPsgdBatch];
+};
+__global__ void __launch_bounds__(256)
+transpose_pad_batched_kernel(TransposeBatch b) {
+  const PsgdTransposeItem it = b.item[blockIdx.y];
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < it.rows_pad; i += stride) {
+#pragma unroll
+    for (int c = 0; c < kBN; ++c)
+      it.Xt[c * it.rows_pad + i] = (i < it.rows && c < it.r) ? it.X[i * it.r + c] : 0.0f;
+  }
+}
+
+struct GatherBatch {
+  int count, world;
+  float scale;
+  PsgdGatherItem item[kPsgdBatch];
+};
+__global__ void __launch_bounds__(256)
+owner_gather_batched_kernel(GatherBatch b) {
+  const PsgdGatherItem& it = b.item[blockIdx.y];
+  const int64_t total = it.rows * it.r;
+  int64_t rpo = (it.rows + b.world - 1) / b.world;
+  if (rpo < 1) rpo = 1;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; e < total; e += stride) {
+    int owner = int((e / it.r) / rpo);
+    if (owner >= b.world) owner = b.world - 1;
+    it.out[e] = it.src[owner][e] * b.scale;
+  }
+}
+
+struct GsBatch {
+  int count;
+  float eps;
+  PsgdGsItem item[kPsgdBatch];
+};
+__global__ void __launch_bounds__(kGsThreads)
+gram_schmidt_batched_kernel(GsBatch b) {
+  __shared__ float sh[kGsThreads / 32];
+  const PsgdGsItem it = b.item[blockIdx.x];
+  float* P = it.P;
+  const int64_t n = it.n;
+  const int r = it.r;
+  for (int j = 0; j < r; ++j) {
+    float ss = 0.f;
+    for (int64_t i = threadIdx.x; i < n; i += kGsThreads) {
+      const float v = P[i * r + j];
+      ss += v * v;
+    }
+    const float inv = 1.0f / (sqrtf(block_sum(ss, sh)) + b.eps);
+    for (int64_t i = threadIdx.x; i < n; i += kGsThreads) P[i * r + j] *= inv;
+    __syncthreads();
+    for (int c = j + 1; c < r; ++c) {
+      float dot = 0.f;
+      for (int64_t i = threadIdx.x; i < n; i += kGsThreads) dot += P[i * r + j] * P[i * r + c];
+      dot = block_sum(dot, sh);
+      for (int64_t i = threadIdx.x; i < n; i += kGsThreads) P[i * r + c] -= dot * P[i * r + j];
+      __syncthreads();
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t psgd_transpose_pad_batched(const PsgdTransposeItem* items, int count, cudaStream_t stream) {
+  for (int base = 0; base < count; base += kPsgdBatch) {
+    TransposeBatch b{};
+    b.count = count - base < kPsgdBatch ? count - base : kPsgdBatch;
+    int64_t max_rows = 1;
+    for (int i = 0; i < b.count; ++i) {
+      b.item[i] = items[base + i];
+      if (b.item[i].r < 1 || b.item[i].r > kBN || b.item[i].rows_pad < b.item[i].rows) return cudaErrorInvalidValue;
+      if (b.item[i].rows_pad > max_rows) max_rows = b.item[i].rows_pad;
+    }
+    int64_t gx = (max_rows + 255) / 256;
+    if (gx > 148) gx = 148;
+    transpose_pad_batched_kernel<<<dim3(unsigned(gx), unsigned(b.count), 1), 256, 0, stream>>>(b);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t psgd_owner_gather_batched(const PsgdGatherItem* items, int count, int world, float scale,
+                                      cudaStream_t stream) {
+  if (world < 1 || world > kMaxWorld) return cudaErrorInvalidValue;
+  for (int base = 0; base < count; base += kPsgdBatch) {
+    GatherBatch b{};
+    b.count = count - base < kPsgdBatch ? count - base : kPsgdBatch;
+    b.world = world;
+    b.scale = scale;
+    int64_t max_total = 1;
+    for (int i = 0; i < b.count; ++i) {
+      b.item[i] = items[base + i];
+      const int64_t t = b.item[i].rows * b.item[i].r;
+      if (t > max_total) max_total = t;
+    }
+    int64_t gx = (max_total + 255) / 256;
+    if (gx > 148) gx = 148;
+    owner_gather_batched_kernel<<<dim3(unsigned(gx), unsigned(b.count), 1), 256, 0, stream>>>(b);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t gram_schmidt_batched(const PsgdGsItem* items, int count, float eps, cudaStream_t stream) {
+  for (int base = 0; base < count; base += kPsgdBatch) {
+    GsBatch b{};
+    b.count = count - base < kPsgdBatch ? count - base : kPsgdBatch;
+    b.eps = eps;
+    for (int i = 0; i < b.count; ++i) {
+      b.item[i] = items[base + i];
+      if (b.item[i].n < 1 || b.item[i].r < 1 || b.item[i].r > kBN) return cudaErrorInvalidValue;
+    }
+    gram_schmidt_batched_kernel<<<b.count, kGsThreads, 0, stream>>>(b);
+  }
+  return cudaGetLastError();
+}
+
 cudaError_t gram_schmidt(float* P, int64_t n, int r, float eps, cudaStream_t stream) {
   if (n < 1 || r < 1 || r > kBN) return cudaErrorInvalidValue;
   gram_schmidt_kernel<<<1, kGsThreads, 0, stream>>>(P, n, r, eps);

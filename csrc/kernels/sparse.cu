@@ -123,6 +123,32 @@ __device__ __forceinline__ void hist_flush(unsigned int* sh, unsigned int* gh) {
   }
 }
 
+// Visit every element of [begin, end) once with f(value): 16-byte loads, four in flight per
+// thread, scalar handling of an unaligned base or a ragged end.  `begin` is a multiple of the
+// tile size, so the vector path applies whenever R itself is 16-byte aligned.
+template <typename F>
+__device__ __forceinline__ void for_each_value(const float* __restrict__ R, int64_t begin, int64_t end, F f) {
+  if ((reinterpret_cast<uintptr_t>(R + begin) & 15) == 0) {
+    const int64_t nvec = (end - begin) >> 2;
+    const float4* v = reinterpret_cast<const float4*>(R + begin);
+    int64_t i = threadIdx.x;
+    for (; i + 3 * kThreads < nvec; i += 4 * kThreads) {
+      const float4 a = v[i], b = v[i + kThreads], c = v[i + 2 * kThreads], d = v[i + 3 * kThreads];
+      f(a.x); f(a.y); f(a.z); f(a.w);
+      f(b.x); f(b.y); f(b.z); f(b.w);
+      f(c.x); f(c.y); f(c.z); f(c.w);
+      f(d.x); f(d.y); f(d.z); f(d.w);
+    }
+    for (; i < nvec; i += kThreads) {
+      const float4 a = v[i];
+      f(a.x); f(a.y); f(a.z); f(a.w);
+    }
+    for (int64_t j = begin + (nvec << 2) + threadIdx.x; j < end; j += kThreads) f(R[j]);
+  } else {
+    for (int64_t j = begin + threadIdx.x; j < end; j += kThreads) f(R[j]);
+  }
+}
+
 // ---- sample rounds
 template <int ROUND>
 __global__ void __launch_bounds__(kThreads)
@@ -215,11 +241,11 @@ trim_round_kernel(const float* __restrict__ R, int64_t n, int64_t chunk, unsigne
   __syncthreads();
   const int64_t begin = int64_t(blockIdx.x) * chunk;
   const int64_t end = begin + chunk < n ? begin + chunk : n;
-  for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
-    const uint32_t key = abs_key(R[i]);
+  for_each_value(R, begin, end, [&](float x) {
+    const uint32_t key = abs_key(x);
     if (key > thr_key && prefix_matches(key, ROUND, prefix))
       atomicAdd(&sh[digit_of(key, ROUND)], 1u);
-  }
+  });
   hist_flush(sh, s->thist[ROUND]);
 }
 
@@ -250,11 +276,11 @@ recount_kernel(const float* __restrict__ R, int64_t n, int64_t chunk, unsigned i
   const int64_t begin = int64_t(blockIdx.x) * chunk;
   const int64_t end = begin + chunk < n ? begin + chunk : n;
   unsigned int g = 0, e = 0;
-  for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
-    const uint32_t key = abs_key(R[i]);
+  for_each_value(R, begin, end, [&](float x) {
+    const uint32_t key = abs_key(x);
     g += key > cut;
     e += key == cut;
-  }
+  });
   atomicAdd(&c_gt, g);
   atomicAdd(&c_eq, e);
   __syncthreads();
@@ -318,7 +344,23 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
   const int64_t begin = int64_t(blockIdx.x) * chunk;
   const int64_t end = begin + chunk < n ? begin + chunk : n;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int64_t base = begin; base < end; base += kTile) {
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(R + begin) & 15) == 0;
+  for (int64_t super = begin; super < end; super += 4 * kTile) {
+    // Look ahead over four tiles with all loads in flight at once: 99.9 % of the data is below
+    // the cut, and a block that finds nothing skips 4096 elements for the price of one barrier.
+    if (vec_ok && super + 4 * kTile <= end) {
+      int hit = 0;
+      float4 q[4];
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        q[t] = *reinterpret_cast<const float4*>(R + super + t * kTile + int64_t(threadIdx.x) * 4);
+#pragma unroll
+      for (int t = 0; t < 4; ++t)
+        hit |= (abs_key(q[t].x) >= cut) | (abs_key(q[t].y) >= cut) | (abs_key(q[t].z) >= cut) |
+               (abs_key(q[t].w) >= cut);
+      if (!__syncthreads_or(hit)) continue;
+    }
+  for (int64_t base = super; base < end && base < super + 4 * kTile; base += kTile) {
     // thread owns 4 consecutive elements so that output order is index order
     const int64_t e0 = base + int64_t(threadIdx.x) * 4;
     float v[4];
@@ -394,6 +436,7 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
       run_e += te;
     }
     __syncthreads();
+  }
   }
   publish_when_grid_done(dst);
 }

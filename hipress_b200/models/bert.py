@@ -62,11 +62,22 @@ class BertForMaskedLM(nn.Module):
             h = self.head_ln(F.gelu(self.head_dense(x)))
             return F.linear(h, self.tok.weight, self.head_bias)
         # score only the masked positions (labels == -100 elsewhere)
-        sel = labels.view(-1) >= 0
-        h = x.view(b * s, -1)[sel]
+        flat = labels.view(-1)
+        cap = getattr(self, "masked_capacity", None)
+        if cap:
+            # fixed-shape selection (no host round trip, so the step can be captured in a CUDA
+            # graph): the `cap` positions picked contain every masked one as long as
+            # cap >= their count; the rest carry label -100 and are ignored by the loss
+            idx = torch.topk((flat >= 0).to(torch.float32), min(int(cap), flat.numel()), sorted=False).indices
+            h = x.view(b * s, -1).index_select(0, idx)
+            target = flat.index_select(0, idx)
+        else:
+            sel = flat >= 0
+            h = x.view(b * s, -1)[sel]
+            target = flat[sel]
         h = self.head_ln(F.gelu(self.head_dense(h)))
         logits = F.linear(h, self.tok.weight, self.head_bias)
-        return F.cross_entropy(logits.float(), labels.view(-1)[sel])
+        return F.cross_entropy(logits.float(), target, ignore_index=-100)
 
 
 def bert_large() -> BertForMaskedLM:

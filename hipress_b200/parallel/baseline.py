@@ -47,11 +47,14 @@ class NcclDataParallel(nn.Module):
         self.comm_stream = torch.cuda.Stream(device=self.device)
         self.steps = 0
         self.launches = 0
+        self.hooks_enabled = True
         for i, p in enumerate(self.params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
 
     def _make_hook(self, index: int):
         def hook(_p):
+            if not self.hooks_enabled:
+                return
             b = self.plan.param_bucket[index]
             self.pending[b] -= 1
             if self.pending[b] == 0:
@@ -76,6 +79,12 @@ class NcclDataParallel(nn.Module):
 
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
+
+    def begin_step(self) -> None:
+        """Nothing to arm: buckets are counted down by the hooks and flushed by ``step``."""
+
+    def grad_buffers(self):
+        return [self.flat_grad]
 
     def step(self) -> None:
         for b, left in enumerate(self.pending):

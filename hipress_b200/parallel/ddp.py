@@ -196,6 +196,7 @@ class CompressedDataParallel(nn.Module):
             self.engine.set_sgd(lr, momentum, weight_decay, fused_sgd)
 
         self._in_step = False
+        self.hooks_enabled = True
         self._hooks = []
         for i, p in enumerate(self.params):
             self._hooks.append(p.register_post_accumulate_grad_hook(self._make_hook(i)))
@@ -204,7 +205,7 @@ class CompressedDataParallel(nn.Module):
     # ------------------------------------------------------------------ hooks
     def _make_hook(self, index: int):
         def hook(_param):
-            if self._in_step:
+            if self._in_step and self.hooks_enabled:
                 self.engine.grad_ready(index, self._dev_index)
         return hook
 
@@ -231,6 +232,10 @@ class CompressedDataParallel(nn.Module):
     def zero_grad(self, set_to_none: bool = False) -> None:  # noqa: D401
         """Gradients live in the flat buffer and are views: they are zeroed, never dropped."""
         self.flat_grad.zero_()
+
+    def grad_buffers(self):
+        """The buffers a backward pass accumulates into (saved and restored around a graph capture)."""
+        return [self.flat_grad]
 
     def set_lr(self, lr: float) -> None:
         self.lr = lr

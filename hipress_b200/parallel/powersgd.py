@@ -96,6 +96,24 @@ class PowerSGDDataParallel(nn.Module):
             raise ValueError("symmetric buffer too small")
         self.emulated = emulated
 
+        # ---- native step driver: batched small kernels + one GEMM / expand launch per matrix
+        self.engine = _C.PsgdEngine(self.world, self.r, self.flat_M)
+        tsize = sum(16 * (_C.psgd_kpad(n) + _C.psgd_kpad(m)) for n, m in self.shapes)
+        self.operand_scratch = torch.zeros(max(tsize, 16), device=dev)
+        cur = 0
+        for i, p in enumerate(self.mats):
+            n, m = self.shapes[i]
+            off = self.offsets[i]
+            pt = self.operand_scratch[cur:cur + 16 * _C.psgd_kpad(n)]
+            cur += pt.numel()
+            qt = self.operand_scratch[cur:cur + 16 * _C.psgd_kpad(m)]
+            cur += qt.numel()
+            self.engine.add_matrix(
+                self._mat(i), self.flat_param[off:off + p.numel()], self.flat_momentum[off:off + p.numel()],
+                self.P[i], self.Q[i], pt, qt,
+                [[self._acc(r, i, 0, par) for r in range(self.world)] for par in (0, 1)],
+                [[self._acc(r, i, 1, par) for r in range(self.world)] for par in (0, 1)])
+
         # ---- vectors: dense P2P average + fused SGD through the engine (one bucket)
         self.vec_engine = None
         if self.vecs:
@@ -126,6 +144,7 @@ class PowerSGDDataParallel(nn.Module):
         self.epoch = 0
         self.steps = 0
         self.launches = 0
+        self.hooks_enabled = True      # no hooks here; kept for the common wrapper interface
 
     def _attach_vec(self, sym: SymmetricMemory) -> None:
         self.vec_symmetric = sym
@@ -154,13 +173,12 @@ class PowerSGDDataParallel(nn.Module):
     def phase_project_p(self) -> None:
         self.epoch += 1
         par = self.epoch & 1
-        for i in range(len(self.mats)):
-            _C.psgd_project(0, self._mat(i), self.Q[i], [self._acc(r, i, 0, par) for r in range(self.world)], False)
+        self.engine.project_p(par, self.device.index)
         _C.signal_flags(self.symmetric.buf, self.flag_off["P"], self.epoch, self.device.index)
         if self.vec_engine is not None:
             self.vec_engine.begin_step()
             self.vec_engine.bucket_ready(0, self.device.index)
-        self.launches += 2 * len(self.mats) + 1
+        self.launches += 1
 
     def phase_project_q(self) -> None:
         par = self.epoch & 1
@@ -168,29 +186,25 @@ class PowerSGDDataParallel(nn.Module):
         # every rank has finished reading the other parity's accumulators: clear them for the next step
         other = self.sym_base + (1 - par) * self.acc_bytes
         self.symmetric.tensor(self.rank, other, self.acc_bytes, "uint8").zero_()
-        scale = 1.0 / self.world
-        for i in range(len(self.mats)):
-            _C.psgd_owner_gather([self._acc(r, i, 0, par) for r in range(self.world)], self.P[i], scale)
-            _C.gram_schmidt(self.P[i], 1e-8)
-            _C.psgd_project(1, self._mat(i), self.P[i], [self._acc(r, i, 1, par) for r in range(self.world)], False)
+        self.engine.project_q(par, self.device.index)
         _C.signal_flags(self.symmetric.buf, self.flag_off["Q"], self.epoch, self.device.index)
-        self.launches += 4 * len(self.mats) + 2
+        self.launches += 3
 
     def phase_apply(self) -> None:
         par = self.epoch & 1
         _C.wait_flags(self.symmetric.buf, self.flag_off["Q"], self.epoch, self.timeout, self.flat_M)
-        scale = 1.0 / self.world
-        for i, p in enumerate(self.mats):
-            off = self.offsets[i]
-            _C.psgd_owner_gather([self._acc(r, i, 1, par) for r in range(self.world)], self.Q[i], scale)
-            _C.psgd_expand_sgd(self.P[i], self.Q[i], self._mat(i), self.flat_param[off:off + p.numel()],
-                               self.flat_momentum[off:off + p.numel()], 1.0, self.lr, self.momentum,
-                               self.weight_decay, self.steps == 0)
+        self.engine.apply(par, self.lr, self.momentum, self.weight_decay, self.steps == 0, self.device.index)
         if self.vec_engine is not None:
             self.vec_engine.finish_step(self.device.index)
             self.vec_grad.zero_()
-        self.launches += 2 * len(self.mats) + 1
+        self.launches += 1
         self.steps += 1
+
+    def begin_step(self) -> None:
+        """Nothing to arm: the whole exchange runs in ``step``."""
+
+    def grad_buffers(self):
+        return [self.flat_M] + ([self.vec_grad] if self.vecs else [])
 
     def step(self) -> None:
         self.phase_project_p()
@@ -223,6 +237,7 @@ class PowerSGDDataParallel(nn.Module):
     def metrics(self) -> Dict[str, float]:
         dense = sum(n * m for n, m in self.shapes) * 4
         wire = sum((n + m) * self.r for n, m in self.shapes) * 4
-        return {"kernel_launches": self.launches + (self.vec_engine.launches if self.vec_engine else 0),
+        return {"kernel_launches": self.launches + self.engine.launches
+                + (self.vec_engine.launches if self.vec_engine else 0),
                 "steps": self.steps, "matrices": len(self.mats), "dense_bytes_per_step": dense,
                 "factor_bytes_per_step": wire, "compression_ratio": dense / wire if wire else float("inf")}
