@@ -40,6 +40,8 @@ def parse():
     ap.add_argument("--batch", type=int, default=None, help="per-GPU batch")
     ap.add_argument("--engine-workers", type=int, default=-1,
                     help="engine worker threads (0 = the hook thread issues the kernels itself, -1 = auto)")
+    ap.add_argument("--bucket-mb", type=float, default=None,
+                    help="gradient bucket size (default 25; 128 for the sparse codecs, whose per-bucket cost is a dozen launches)")
     ap.add_argument("--cuda-graph", type=int, default=1,
                     help="1 = replay forward+backward from one CUDA graph (ours only), 0 = eager")
     ap.add_argument("--dgc-start-step", type=int, default=400,
@@ -100,22 +102,23 @@ class OurTrainer:
         net.train()
         # VGG without normalisation layers diverges at 0.1 on random data
         self.lr = {"resnet50": 0.1, "vgg19": 0.01, "bert_large": 1e-4}[args.model]
+        self.bucket_mb = args.bucket_mb or (128.0 if self.algorithm in ("dgc", "graddrop") else 25.0)
         if self.algorithm == "powersgd":
             from hipress_b200.parallel.powersgd import PowerSGDDataParallel
             self.model = PowerSGDDataParallel(net, rank_r=4, lr=self.lr, momentum=0.9)
         elif self.algorithm == "dgc":
             from hipress_b200.parallel.dgc import DGCDataParallel
             # measured in the steady state: the 400-step sparsity warm-up is skipped, not shortened
-            self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4,
+            self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4, bucket_mb=self.bucket_mb,
                                          start_step=args.dgc_start_step)
         elif self.algorithm == "nccl":
             from hipress_b200.parallel.baseline import NcclDataParallel
-            self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9,
+            self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9, bucket_mb=self.bucket_mb,
                                           optimizer="adamw" if args.model == "bert_large" else "sgd",
                                           weight_decay=0.01 if args.model == "bert_large" else 0.0)
         else:
             cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
-                                    threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=25.0,
+                                    threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=self.bucket_mb,
                                     num_workers=args.engine_workers)
             self.model = CompressedDataParallel(net, cfg, lr=self.lr, momentum=0.9, weight_decay=0.0, fused_sgd=True)
 
@@ -341,7 +344,7 @@ def run(args):
         "data": "synthetic", "impl": args.impl,
         "config": {"model": args.model, "global_batch": global_batch, "per_gpu_batch": batch,
                    "seq_len": 128 if args.model == "bert_large" else None,
-                   "parallelism": f"dp{world}", "algorithm": alg, "bucket_mb": 25,
+                   "parallelism": f"dp{world}", "algorithm": alg, "bucket_mb": getattr(trainer, "bucket_mb", 25),
                    "optimizer": {"resnet50": "sgd momentum 0.9 lr 0.1", "vgg19": "sgd momentum 0.9 lr 0.01",
                                  "bert_large": "adamw lr 1e-4 (fused)"}[args.model],
                    "cuda_graph": getattr(trainer, "graph_note", "off"),

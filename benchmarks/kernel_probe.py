@@ -47,7 +47,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="terngrad",
                     choices=["terngrad", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q",
-                             "psgd_expand", "sgd"])
+                             "psgd_expand", "sgd", "adamw", "terngrad_unpack_apply", "bn_fwd", "bn_bwd"])
     ap.add_argument("--mb", type=float, default=64.0)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--world", type=int, default=8, help="payload count for the unpack kernels")
@@ -105,6 +105,49 @@ def main():
             out = torch.zeros(rows * cols, device=dev)
             fn = lambda: ops.psgd_expand_feedback(P, Q, M, out)
             traffic = rows * cols * 12
+    elif k == "terngrad_unpack_apply":
+        # what a training step runs per bucket: decode `world` payloads, average, fused SGD step,
+        # zeros left in the gradient bucket
+        import hipress_b200 as hp
+        from hipress_b200.parallel import SymmetricMemory
+        cfg = dict(rank=0, world=1, device=0, codec="terngrad", bitwidth=2, enable_random=1, error_feedback=1,
+                   clear_grad=1, num_workers=0)
+        eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
+        sym = SymmetricMemory(eng.symmetric_bytes, dev, None)
+        p, m = torch.randn(n, device=dev), torch.zeros(n, device=dev)
+        eng.set_buffers(g, r, p, m, None, None)
+        eng.set_symmetric(sym.buf)
+        eng.set_sgd(0.1, 0.9, 0.0, True)
+
+        def fn():
+            eng.begin_step()
+            eng.bucket_ready(0, 0)
+            eng.finish_step(0)
+        traffic = n * (8 + 8 + 4 + 0.25) + n * (0.25 + 4 + 16)   # compress (with min/max pass) + unpack/apply
+    elif k in ("bn_fwd", "bn_bwd"):
+        # one ResNet-50 stage-1 activation: [N, 256, 56, 56] bf16 channels-last, --mb = its size
+        import hipress_b200 as hp
+        c = 256
+        imgs = max(1, int(args.mb * (1 << 20) / 2 / (c * 56 * 56)))
+        shape = (imgs, c, 56, 56)
+        x = torch.randn(shape, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        res = torch.randn(shape, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        w, b = torch.ones(c, device=dev), torch.zeros(c, device=dev)
+        y, stats = hp._C.bn_forward(x, res, w, b, None, None, None, 0.1, 1e-5, True)
+        nbytes = x.numel() * 2
+        if k == "bn_fwd":
+            fn = lambda: hp._C.bn_forward(x, res, w, b, None, None, None, 0.1, 1e-5, True)
+            traffic = nbytes * 4          # stats: read x; apply: read x, residual, write y
+        else:
+            dy = torch.randn(shape, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+            fn = lambda: hp._C.bn_backward(dy, x, y, w, stats, True, True)
+            traffic = nbytes * 8          # reduce: dy, x, y; elemt: dy, x, y -> dx, dres
+        n = x.numel()
+    elif k == "adamw":
+        import hipress_b200 as hp
+        p, m, v = torch.randn(n, device=dev), torch.zeros(n, device=dev), torch.zeros(n, device=dev)
+        fn = lambda: hp._C.adamw_apply(g, p, m, v, 0.5, 1e-4, 0.9, 0.999, 1e-8, 0.01, 3, True)
+        traffic = n * 32
     else:
         import hipress_b200 as hp
         p, m = torch.randn(n, device=dev), torch.zeros(n, device=dev)

@@ -76,6 +76,7 @@ runtime::EngineConfig config_from(const py::dict& d) {
   c.flag_timeout_ns = uint64_t(get("flag_timeout_s", 20.0) * 1e9);
   c.num_workers = get("num_workers", 1);
   c.defer_recv = get("defer_recv", 0);
+  c.clear_grad = get("clear_grad", 0);
   c.momentum_correction = get("momentum_correction", 0);
   c.dgc_momentum = get("dgc_momentum", 0.9f);
   c.dgc_clip = get("dgc_clip", 0.0f);
@@ -154,6 +155,16 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("powersgd_decode", &ops::powersgd_decode);
   m.def("psgd_project", &ops::psgd_project, py::arg("mode"), py::arg("M"), py::arg("X"),
         py::arg("owners"), py::arg("simt") = false);
+  m.def("bn_supported", &ops::bn_supported, py::arg("x"));
+  m.def("bn_forward", &ops::bn_forward, py::arg("x"), py::arg("residual"), py::arg("weight"), py::arg("bias"),
+        py::arg("running_mean"), py::arg("running_var"), py::arg("num_batches"), py::arg("momentum"),
+        py::arg("eps"), py::arg("relu"));
+  m.def("bn_backward", &ops::bn_backward, py::arg("dy"), py::arg("x"), py::arg("y"), py::arg("weight"),
+        py::arg("stats"), py::arg("relu"), py::arg("want_dres"));
+  m.def("maxpool_supported", &ops::maxpool_supported, py::arg("x"));
+  m.def("maxpool3x3s2_forward", &ops::maxpool3x3s2_forward, py::arg("x"));
+  m.def("maxpool3x3s2_backward", &ops::maxpool3x3s2_backward, py::arg("dy"), py::arg("idx"), py::arg("h"),
+        py::arg("w"));
   m.def("psgd_kpad", &cuda::psgd_kpad, py::arg("k"));
   m.def("gram_schmidt", &ops::gram_schmidt, py::arg("P"), py::arg("eps") = 1e-8);
   m.def("psgd_expand_feedback", &ops::psgd_expand_feedback, py::arg("P"), py::arg("Q"), py::arg("M"),
@@ -168,7 +179,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   // fused SGD-momentum over flat fp32 buffers
   m.def("sgd_apply",
         [](torch::Tensor grad, torch::Tensor param, torch::Tensor momentum, double scale, double lr,
-           double mu, double wd, bool first_step) {
+           double mu, double wd, bool first_step, bool clear_grad) {
           TORCH_CHECK(grad.is_cuda() && param.is_cuda() && momentum.is_cuda(), "CUDA tensors expected");
           TORCH_CHECK(grad.numel() == param.numel() && grad.numel() == momentum.numel(), "size mismatch");
           c10::cuda::CUDAGuard guard(grad.device());
@@ -179,15 +190,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           a.mu = float(mu);
           a.weight_decay = float(wd);
           a.first_step = first_step ? 1 : 0;
+          a.clear_grad = clear_grad ? 1 : 0;
           cudaError_t e = cuda::sgd_apply_dense(grad.data_ptr<float>(), float(scale), a, grad.numel(),
                                                 current_stream(grad.get_device()));
           TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
-        });
+        },
+        py::arg("grad"), py::arg("param"), py::arg("momentum"), py::arg("scale"), py::arg("lr"),
+        py::arg("mu"), py::arg("weight_decay"), py::arg("first_step"), py::arg("clear_grad") = false);
 
   // fused AdamW (decoupled weight decay, bias correction) over flat fp32 buffers; step is 1-based
   m.def("adamw_apply",
         [](torch::Tensor grad, torch::Tensor param, torch::Tensor exp_avg, torch::Tensor exp_avg_sq,
-           double scale, double lr, double beta1, double beta2, double eps, double wd, int64_t step) {
+           double scale, double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+           bool clear_grad) {
           TORCH_CHECK(grad.is_cuda() && param.is_cuda() && exp_avg.is_cuda() && exp_avg_sq.is_cuda(),
                       "CUDA tensors expected");
           TORCH_CHECK(grad.numel() == param.numel() && grad.numel() == exp_avg.numel() &&
@@ -203,10 +218,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           a.eps = float(eps);
           a.weight_decay = float(wd);
           a.step = int(step);
+          a.clear_grad = clear_grad ? 1 : 0;
           cudaError_t e = cuda::adamw_apply_dense(grad.data_ptr<float>(), float(scale), a, grad.numel(),
                                                   current_stream(grad.get_device()));
           TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
-        });
+        },
+        py::arg("grad"), py::arg("param"), py::arg("exp_avg"), py::arg("exp_avg_sq"), py::arg("scale"),
+        py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"),
+        py::arg("step"), py::arg("clear_grad") = false);
 
   // LCG draws, for checking the generator against the reference's
   m.def("lcg_draws", [](uint32_t seed, int count) {

@@ -74,21 +74,45 @@ dgc_mask_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restr
   }
 }
 
+__device__ __forceinline__ void adamw_one(const AdamWApply& a, float bc1, float rsqrt_bc2, float g,
+                                          float& p, float& m, float& v) {
+  p -= a.lr * a.weight_decay * p;  // decoupled weight decay
+  m = a.beta1 * m + (1.0f - a.beta1) * g;
+  v = a.beta2 * v + (1.0f - a.beta2) * g * g;
+  const float denom = sqrtf(v) * rsqrt_bc2 + a.eps;
+  p -= (a.lr / bc1) * (m / denom);
+}
+
+// VEC: all four arrays 16-byte aligned; four elements per thread and iteration.
+template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
-adamw_kernel(const float* __restrict__ grad, float scale, AdamWApply a, int64_t n) {
+adamw_kernel(float* __restrict__ grad, float scale, AdamWApply a, int64_t n) {
   const float bc1 = 1.0f - powf(a.beta1, float(a.step));
-  const float bc2 = 1.0f - powf(a.beta2, float(a.step));
+  const float rsqrt_bc2 = 1.0f / sqrtf(1.0f - powf(a.beta2, float(a.step)));
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const float g = grad[i] * scale;
-    float p = a.param[i];
-    p -= a.lr * a.weight_decay * p;  // decoupled weight decay
-    const float m = a.beta1 * a.exp_avg[i] + (1.0f - a.beta1) * g;
-    const float v = a.beta2 * a.exp_avg_sq[i] + (1.0f - a.beta2) * g * g;
+  const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nv = VEC ? (n >> 2) : 0;
+  for (int64_t i = tid; i < nv; i += stride) {
+    const float4 g4 = reinterpret_cast<const float4*>(grad)[i];
+    const float4 p4 = reinterpret_cast<const float4*>(a.param)[i];
+    const float4 m4 = reinterpret_cast<const float4*>(a.exp_avg)[i];
+    const float4 v4 = reinterpret_cast<const float4*>(a.exp_avg_sq)[i];
+    float g[4] = {g4.x, g4.y, g4.z, g4.w}, p[4] = {p4.x, p4.y, p4.z, p4.w};
+    float m[4] = {m4.x, m4.y, m4.z, m4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) adamw_one(a, bc1, rsqrt_bc2, g[k] * scale, p[k], m[k], v[k]);
+    reinterpret_cast<float4*>(a.exp_avg)[i] = make_float4(m[0], m[1], m[2], m[3]);
+    reinterpret_cast<float4*>(a.exp_avg_sq)[i] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(a.param)[i] = make_float4(p[0], p[1], p[2], p[3]);
+    if (a.clear_grad) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int64_t i = (nv << 2) + tid; i < n; i += stride) {
+    float p = a.param[i], m = a.exp_avg[i], v = a.exp_avg_sq[i];
+    adamw_one(a, bc1, rsqrt_bc2, grad[i] * scale, p, m, v);
     a.exp_avg[i] = m;
     a.exp_avg_sq[i] = v;
-    const float denom = sqrtf(v) / sqrtf(bc2) + a.eps;
-    a.param[i] = p - (a.lr / bc1) * (m / denom);
+    a.param[i] = p;
+    if (a.clear_grad) grad[i] = 0.f;
   }
 }
 
@@ -115,11 +139,15 @@ cudaError_t dgc_mask(const uint8_t* payload, int64_t payload_capacity, float* u,
   return cudaGetLastError();
 }
 
-cudaError_t adamw_apply_dense(const float* grad, float scale, const AdamWApply& apply, int64_t n,
+cudaError_t adamw_apply_dense(float* grad, float scale, const AdamWApply& apply, int64_t n,
                               cudaStream_t stream) {
   if (n <= 0 || !apply.param || !apply.exp_avg || !apply.exp_avg_sq || apply.step < 1)
     return cudaErrorInvalidValue;
-  adamw_kernel<<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(grad, scale, apply, n);
+  const bool vec = ((reinterpret_cast<uintptr_t>(grad) | reinterpret_cast<uintptr_t>(apply.param) |
+                     reinterpret_cast<uintptr_t>(apply.exp_avg) |
+                     reinterpret_cast<uintptr_t>(apply.exp_avg_sq)) & 15) == 0;
+  if (vec) adamw_kernel<true><<<grid_for((n + 3) >> 2, 148 * 8), kThreads, 0, stream>>>(grad, scale, apply, n);
+  else adamw_kernel<false><<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(grad, scale, apply, n);
   return cudaGetLastError();
 }
 

@@ -46,6 +46,10 @@ struct SgdApply {
   float* momentum = nullptr;
   float lr = 0.f, mu = 0.f, weight_decay = 0.f;
   int first_step = 0;  // buf = g on the first step (torch.optim.SGD semantics)
+  // The caller does not keep the dense gradient: the kernel that applies the update writes
+  // zeros where it would have written the gradient, which leaves the buffer ready for the next
+  // backward pass and saves the separate clearing pass.
+  int clear_grad = 0;
 };
 
 // Error codes written to a device status word by bounded waits / bounds checks.
@@ -136,10 +140,41 @@ struct AdamWApply {
   float* exp_avg_sq = nullptr;
   float lr = 0.f, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0.f;
   int step = 1;  // 1-based
+  int clear_grad = 0;  // write zeros over grad after reading it (see SgdApply::clear_grad)
 };
 // Fused AdamW (decoupled weight decay, bias correction) on g = scale*grad.
-cudaError_t adamw_apply_dense(const float* grad, float scale, const AdamWApply& apply, int64_t n,
+cudaError_t adamw_apply_dense(float* grad, float scale, const AdamWApply& apply, int64_t n,
                               cudaStream_t stream);
+
+// ---------------------------------------------------------------- batch normalisation
+// Training-mode batch norm over channels-last bf16 activations ([rows][channels], rows =
+// batch x height x width), fused with an optional residual add and ReLU.  channels/8 must be a
+// power of two up to 32 or a multiple of 32 (bn_supported).  Scratch owned by the caller:
+// partial = 2*bn_partial_elems floats.
+constexpr int kBnMaxRowBlocks = 1184;
+bool bn_supported(int64_t rows, int channels);
+int64_t bn_partial_elems(int64_t rows, int channels);
+// y = act(bn(x) [+ residual]); writes mean, invstd, ab = (gamma*invstd, beta - mean*gamma*invstd)
+// per channel and updates the running statistics (unbiased variance) when given.
+cudaError_t bn_forward(const void* x, const void* residual, void* y, int64_t rows, int channels,
+                       const float* gamma, const float* beta, float* running_mean, float* running_var,
+                       long long* num_batches, float momentum, float eps, int relu, float* mean,
+                       float* invstd, float* ab, float* partial, cudaStream_t stream);
+// dy' = relu ? dy*(y > 0) : dy.  dx = d loss / d x; dres (optional) = dy'; dgamma, dbeta fp32;
+// coef = 4*channels floats of scratch.
+cudaError_t bn_backward(const void* dy, const void* x, const void* y, void* dx, void* dres, int64_t rows,
+                        int channels, const float* gamma, const float* mean, const float* invstd,
+                        int relu, float* dgamma, float* dbeta, float* coef, float* partial,
+                        cudaStream_t stream);
+
+// ---------------------------------------------------------------- max pooling
+// 3x3, stride 2, padding 1 over channels-last bf16 [n][h][w][c] (c a multiple of 8).  The forward
+// writes y [n][ho][wo][c] (ho = (h-1)/2 + 1) and one byte per output element: the winning window
+// position kh*3 + kw.  The backward gathers, without atomics.
+cudaError_t maxpool3x3s2_forward(const void* x, void* y, uint8_t* idx, int n, int h, int w, int c,
+                                 cudaStream_t stream);
+cudaError_t maxpool3x3s2_backward(const void* dy, const uint8_t* idx, void* dx, int n, int h, int w, int c,
+                                  cudaStream_t stream);
 
 // ---------------------------------------------------------------- PowerSGD
 // All matrices row-major fp32.  Mat is n x m, P is n x r, Q is m x r, r <= 16.

@@ -61,19 +61,20 @@ sgd_dense_kernel(float* __restrict__ grad, float scale, SgdApply a, int64_t n) {
         bb[k] = a.first_step ? d : a.mu * bb[k] + d;
         pp[k] -= a.lr * bb[k];
       }
-      reinterpret_cast<float4*>(grad)[i] = make_float4(gg[0], gg[1], gg[2], gg[3]);
+      reinterpret_cast<float4*>(grad)[i] =
+          a.clear_grad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(gg[0], gg[1], gg[2], gg[3]);
       reinterpret_cast<float4*>(a.momentum)[i] = make_float4(bb[0], bb[1], bb[2], bb[3]);
       reinterpret_cast<float4*>(a.param)[i] = make_float4(pp[0], pp[1], pp[2], pp[3]);
     }
     for (int64_t i = (nv << 2) + tid; i < n; i += stride) {
       const float g = grad[i] * scale;
-      grad[i] = g;
+      grad[i] = a.clear_grad ? 0.f : g;
       sgd_update(a, i, g);
     }
   } else {
     for (int64_t i = tid; i < n; i += stride) {
       const float g = grad[i] * scale;
-      grad[i] = g;
+      grad[i] = a.clear_grad ? 0.f : g;
       sgd_update(a, i, g);
     }
   }

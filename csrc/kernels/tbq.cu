@@ -85,13 +85,13 @@ template <bool APPLY>
 __global__ void __launch_bounds__(kUnpackThreads)
 tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
                       float post_scale, SgdApply apply) {
-  __shared__ __align__(16) float lut[256 * 4];
-  for (int v = threadIdx.x; v < 256; v += blockDim.x) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) lut[lut_row(uint32_t(v)) * 4 + j] = tbq_dequant((uint32_t(v) >> (2 * j)) & 3u, thr);
-  }
+  // nibble -> 2 decoded values; one 128-byte table shared by all ranks (see unpack_lut.cuh)
+  __shared__ __align__(128) float lut[16 * 2];
+  uint32_t first[kMaxWorld];
+  unpack_nibble_prefetch<2>(src, 0, n, first);
+  if (threadIdx.x < 32) lut[threadIdx.x] = tbq_dequant((uint32_t(threadIdx.x) >> 1 >> (2 * (threadIdx.x & 1))) & 3u, thr);
   __syncthreads();
-  unpack_lut_body<4, APPLY>(lut, 0, src, 0, out, n, add, post_scale, apply);
+  unpack_nibble_body<2, APPLY, true>(lut, first, src, 0, out, n, add, post_scale, apply);
 }
 
 inline int grid_for(int64_t items, int threads, int max_blocks) {
@@ -122,7 +122,7 @@ cudaError_t tbq_unpack_accum(const UnpackSources& src, float threshold, float* o
                              cudaStream_t stream) {
   if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
   // one thread decodes 16 elements per iteration
-  const int grid = grid_for((n + 15) >> 4, kUnpackThreads, 148 * 8);
+  const int grid = grid_for((n + 15) >> 4, kUnpackThreads, 148 * 4);
   if (apply.param != nullptr)
     tbq_unpack_lut_kernel<true><<<grid, kUnpackThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply);
   else

@@ -221,9 +221,12 @@ template <int BW, bool APPLY>
 __global__ void __launch_bounds__(kUnpackThreads)
 tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
                        float post_scale, SgdApply apply, int* status) {
-  extern __shared__ __align__(16) float lut[];  // [world][256][dpb]
+  extern __shared__ __align__(16) float lut[];  // [world][256][dpb], byte-table path only
+  __shared__ __align__(128) float nib[(BW == 1 || BW == 2 || BW == 4) ? kMaxWorld * 16 * (4 / (BW ? BW : 1)) : 1];
   __shared__ TernHeader hdr[kMaxWorld];
   __shared__ int all_ok;
+  uint32_t first[kMaxWorld];
+  if constexpr (BW == 1 || BW == 2 || BW == 4) unpack_nibble_prefetch<BW>(src, kTernHeaderBytes, n, first);
   if (threadIdx.x == 0) all_ok = 1;
   __syncthreads();
   if (threadIdx.x < src.world) {
@@ -239,6 +242,17 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
   __syncthreads();
   if (!all_ok) {
     if (blockIdx.x == 0 && threadIdx.x == 0 && status) atomicExch(status, int(kBadHeader));
+    return;
+  }
+  if constexpr (BW == 1 || BW == 2 || BW == 4) {
+    // nibble tables (see unpack_lut.cuh): entry (rank, nibble, slot)
+    constexpr int DPN = 4 / BW;
+    for (int i = threadIdx.x; i < src.world * 16 * DPN; i += blockDim.x) {
+      const int r = i / (16 * DPN), v = (i / DPN) & 15, j = i % DPN;
+      nib[i] = tern_dequant((uint32_t(v) >> (BW * j)) & ((1u << BW) - 1u), hdr[r].gap, hdr[r].mn);
+    }
+    __syncthreads();
+    unpack_nibble_body<BW, APPLY, false>(nib, first, src, kTernHeaderBytes, out, n, add, post_scale, apply);
     return;
   }
   const int dpb = 8 / bw;
@@ -267,7 +281,8 @@ cudaError_t launch_tern_unpack(const UnpackSources& src, float* out, int64_t n, 
                                const SgdApply& apply, int* status, cudaStream_t stream) {
   // table size: world x 256 x dpb floats; without a known bitwidth, room for 1-bit payloads (dpb = 8)
   const int dpb = BW > 0 ? 8 / BW : 8;
-  const size_t smem = size_t(src.world) * 256 * dpb * sizeof(float);
+  const bool nibble = BW == 1 || BW == 2 || BW == 4;
+  const size_t smem = nibble ? 0 : size_t(src.world) * 256 * dpb * sizeof(float);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(tern_unpack_lut_kernel<BW, APPLY>,
@@ -278,7 +293,7 @@ cudaError_t launch_tern_unpack(const UnpackSources& src, float* out, int64_t n, 
   // one thread decodes 4 payload bytes per rank and iteration; a CTA covers at least 4 K
   // elements so that building the table stays small against the decode work
   const int64_t groups = (n + 4 * dpb - 1) / (4 * dpb);
-  const int grid = grid_for(groups, kUnpackThreads, 148 * 8);
+  const int grid = grid_for(groups, kUnpackThreads, nibble ? 148 * 4 : 148 * 8);
   tern_unpack_lut_kernel<BW, APPLY><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status);
   return cudaGetLastError();
 }

@@ -110,14 +110,16 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
 #pragma unroll
       for (int k = 0; k < EPG; ++k) acc[k] = hp_mul(acc[k], post_scale);
     }
+    const bool clear = APPLY && apply.clear_grad;
     if (out_vec) {
 #pragma unroll
       for (int q = 0; q < EPG / 4; ++q)
         reinterpret_cast<float4*>(out + e0)[q] =
-            make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+            clear ? make_float4(0.f, 0.f, 0.f, 0.f)
+                  : make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
     } else {
 #pragma unroll
-      for (int k = 0; k < EPG; ++k) out[e0 + k] = acc[k];
+      for (int k = 0; k < EPG; ++k) out[e0 + k] = clear ? 0.f : acc[k];
     }
     if (APPLY) {
       if (apply_vec) {
@@ -141,7 +143,135 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
         acc = (r == 0 && !add) ? v : hp_add(v, acc);
       }
       if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
-      out[e] = acc;
+      out[e] = (APPLY && apply.clear_grad) ? 0.f : acc;
+      if (APPLY) sgd_update(apply, e, acc);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- nibble tables
+// The byte table above costs one 16-byte shared-memory read per payload byte, and because a
+// rank's table spans 4 KB, rows of different bytes collide on banks (measured: 2.2 wavefronts
+// per quarter-warp read for 2-bit gradient payloads).  For bitwidths 1, 2 and 4 the table can
+// instead be indexed by a 4-bit nibble: 16 rows of 4/BW floats.  At 2 bits a rank's table is
+// exactly 128 bytes -- one row of all 32 banks -- so any two lanes either read the same row
+// (a broadcast) or different banks: the reads are conflict free whatever the data, the table
+// needs no swizzle, and building it is 16 entries per rank instead of 256.
+//
+// lut: entry (rank r, nibble v, slot j) at lut[(r*16 + v)*DPN + j], DPN = 4/BW (r = 0 when shared).
+//
+// The first payload words of a thread are requested by unpack_nibble_prefetch *before* the
+// kernel reads headers and builds its tables, so that the DRAM latency of the first loads and
+// the dependent loads of the prologue overlap instead of adding up.  A word is only requested
+// when it lies inside the slot (payload_bytes), whatever the header will turn out to say.
+template <int BW>
+__device__ __forceinline__ void unpack_nibble_prefetch(const UnpackSources& src, int data_offset, int64_t n,
+                                                       uint32_t (&w)[kMaxWorld]) {
+  constexpr int EPG = 8 * (4 / BW);
+  const int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+#pragma unroll
+  for (int r = 0; r < kMaxWorld; ++r)
+    w[r] = (r < src.world && grp < n / EPG && data_offset + (grp + 1) * 4 <= src.payload_bytes[r])
+               ? load_u32_any(src.payload[r] + data_offset + grp * 4)
+               : 0u;
+}
+
+// SHARED: all ranks decode through one table (TBQ); otherwise rank r's table starts 16 rows
+// after rank r-1's.  w: the words unpack_nibble_prefetch returned for this thread.
+template <int BW, bool APPLY, bool SHARED>
+__device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&w)[kMaxWorld],
+                                                   const UnpackSources& src, int data_offset,
+                                                   float* __restrict__ out, int64_t n, int add,
+                                                   float post_scale, const SgdApply& apply) {
+  static_assert(BW == 1 || BW == 2 || BW == 4, "nibble tables cover bitwidths 1, 2 and 4");
+  constexpr int DPN = 4 / BW;                                  // elements per nibble
+  constexpr int EPG = 8 * DPN;                                 // elements per 32-bit payload word
+  constexpr int ROW_SHIFT = DPN == 4 ? 4 : (DPN == 2 ? 3 : 2);  // log2(bytes per table row)
+  constexpr int rank_stride = SHARED ? 0 : 16;
+  const int64_t full_groups = n / EPG;
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  const bool out_vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const bool apply_vec = APPLY && ((reinterpret_cast<uintptr_t>(apply.param) |
+                                    reinterpret_cast<uintptr_t>(apply.momentum)) & 15) == 0;
+  int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; grp < full_groups; grp += stride) {
+    const int64_t e0 = grp * EPG;
+    const int64_t nxt = grp + stride;
+    uint32_t wn[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      wn[r] = (r < src.world && nxt < full_groups) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
+    float acc[EPG];
+    if (add) {
+#pragma unroll
+      for (int k = 0; k < EPG; ++k) acc[k] = out[e0 + k];
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) {
+      if (r < src.world) {
+        const char* table = reinterpret_cast<const char*>(lut) + r * rank_stride * DPN * 4;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          // byte offset of the row of nibble k: ((w >> 4k) & 15) << ROW_SHIFT in one shift + mask
+          const uint32_t off = (4 * k >= ROW_SHIFT ? (w[r] >> (4 * k - ROW_SHIFT)) : (w[r] << (ROW_SHIFT - 4 * k))) &
+                               (15u << ROW_SHIFT);
+          float v[DPN];
+          if (DPN == 4) {
+            const float4 t = *reinterpret_cast<const float4*>(table + off);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+          } else if (DPN == 2) {
+            const float2 t = *reinterpret_cast<const float2*>(table + off);
+            v[0] = t.x; v[1] = t.y;
+          } else {
+            v[0] = *reinterpret_cast<const float*>(table + off);
+          }
+#pragma unroll
+          for (int j = 0; j < DPN; ++j)
+            acc[k * DPN + j] = (r == 0 && !add) ? v[j] : hp_add(v[j], acc[k * DPN + j]);
+        }
+      }
+    }
+    if (post_scale != 1.0f) {
+#pragma unroll
+      for (int k = 0; k < EPG; ++k) acc[k] = hp_mul(acc[k], post_scale);
+    }
+    const bool clear = APPLY && apply.clear_grad;
+    if (out_vec) {
+#pragma unroll
+      for (int q = 0; q < EPG / 4; ++q)
+        reinterpret_cast<float4*>(out + e0)[q] =
+            clear ? make_float4(0.f, 0.f, 0.f, 0.f)
+                  : make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < EPG; ++k) out[e0 + k] = clear ? 0.f : acc[k];
+    }
+    if (APPLY) {
+      if (apply_vec) {
+#pragma unroll
+        for (int q = 0; q < EPG / 4; ++q) sgd_update4(apply, e0 + 4 * q, acc + 4 * q);
+      } else {
+#pragma unroll
+        for (int k = 0; k < EPG; ++k) sgd_update(apply, e0 + k, acc[k]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) w[r] = wn[r];
+  }
+  // fewer than EPG leftover elements: one thread, element by element
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    constexpr int DPB = 8 / BW;
+    for (int64_t e = full_groups * EPG; e < n; ++e) {
+      float acc = add ? out[e] : 0.f;
+      const int in_byte = int(e % DPB);
+      for (int r = 0; r < src.world; ++r) {
+        const uint32_t byte = src.payload[r][data_offset + e / DPB];
+        const uint32_t nib = (byte >> (4 * (in_byte / DPN))) & 15u;
+        const float v = lut[(size_t(r) * rank_stride + nib) * DPN + in_byte % DPN];
+        acc = (r == 0 && !add) ? v : hp_add(v, acc);
+      }
+      if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
+      out[e] = (APPLY && apply.clear_grad) ? 0.f : acc;
       if (APPLY) sgd_update(apply, e, acc);
     }
   }

@@ -81,6 +81,28 @@ void psgd_expand_sgd(const torch::Tensor& P, const torch::Tensor& Q, torch::Tens
 int64_t read_status(const torch::Tensor& like, bool reset);
 // Zero-initialised per-(device, stream) scratch used by kernels that need it.
 void* scratch_for(const torch::Tensor& like, size_t bytes);
+// Fused training-mode batch norm (+ residual add, + ReLU) for channels-last bf16 activations.
+// bn_forward returns {y, stats}; stats = [4][C] floats (mean, invstd, scale/shift pairs) and is
+// what bn_backward needs.  bn_backward returns {dx, dweight, dbias [, dresidual]}.
+bool bn_supported(const torch::Tensor& x);
+std::vector<torch::Tensor> bn_forward(const torch::Tensor& x, const c10::optional<torch::Tensor>& residual,
+                                      const c10::optional<torch::Tensor>& weight,
+                                      const c10::optional<torch::Tensor>& bias,
+                                      c10::optional<torch::Tensor> running_mean,
+                                      c10::optional<torch::Tensor> running_var,
+                                      c10::optional<torch::Tensor> num_batches, double momentum, double eps,
+                                      bool relu);
+std::vector<torch::Tensor> bn_backward(const torch::Tensor& dy, const torch::Tensor& x,
+                                       const c10::optional<torch::Tensor>& y,
+                                       const c10::optional<torch::Tensor>& weight, const torch::Tensor& stats,
+                                       bool relu, bool want_dres);
+
+// 3x3 / stride 2 / padding 1 max pooling of channels-last bf16 activations: {y, idx} forward
+// (idx: winning window position per output element, one byte), gather backward.
+bool maxpool_supported(const torch::Tensor& x);
+std::vector<torch::Tensor> maxpool3x3s2_forward(const torch::Tensor& x);
+torch::Tensor maxpool3x3s2_backward(const torch::Tensor& dy, const torch::Tensor& idx, int64_t h, int64_t w);
+
 int* status_word_for(const torch::Tensor& like);
 
 }  // namespace ops

@@ -316,6 +316,7 @@ void DdpEngine::issue_recv(int b, int worker) {
     apply.mu = sgd_mu_;
     apply.weight_decay = wd_;
     apply.first_step = steps_ == 0 ? 1 : 0;
+    apply.clear_grad = cfg_.clear_grad;
   }
   int launched = 0;
   // ---- recv stream: wait for all ranks, decode everything in one pass
@@ -369,6 +370,7 @@ void DdpEngine::issue_recv(int b, int worker) {
     aw.eps = eps_;
     aw.weight_decay = wd_;
     aw.step = int(steps_) + 1;
+    aw.clear_grad = cfg_.clear_grad;
     check(cuda::adamw_apply_dense(g, 1.0f, aw, n, w.recv), "adamw_apply_dense");
     launched += 1;
   }

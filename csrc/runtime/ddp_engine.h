@@ -61,6 +61,9 @@ struct EngineConfig {
   // caller lets all ranks push, synchronises, and only then finishes the steps,
   // so that no kernel ever waits for a kernel that has not been launched yet.
   int defer_recv = 0;
+  // The fused optimizer kernel leaves zeros in the gradient bucket instead of the averaged
+  // gradient (nobody reads it after a fused update), so no separate clearing pass is needed.
+  int clear_grad = 0;
 };
 
 struct BucketDesc {

@@ -1,0 +1,99 @@
+"""Layers of the model zoo that run on this framework's own kernels.
+
+``MaxPool3x3s2`` is the ResNet stem's pooling layer on a gather-style kernel pair.
+
+``FusedBatchNormAct`` is ``nn.BatchNorm2d`` (same parameters, buffers and state-dict keys)
+whose training-mode forward and backward on channels-last bf16 CUDA activations run on the
+hand-written streaming kernels of ``csrc/kernels/bn.cu``, with the ReLU and the residual add
+of a ResNet block folded in:
+
+    y = relu(batch_norm(x) [+ residual])
+
+Profiling the ResNet-50 benchmark step showed the stock channels-last batch-norm kernels at
+54 % of the device time; these kernels do the same maths in two passes forward and two
+backward, each close to one read/write of the activations at HBM speed.  Anything the kernels
+do not cover (CPU tensors, fp32 activations, NCHW layout, eval mode, odd channel counts) takes
+the stock PyTorch path with identical semantics.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import _C
+
+
+class _FusedBnFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, bias, running_mean, running_var, num_batches,
+                momentum: float, eps: float, relu: bool):
+        y, stats = _C.bn_forward(x, residual, weight, bias, running_mean, running_var, num_batches,
+                                 momentum, eps, relu)
+        ctx.save_for_backward(x, y if relu else None, weight, stats)
+        ctx.relu = relu
+        ctx.has_residual = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, y, weight, stats = ctx.saved_tensors
+        dy = dy.contiguous(memory_format=torch.channels_last)
+        out = _C.bn_backward(dy, x, y, weight, stats, ctx.relu, ctx.has_residual)
+        dres = out[3] if ctx.has_residual else None
+        return out[0], dres, out[1], out[2], None, None, None, None, None, None
+
+
+class FusedBatchNormAct(nn.BatchNorm2d):
+    """Batch norm, optional residual add, optional ReLU: ``forward(x, residual=None)``."""
+
+    def __init__(self, num_features: int, relu: bool = False, eps: float = 1e-5, momentum: float = 0.1):
+        super().__init__(num_features, eps=eps, momentum=momentum, affine=True, track_running_stats=True)
+        self.relu = relu
+
+    def _fused_ok(self, x: torch.Tensor, residual: Optional[torch.Tensor]) -> bool:
+        if _C is None or not (self.training and x.is_cuda and x.dtype == torch.bfloat16 and self.momentum is not None):
+            return False
+        if residual is not None and (residual.dtype != x.dtype or residual.shape != x.shape or
+                                     not residual.is_contiguous(memory_format=torch.channels_last)):
+            return False
+        return _C.bn_supported(x)
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self._fused_ok(x, residual):
+            return _FusedBnFunction.apply(x, residual, self.weight, self.bias, self.running_mean,
+                                          self.running_var, self.num_batches_tracked,
+                                          float(self.momentum), float(self.eps), self.relu)
+        y = super().forward(x)
+        if residual is not None:
+            y = y + residual
+        return F.relu(y) if self.relu else y
+
+    def extra_repr(self) -> str:
+        return super().extra_repr() + f", relu={self.relu}"
+
+
+class _MaxPoolFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        y, idx = _C.maxpool3x3s2_forward(x)
+        ctx.save_for_backward(idx)
+        ctx.hw = (x.shape[2], x.shape[3])
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (idx,) = ctx.saved_tensors
+        return _C.maxpool3x3s2_backward(dy.contiguous(memory_format=torch.channels_last), idx, *ctx.hw)
+
+
+class MaxPool3x3s2(nn.Module):
+    """``nn.MaxPool2d(3, stride=2, padding=1)``; channels-last bf16 CUDA activations run on
+    ``csrc/kernels/pool.cu`` (one index byte per output, gather backward without atomics)."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if _C is not None and x.is_cuda and _C.maxpool_supported(x):
+            return _MaxPoolFunction.apply(x)
+        return F.max_pool2d(x, 3, stride=2, padding=1)

@@ -71,10 +71,10 @@ class NcclDataParallel(nn.Module):
             if self.optimizer == "adamw":
                 _C.adamw_apply(g, self.flat_param[off:off + numel], self.flat_momentum[off:off + numel],
                                self.flat_second[off:off + numel], 1.0 / self.world, self.lr, self.betas[0],
-                               self.betas[1], self.eps, self.weight_decay, self.steps + 1)
+                               self.betas[1], self.eps, self.weight_decay, self.steps + 1, True)
             else:
                 _C.sgd_apply(g, self.flat_param[off:off + numel], self.flat_momentum[off:off + numel],
-                             1.0 / self.world, self.lr, self.momentum, self.weight_decay, self.steps == 0)
+                             1.0 / self.world, self.lr, self.momentum, self.weight_decay, self.steps == 0, True)
             self.launches += 1
 
     def forward(self, *args, **kwargs):
@@ -92,8 +92,7 @@ class NcclDataParallel(nn.Module):
                 self._launch(b)
         torch.cuda.current_stream().wait_stream(self.comm_stream)
         self.pending = [b[2] for b in self.plan.buckets]
-        self.flat_grad.zero_()
-        self.steps += 1
+        self.steps += 1            # the fused optimizer kernels left zeros in flat_grad
 
     def check(self) -> None:
         torch.cuda.synchronize()

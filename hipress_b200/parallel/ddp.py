@@ -177,6 +177,9 @@ class CompressedDataParallel(nn.Module):
                            if process_group is not None else 0, group=process_group)
 
         cfg_dict = self.config.engine_dict(rank, world, dev.index)
+        # with a fused optimizer nobody reads the averaged gradient: the kernel that applies the
+        # update leaves zeros behind, ready for the next backward pass
+        cfg_dict["clear_grad"] = 1 if fused else 0
         if self.config.num_workers < 0:
             per_bucket = {"dgc": 12 + world, "graddrop": 10 + world}.get(self.config.algorithm, 4)
             cfg_dict["num_workers"] = 1 if len(self.plan.buckets) * per_bucket > 200 else 0
@@ -226,8 +229,6 @@ class CompressedDataParallel(nn.Module):
             raise RuntimeError("step() without a forward/backward since the last step()")
         self.engine.finish_step(self._dev_index)
         self._in_step = False
-        if self.fused_sgd:
-            self.flat_grad.zero_()
 
     def zero_grad(self, set_to_none: bool = False) -> None:  # noqa: D401
         """Gradients live in the flat buffer and are views: they are zeroed, never dropped."""

@@ -1,0 +1,139 @@
+"""Fused batch-norm kernels against a plain PyTorch fp32 restatement of the same op."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from hipress_b200 import _C
+from hipress_b200.models import resnet_tiny
+from hipress_b200.models.layers import FusedBatchNormAct
+
+pytestmark = pytest.mark.gpu
+
+
+def reference(x, res, w, b, relu, eps=1e-5):
+    """fp32 autograd restatement on the bf16-rounded inputs."""
+    xf = x.float().detach().requires_grad_(True)
+    rf = res.float().detach().requires_grad_(True) if res is not None else None
+    wf, bf = w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    y = F.batch_norm(xf, None, None, wf, bf, True, 0.1, eps)
+    if rf is not None:
+        y = y + rf
+    if relu:
+        y = F.relu(y)
+    return xf, rf, wf, bf, y
+
+
+@pytest.mark.parametrize("shape", [(4, 64, 56, 56), (3, 8, 7, 5), (2, 16, 9, 9), (5, 32, 6, 6),
+                                    (2, 256, 14, 14), (2, 512, 7, 7), (1, 2048, 7, 7), (64, 128, 28, 28)])
+@pytest.mark.parametrize("relu,residual", [(False, False), (True, False), (True, True), (False, True)])
+def test_forward_backward_match_fp32_reference(shape, relu, residual):
+    torch.manual_seed(0)
+    n, c, h, w_ = shape
+    x = (torch.randn(shape, device="cuda") * 1.7 + 0.4).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    res = torch.randn(shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last) if residual else None
+    layer = FusedBatchNormAct(c, relu=relu).cuda().train()
+    with torch.no_grad():
+        layer.weight.uniform_(0.5, 1.5)
+        layer.bias.uniform_(-0.5, 0.5)
+    xg = x.clone().requires_grad_(True)
+    rg = res.clone().requires_grad_(True) if residual else None
+    y = layer(xg, rg)
+    assert y.dtype == torch.bfloat16 and y.is_contiguous(memory_format=torch.channels_last)
+    dy = torch.randn(shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y.backward(dy)
+
+    xf, rf, wf, bf, yr = reference(x, res, layer.weight, layer.bias, relu)
+    # the fused kernel masks with the bf16-rounded output; do the same in the restatement
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, atol=3e-2, rtol=2e-2)          # bf16 output rounding
+    m = float(n * h * w_)
+    torch.testing.assert_close(xg.grad.float(), xf.grad, atol=3e-2 * float(xf.grad.abs().max()) + 1e-3, rtol=3e-2)
+    scale = (m ** 0.5)
+    torch.testing.assert_close(layer.weight.grad, wf.grad, atol=2e-2 * scale, rtol=2e-2)
+    torch.testing.assert_close(layer.bias.grad, bf.grad, atol=2e-2 * scale, rtol=2e-2)
+    if residual:
+        torch.testing.assert_close(rg.grad.float(), rf.grad, atol=1e-2, rtol=1e-2)
+    # running statistics follow nn.BatchNorm2d (unbiased variance, momentum 0.1)
+    xm = x.float().transpose(0, 1).reshape(c, -1)
+    torch.testing.assert_close(layer.running_mean, 0.1 * xm.mean(1), atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(layer.running_var, 0.9 + 0.1 * xm.var(1, unbiased=True), atol=1e-4, rtol=1e-4)
+    assert int(layer.num_batches_tracked) == 1
+
+
+def test_statistics_survive_a_large_mean():
+    """Variance of data with |mean| >> std: the per-block + Chan combination must not cancel."""
+    torch.manual_seed(1)
+    shape = (8, 64, 28, 28)
+    x = (torch.randn(shape, device="cuda") * 0.25 + 40.0).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    _, stats = _C.bn_forward(x, None, None, None, None, None, None, 0.1, 1e-5, False)
+    xm = x.double().transpose(0, 1).reshape(64, -1)
+    torch.testing.assert_close(stats[0].double(), xm.mean(1), atol=1e-4, rtol=1e-6)
+    invstd = 1.0 / torch.sqrt(xm.var(1, unbiased=False) + 1e-5)
+    torch.testing.assert_close(stats[1].double(), invstd, atol=0, rtol=2e-3)
+
+
+def test_unsupported_inputs_take_the_stock_path():
+    layer = FusedBatchNormAct(12, relu=True).cuda().train()     # 12 channels: not a multiple of 8
+    x = torch.randn(2, 12, 5, 5, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    assert not _C.bn_supported(x)
+    y = layer(x)
+    assert y.shape == x.shape and float(y.min()) >= 0
+    layer64 = FusedBatchNormAct(64, relu=False).cuda().train()
+    xf = torch.randn(2, 64, 5, 5, device="cuda")                 # fp32 activations
+    ref = F.batch_norm(xf, None, None, layer64.weight, layer64.bias, True, 0.1, 1e-5)
+    torch.testing.assert_close(layer64(xf), ref)
+    layer64.eval()
+    xb = xf.to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    assert layer64(xb).shape == xb.shape
+
+
+def test_resnet_with_fused_layers_matches_stock_layers():
+    """Same tiny ResNet, once through the fused kernels (bf16 channels-last) and once with the
+    layers forced onto the stock path: losses and input-layer gradients agree to bf16 accuracy."""
+    torch.manual_seed(0)
+    net = resnet_tiny(10).cuda().to(memory_format=torch.channels_last).train()
+    x = torch.randn(16, 3, 64, 64, device="cuda").contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (16,), device="cuda")
+
+    def run(fused):
+        net.zero_grad(set_to_none=True)
+        saved = FusedBatchNormAct._fused_ok
+        if not fused:
+            FusedBatchNormAct._fused_ok = lambda self, a, b: False
+        try:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = F.cross_entropy(net(x), y)
+            loss.backward()
+        finally:
+            FusedBatchNormAct._fused_ok = saved
+        return float(loss.detach()), net.conv1.weight.grad.clone(), net.fc.weight.grad.clone()
+
+    l1, g1, f1 = run(True)
+    l0, g0, f0 = run(False)
+    assert abs(l1 - l0) < 3e-2, (l1, l0)
+    cos = lambda a, b: float((a * b).sum() / (a.norm() * b.norm() + 1e-12))
+    assert cos(f1, f0) > 0.99 and cos(g1, g0) > 0.95, (cos(f1, f0), cos(g1, g0))
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 112, 112), (3, 8, 7, 9), (1, 16, 1, 1), (2, 32, 10, 5)])
+def test_maxpool_matches_torch(shape):
+    from hipress_b200.models.layers import MaxPool3x3s2
+    torch.manual_seed(0)
+    x = torch.randn(shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    xg = x.clone().requires_grad_(True)
+    y = MaxPool3x3s2()(xg)
+    xr = x.float().requires_grad_(True)
+    yr = F.max_pool2d(xr, 3, stride=2, padding=1)
+    assert y.shape == yr.shape and y.is_contiguous(memory_format=torch.channels_last)
+    assert torch.equal(y.float(), yr)                         # a maximum of bf16 values is exact
+    dy = torch.randn(y.shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y.backward(dy)
+    yr.backward(dy.float())
+    # up to four bf16 gradients summed in fp32, rounded once
+    torch.testing.assert_close(xg.grad.float(), xr.grad, atol=2e-2, rtol=1e-2)
+
+
+def test_maxpool_falls_back_for_other_inputs():
+    from hipress_b200.models.layers import MaxPool3x3s2
+    x = torch.randn(2, 6, 9, 9, device="cuda")
+    assert torch.equal(MaxPool3x3s2()(x), F.max_pool2d(x, 3, stride=2, padding=1))

