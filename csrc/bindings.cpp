@@ -165,6 +165,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("maxpool3x3s2_forward", &ops::maxpool3x3s2_forward, py::arg("x"));
   m.def("maxpool3x3s2_backward", &ops::maxpool3x3s2_backward, py::arg("dy"), py::arg("idx"), py::arg("h"),
         py::arg("w"));
+  m.def("bias_relu_supported", &ops::bias_relu_supported, py::arg("x"), py::arg("pool"));
+  m.def("bias_relu_forward", &ops::bias_relu_forward, py::arg("x"), py::arg("bias"), py::arg("pool"));
+  m.def("bias_relu_backward", &ops::bias_relu_backward, py::arg("dy"), py::arg("y"), py::arg("idx"),
+        py::arg("pool"));
   m.def("psgd_kpad", &cuda::psgd_kpad, py::arg("k"));
   m.def("gram_schmidt", &ops::gram_schmidt, py::arg("P"), py::arg("eps") = 1e-8);
   m.def("psgd_expand_feedback", &ops::psgd_expand_feedback, py::arg("P"), py::arg("Q"), py::arg("M"),

@@ -26,79 +26,12 @@
 #include <cuda_bf16.h>
 
 #include "kernels.h"
+#include "nhwc.cuh"
 
 namespace hipress {
 namespace cuda {
 
 namespace {
-
-constexpr int kBnThreads = 256;
-constexpr int kBnVec = 8;  // channels per thread
-
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[kBnVec]) {
-  const uint4 raw = *reinterpret_cast<const uint4*>(p);
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const float2 f = __bfloat1622float2(h[q]);
-    v[2 * q] = f.x;
-    v[2 * q + 1] = f.y;
-  }
-}
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[kBnVec]) {
-  uint4 raw;
-  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(v[2 * q], v[2 * q + 1]);
-  *reinterpret_cast<uint4*>(p) = raw;
-}
-
-struct Geom {
-  int tx;                  // threads along channels (power of two, <= 32)
-  int tiles;               // channel tiles = C / (tx * 8)
-  int row_blocks;          // CTAs along rows
-  int64_t rows_per_block;
-};
-
-// Threads of a CTA: tx = t % g.tx (channel group), ty = t / g.tx (row lane), TY = 256 / g.tx.
-struct Lane {
-  int tx, ty, TY, c0;
-  int64_t r_begin, r_end;
-};
-__device__ __forceinline__ Lane lane_of(int tx_count, int64_t M, int64_t rows_per_block) {
-  Lane l;
-  l.tx = threadIdx.x % tx_count;
-  l.ty = threadIdx.x / tx_count;
-  l.TY = kBnThreads / tx_count;
-  l.c0 = (blockIdx.x * tx_count + l.tx) * kBnVec;
-  l.r_begin = int64_t(blockIdx.y) * rows_per_block;
-  l.r_end = l.r_begin + rows_per_block < M ? l.r_begin + rows_per_block : M;
-  return l;
-}
-
-// Sums a[0..8) and b[0..8) of every thread over the row lanes of the CTA; on return thread t
-// (t < tx_count*8) holds the CTA totals of channel t of the tile in (ra, rb).
-__device__ __forceinline__ void reduce_rows(const float (&a)[kBnVec], const float (&b)[kBnVec], int tx_count,
-                                            float* sh /* 2 * 256 * 8 floats */, float& ra, float& rb) {
-  const int tx = threadIdx.x % tx_count, ty = threadIdx.x / tx_count;
-  const int ct = tx_count * kBnVec, TY = kBnThreads / tx_count;
-  float* sa = sh;
-  float* sb = sh + kBnThreads * kBnVec;
-#pragma unroll
-  for (int k = 0; k < kBnVec; ++k) {
-    sa[ty * ct + tx * kBnVec + k] = a[k];
-    sb[ty * ct + tx * kBnVec + k] = b[k];
-  }
-  __syncthreads();
-  ra = 0.f;
-  rb = 0.f;
-  if (int(threadIdx.x) < ct) {
-    for (int y = 0; y < TY; ++y) {
-      ra += sa[y * ct + threadIdx.x];
-      rb += sb[y * ct + threadIdx.x];
-    }
-  }
-}
 
 // ---------------------------------------------------------------- forward: statistics
 __global__ void __launch_bounds__(kBnThreads)
@@ -146,15 +79,16 @@ bn_stats_kernel(const __nv_bfloat16* __restrict__ x, int64_t M, int C, int tx_co
 constexpr int kFinChannels = 32;  // channels per finalize CTA (one per lane)
 constexpr int kFinThreads = 1024;
 constexpr int kFinWarps = kFinThreads / 32;
-constexpr int kFinBatch = 4;      // partials requested together: their load latencies overlap
+constexpr int kFinBatch = 10;     // partials requested together: their load latencies overlap
 
 // Chan et al.: merge (count, mean, M2) of two disjoint sets.
 __device__ __forceinline__ void chan_merge(float& cnt, float& mean, float& m2, float nb, float mb, float m2b) {
   if (nb <= 0.f) return;
   const float tot = cnt + nb;
   const float delta = mb - mean;
-  mean += delta * (nb / tot);
-  m2 += m2b + delta * delta * (cnt * nb / tot);
+  const float frac = __fdividef(nb, tot);  // weights of a mean: 2 ulp is plenty, an IEEE divide per step is not free
+  mean += delta * frac;
+  m2 += m2b + delta * delta * (cnt * frac);
   cnt = tot;
 }
 
@@ -172,6 +106,16 @@ bn_stats_finalize_kernel(const float2* __restrict__ partial, int row_blocks, int
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.x * kFinChannels + lane;
   float cnt = 0.f, mean = 0.f, m2 = 0.f;
+  // per-channel scalars of the epilogue, requested now so that they arrive during the merge
+  float w_c = 1.f, b_c = 0.f, rm_c = 0.f, rv_c = 0.f;
+  if (warp == 0 && c < C) {
+    if (gamma) w_c = gamma[c];
+    if (beta) b_c = beta[c];
+    if (running_mean) {
+      rm_c = running_mean[c];
+      rv_c = running_var[c];
+    }
+  }
   if (c < C) {
     for (int y0 = warp; y0 < row_blocks; y0 += kFinWarps * kFinBatch) {
       float2 p[kFinBatch];
@@ -200,11 +144,11 @@ bn_stats_finalize_kernel(const float2* __restrict__ partial, int row_blocks, int
   const float invstd = rsqrtf(var + eps);
   mean_out[c] = mean;
   invstd_out[c] = invstd;
-  const float a = gamma ? gamma[c] * invstd : invstd;
-  ab_out[c] = make_float2(a, (beta ? beta[c] : 0.f) - mean * a);
+  const float a = w_c * invstd;
+  ab_out[c] = make_float2(a, b_c - mean * a);
   if (running_mean) {
-    running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * mean;
-    running_var[c] = (1.f - momentum) * running_var[c] + momentum * (cnt > 1.f ? m2 / (cnt - 1.f) : var);
+    running_mean[c] = (1.f - momentum) * rm_c + momentum * mean;
+    running_var[c] = (1.f - momentum) * rv_c + momentum * (cnt > 1.f ? m2 / (cnt - 1.f) : var);
   }
   if (num_batches && c == 0) *num_batches += 1;
 }
@@ -317,6 +261,12 @@ bn_bwd_finalize_kernel(const float2* __restrict__ partial, int row_blocks, int64
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = blockIdx.x * kFinChannels + lane;
   float t1 = 0.f, t2 = 0.f;
+  float is = 0.f, m = 0.f, wgt = 1.f;  // requested now, used after the merge
+  if (warp == 0 && c < C) {
+    is = invstd[c];
+    m = mean[c];
+    if (gamma) wgt = gamma[c];
+  }
   if (c < C) {
     for (int y0 = warp; y0 < row_blocks; y0 += kFinWarps * kFinBatch) {
       float2 p[kFinBatch];
@@ -340,8 +290,6 @@ bn_bwd_finalize_kernel(const float2* __restrict__ partial, int row_blocks, int64
     t1 += sh[0][w][lane];
     t2 += sh[1][w][lane];
   }
-  const float is = invstd[c], m = mean[c];
-  const float wgt = gamma ? gamma[c] : 1.f;
   if (dbeta) dbeta[c] = t1;
   if (dgamma) dgamma[c] = t2 * is;
   // dx = a*(dy' - mean(dy') - xhat*mean(dy'*xhat)),  xhat = (x - m)*is,  a = w*is
@@ -403,26 +351,6 @@ bn_bwd_elemt_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* _
     store8(dx + r * C + l.c0, v);
     if (ADD) store8(dres + r * C + l.c0, g);
   }
-}
-
-bool geometry(int64_t M, int C, Geom* g) {
-  if (M < 1 || C < kBnVec || C % kBnVec) return false;
-  const int groups = C / kBnVec;
-  int tx = 1;
-  while (tx < 32 && tx < groups) tx <<= 1;
-  if (groups % tx) return false;  // C/8 must be a power of two up to 32, or a multiple of 32
-  g->tx = tx;
-  g->tiles = groups / tx;
-  const int ty = kBnThreads / tx;
-  // one wave: these kernels hold ~64 registers per thread, so 4 CTAs of 256 threads fit an SM
-  int64_t want = (148 * 4 + g->tiles - 1) / g->tiles;
-  const int64_t most = (M + int64_t(ty) * 4 - 1) / (int64_t(ty) * 4);  // >= 4 rows per thread
-  if (want > most) want = most;
-  if (want < 1) want = 1;
-  if (want > kBnMaxRowBlocks) want = kBnMaxRowBlocks;
-  g->rows_per_block = (M + want - 1) / want;
-  g->row_blocks = int((M + g->rows_per_block - 1) / g->rows_per_block);
-  return true;
 }
 
 }  // namespace

@@ -167,6 +167,19 @@ cudaError_t bn_backward(const void* dy, const void* x, const void* y, void* dx, 
                         int relu, float* dgamma, float* dbeta, float* coef, float* partial,
                         cudaStream_t stream);
 
+// ---------------------------------------------------------------- bias + ReLU (+ 2x2 max pool)
+// Convolution epilogue over channels-last bf16 [n][h][w][c]; c as for batch norm.  With pool,
+// h and w must be even, y is [n][h/2][w/2][c] and idx holds the arg max (0..3 = 2*row + column)
+// per output element.  partial = bias_relu_partial_elems(output rows, c) floats of scratch.
+bool bias_relu_supported(int64_t rows, int channels);
+int64_t bias_relu_partial_elems(int64_t rows, int channels);
+cudaError_t bias_relu_forward(const void* x, const float* bias, void* y, uint8_t* idx, int n, int h, int w,
+                              int channels, int pool, cudaStream_t stream);
+// dz [n][h][w][c] = gradient w.r.t. the convolution output, dbias [c] fp32.
+cudaError_t bias_relu_backward(const void* dy, const void* y, const uint8_t* idx, void* dz, float* dbias,
+                               float* partial, int n, int h, int w, int channels, int pool,
+                               cudaStream_t stream);
+
 // ---------------------------------------------------------------- max pooling
 // 3x3, stride 2, padding 1 over channels-last bf16 [n][h][w][c] (c a multiple of 8).  The forward
 // writes y [n][ho][wo][c] (ho = (h-1)/2 + 1) and one byte per output element: the winning window

@@ -91,7 +91,10 @@ tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int
   unpack_nibble_prefetch<2>(src, 0, n, first);
   if (threadIdx.x < 32) lut[threadIdx.x] = tbq_dequant((uint32_t(threadIdx.x) >> 1 >> (2 * (threadIdx.x & 1))) & 3u, thr);
   __syncthreads();
-  unpack_nibble_body<2, APPLY, true>(lut, first, src, 0, out, n, add, post_scale, apply);
+  if (unpack_coalesced_ok(src, out, APPLY, apply))
+    unpack_nibble_body_coalesced2<APPLY, true>(lut, first, src, 0, out, n, add, post_scale, apply);
+  else
+    unpack_nibble_body<2, APPLY, true>(lut, first, src, 0, out, n, add, post_scale, apply);
 }
 
 inline int grid_for(int64_t items, int threads, int max_blocks) {

@@ -252,6 +252,12 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
       nib[i] = tern_dequant((uint32_t(v) >> (BW * j)) & ((1u << BW) - 1u), hdr[r].gap, hdr[r].mn);
     }
     __syncthreads();
+    if constexpr (BW == 2) {
+      if (unpack_coalesced_ok(src, out, APPLY, apply)) {
+        unpack_nibble_body_coalesced2<APPLY, false>(nib, first, src, kTernHeaderBytes, out, n, add, post_scale, apply);
+        return;
+      }
+    }
     unpack_nibble_body<BW, APPLY, false>(nib, first, src, kTernHeaderBytes, out, n, add, post_scale, apply);
     return;
   }

@@ -277,5 +277,90 @@ __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&
   }
 }
 
+// ---------------------------------------------------------------- one or two payloads, 2 bits
+// With one or two payloads the kernel is bound by the dense traffic (gradient out, parameters
+// and momentum in and out), not by the decode, and the mapping above -- a thread owning 64
+// contiguous bytes of every dense array -- makes each 16-byte access of a warp touch 32
+// different sectors.  Here lane L of a warp handles payload byte j*32 + L (j = 0..3) of the
+// warp's 128-byte payload chunk, i.e. elements (j*32 + L)*4 .. +3 of the chunk's 512: every
+// dense access is a 512-byte contiguous run across the warp.  The payload is still loaded one
+// 32-bit word per lane; bytes reach their lanes by shuffle.
+template <bool APPLY, bool SHARED>
+__device__ __forceinline__ void unpack_nibble_body_coalesced2(const float* lut, uint32_t (&w)[kMaxWorld],
+                                                              const UnpackSources& src, int data_offset,
+                                                              float* __restrict__ out, int64_t n, int add,
+                                                              float post_scale, const SgdApply& apply) {
+  constexpr int rank_stride_bytes = SHARED ? 0 : 16 * 2 * 4;
+  const int64_t full_groups = n / 16;            // complete 32-bit payload words
+  const int64_t full_chunks = full_groups / 32;  // complete 128-byte warp chunks
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = int64_t(gridDim.x) * (blockDim.x >> 5);
+  const bool clear = APPLY && apply.clear_grad;
+  int64_t chunk = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  for (; chunk < full_chunks; chunk += warps) {
+    const int64_t nxt = (chunk + warps) * 32 + lane;
+    uint32_t wn[kMaxWorld];
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      wn[r] = (r < src.world && chunk + warps < full_chunks) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t e = chunk * 512 + int64_t(j * 32 + lane) * 4;
+      float acc[4];
+      if (add) {
+        const float4 o = *reinterpret_cast<const float4*>(out + e);
+        acc[0] = o.x; acc[1] = o.y; acc[2] = o.z; acc[3] = o.w;
+      }
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r < src.world) {
+          const uint32_t word = __shfl_sync(0xffffffffu, w[r], j * 8 + (lane >> 2));
+          const uint32_t byte = (word >> (8 * (lane & 3))) & 255u;
+          const char* table = reinterpret_cast<const char*>(lut) + r * rank_stride_bytes;
+          const float2 lo = *reinterpret_cast<const float2*>(table + ((byte & 15u) << 3));
+          const float2 hi = *reinterpret_cast<const float2*>(table + ((byte >> 4) << 3));
+          const float v[4] = {lo.x, lo.y, hi.x, hi.y};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) acc[k] = (r == 0 && !add) ? v[k] : hp_add(v[k], acc[k]);
+        }
+      }
+      if (post_scale != 1.0f) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[k] = hp_mul(acc[k], post_scale);
+      }
+      *reinterpret_cast<float4*>(out + e) =
+          clear ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(acc[0], acc[1], acc[2], acc[3]);
+      if (APPLY) sgd_update4(apply, e, acc);
+    }
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r) w[r] = wn[r];
+  }
+  // payload words past the last complete chunk (fewer than 32) and the elements past the last
+  // complete word (fewer than 16): block 0, element by element
+  if (blockIdx.x == 0) {
+    for (int64_t e = full_chunks * 512 + threadIdx.x; e < n; e += blockDim.x) {
+      float acc = add ? out[e] : 0.f;
+      for (int r = 0; r < src.world; ++r) {
+        const uint32_t byte = src.payload[r][data_offset + (e >> 2)];
+        const uint32_t nib = (byte >> (4 * ((e & 3) >> 1))) & 15u;
+        const float v = lut[(size_t(SHARED ? 0 : r) * 16 + nib) * 2 + (e & 1)];
+        acc = (r == 0 && !add) ? v : hp_add(v, acc);
+      }
+      if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
+      out[e] = clear ? 0.f : acc;
+      if (APPLY) sgd_update(apply, e, acc);
+    }
+  }
+}
+
+// True when unpack_nibble_body_coalesced2 applies: 2-bit payloads of at most two ranks and
+// 16-byte aligned dense arrays.
+__device__ __forceinline__ bool unpack_coalesced_ok(const UnpackSources& src, const float* out, bool apply_on,
+                                                    const SgdApply& apply) {
+  uintptr_t bits = reinterpret_cast<uintptr_t>(out);
+  if (apply_on) bits |= reinterpret_cast<uintptr_t>(apply.param) | reinterpret_cast<uintptr_t>(apply.momentum);
+  return src.world <= 2 && (bits & 15) == 0;
+}
+
 }  // namespace cuda
 }  // namespace hipress

@@ -149,5 +149,55 @@ torch::Tensor maxpool3x3s2_backward(const torch::Tensor& dy, const torch::Tensor
   return dx;
 }
 
+// ---------------------------------------------------------------- bias + ReLU (+ 2x2 max pool)
+bool bias_relu_supported(const torch::Tensor& x, bool pool) {
+  if (!x.is_cuda() || x.scalar_type() != torch::kBFloat16 || x.dim() != 4 || x.numel() == 0 ||
+      !x.is_contiguous(at::MemoryFormat::ChannelsLast))
+    return false;
+  if (pool && ((x.size(2) & 1) || (x.size(3) & 1))) return false;
+  const int64_t rows = x.size(0) * (pool ? x.size(2) / 2 : x.size(2)) * (pool ? x.size(3) / 2 : x.size(3));
+  return cuda::bias_relu_supported(rows, int(x.size(1)));
+}
+
+std::vector<torch::Tensor> bias_relu_forward(const torch::Tensor& x, const torch::Tensor& bias, bool pool) {
+  TORCH_CHECK(bias_relu_supported(x, pool), "bias_relu: unsupported activation tensor");
+  const int n = int(x.size(0)), c = int(x.size(1)), h = int(x.size(2)), w = int(x.size(3));
+  const int ho = pool ? h / 2 : h, wo = pool ? w / 2 : w;
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty({n, c, ho, wo}, x.options(), at::MemoryFormat::ChannelsLast);
+  torch::Tensor idx;
+  if (pool) idx = torch::empty({n, c, ho, wo}, x.options().dtype(torch::kUInt8), at::MemoryFormat::ChannelsLast);
+  HP_BN_CHECK(cuda::bias_relu_forward(x.data_ptr(), opt_f32(bias, c, "bias"), y.data_ptr(),
+                                      pool ? idx.data_ptr<uint8_t>() : nullptr, n, h, w, c, pool ? 1 : 0,
+                                      at::cuda::getCurrentCUDAStream()));
+  if (pool) return {y, idx};
+  return {y};
+}
+
+std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const torch::Tensor& y,
+                                              const c10::optional<torch::Tensor>& idx, bool pool) {
+  const Shape s = check_activation(y, "y");
+  const Shape g = check_activation(dy, "dy");
+  TORCH_CHECK(g.rows == s.rows && g.channels == s.channels && dy.sizes() == y.sizes(), "dy must have y's shape");
+  const int n = int(y.size(0)), c = int(y.size(1));
+  const int h = int(y.size(2)) * (pool ? 2 : 1), w = int(y.size(3)) * (pool ? 2 : 1);
+  const uint8_t* ip = nullptr;
+  if (pool) {
+    TORCH_CHECK(idx && idx->defined() && idx->is_cuda() && idx->scalar_type() == torch::kUInt8 &&
+                    idx->sizes() == y.sizes() && idx->is_contiguous(at::MemoryFormat::ChannelsLast),
+                "idx must be the forward's index tensor");
+    ip = idx->data_ptr<uint8_t>();
+  }
+  c10::cuda::CUDAGuard guard(y.device());
+  auto dz = torch::empty({n, c, h, w}, y.options(), at::MemoryFormat::ChannelsLast);
+  auto f32 = y.options().dtype(torch::kFloat32);
+  auto db = torch::empty({c}, f32);
+  auto partial = torch::empty({cuda::bias_relu_partial_elems(s.rows, c)}, f32);
+  HP_BN_CHECK(cuda::bias_relu_backward(dy.data_ptr(), y.data_ptr(), ip, dz.data_ptr(), db.data_ptr<float>(),
+                                       partial.data_ptr<float>(), n, h, w, c, pool ? 1 : 0,
+                                       at::cuda::getCurrentCUDAStream()));
+  return {dz, db};
+}
+
 }  // namespace ops
 }  // namespace hipress

@@ -103,6 +103,13 @@ bool maxpool_supported(const torch::Tensor& x);
 std::vector<torch::Tensor> maxpool3x3s2_forward(const torch::Tensor& x);
 torch::Tensor maxpool3x3s2_backward(const torch::Tensor& dy, const torch::Tensor& idx, int64_t h, int64_t w);
 
+// Convolution epilogue: y = relu(x + bias), optionally followed by 2x2 / stride 2 max pooling,
+// over channels-last bf16 activations.  forward -> {y [, idx]}; backward -> {dz, dbias}.
+bool bias_relu_supported(const torch::Tensor& x, bool pool);
+std::vector<torch::Tensor> bias_relu_forward(const torch::Tensor& x, const torch::Tensor& bias, bool pool);
+std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const torch::Tensor& y,
+                                              const c10::optional<torch::Tensor>& idx, bool pool);
+
 int* status_word_for(const torch::Tensor& like);
 
 }  // namespace ops

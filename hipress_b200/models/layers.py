@@ -1,6 +1,7 @@
 """Layers of the model zoo that run on this framework's own kernels.
 
 ``MaxPool3x3s2`` is the ResNet stem's pooling layer on a gather-style kernel pair.
+``FusedBiasReLU`` is the epilogue of VGG's convolutions: bias + ReLU (+ 2x2 max pooling).
 
 ``FusedBatchNormAct`` is ``nn.BatchNorm2d`` (same parameters, buffers and state-dict keys)
 whose training-mode forward and backward on channels-last bf16 CUDA activations run on the
@@ -97,3 +98,39 @@ class MaxPool3x3s2(nn.Module):
         if _C is not None and x.is_cuda and _C.maxpool_supported(x):
             return _MaxPoolFunction.apply(x)
         return F.max_pool2d(x, 3, stride=2, padding=1)
+
+
+class _BiasReluFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bias, pool: bool):
+        out = _C.bias_relu_forward(x, bias, pool)
+        ctx.save_for_backward(out[0], out[1] if pool else None)
+        ctx.pool = pool
+        return out[0]
+
+    @staticmethod
+    def backward(ctx, dy):
+        y, idx = ctx.saved_tensors
+        dz, db = _C.bias_relu_backward(dy.contiguous(memory_format=torch.channels_last), y, idx, ctx.pool)
+        return dz, db, None
+
+
+class FusedBiasReLU(nn.Module):
+    """Epilogue of a bias-free convolution: ``relu(x + bias)`` and, with ``pool=True``, the
+    2x2 / stride 2 max pooling that follows it, in one pass on ``csrc/kernels/bias_act.cu``
+    (pooling commutes with the monotonic bias + ReLU, so the full-size activation is never
+    written).  Owns the bias the convolution would have had."""
+
+    def __init__(self, num_features: int, pool: bool = False):
+        super().__init__()
+        self.bias = nn.Parameter(torch.zeros(num_features))
+        self.pool = pool
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if _C is not None and x.is_cuda and _C.bias_relu_supported(x, self.pool):
+            return _BiasReluFunction.apply(x, self.bias, self.pool)
+        y = F.relu(x + self.bias.view(1, -1, 1, 1).to(x.dtype))
+        return F.max_pool2d(y, 2, 2) if self.pool else y
+
+    def extra_repr(self) -> str:
+        return f"{self.bias.numel()}, pool={self.pool}"

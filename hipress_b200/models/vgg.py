@@ -1,8 +1,15 @@
-"""VGG-19: 16 convolutions + classifier 25088 -> 4096 -> 4096 -> 1000 (143.7 M parameters)."""
+"""VGG-19: 16 convolutions + classifier 25088 -> 4096 -> 4096 -> 1000 (143.7 M parameters).
+
+Each convolution is bias-free and followed by ``layers.FusedBiasReLU``, which owns the bias and
+applies bias + ReLU (and the 2x2 max pooling where one follows) in one pass of this framework's
+kernels; parameter count and maths are those of the usual conv(bias) -> ReLU -> pool stack.
+"""
 from __future__ import annotations
 
 import torch
 import torch.nn as nn
+
+from .layers import FusedBiasReLU
 
 CFG19 = [64, 64, "M", 128, 128, "M", 256, 256, 256, 256, "M", 512, 512, 512, 512, "M", 512, 512, 512, 512, "M"]
 
@@ -13,13 +20,13 @@ class VGG(nn.Module):
         super().__init__()
         layers, c = [], 3
         pools = 0
-        for v in cfg:
+        for i, v in enumerate(cfg):
             if v == "M":
-                layers.append(nn.MaxPool2d(2, 2))
-                pools += 1
-            else:
-                layers += [nn.Conv2d(c, v, 3, padding=1), nn.ReLU(inplace=True)]
-                c = v
+                pools += 1          # folded into the preceding epilogue
+                continue
+            pooled = i + 1 < len(cfg) and cfg[i + 1] == "M"
+            layers += [nn.Conv2d(c, v, 3, padding=1, bias=False), FusedBiasReLU(v, pool=pooled)]
+            c = v
         self.features = nn.Sequential(*layers)
         side = in_hw // (2 ** pools)
         self.classifier = nn.Sequential(
@@ -29,7 +36,6 @@ class VGG(nn.Module):
         for m in self.modules():
             if isinstance(m, nn.Conv2d):
                 nn.init.kaiming_normal_(m.weight, mode="fan_out", nonlinearity="relu")
-                nn.init.zeros_(m.bias)
             elif isinstance(m, nn.Linear):
                 nn.init.normal_(m.weight, 0, 0.01)
                 nn.init.zeros_(m.bias)

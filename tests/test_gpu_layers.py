@@ -1,4 +1,5 @@
-"""Fused batch-norm kernels against a plain PyTorch fp32 restatement of the same op."""
+"""Fused layer kernels (batch norm + residual + ReLU, max pooling, bias + ReLU + pooling) against
+plain PyTorch fp32 restatements of the same ops."""
 import pytest
 import torch
 import torch.nn.functional as F
@@ -137,3 +138,50 @@ def test_maxpool_falls_back_for_other_inputs():
     from hipress_b200.models.layers import MaxPool3x3s2
     x = torch.randn(2, 6, 9, 9, device="cuda")
     assert torch.equal(MaxPool3x3s2()(x), F.max_pool2d(x, 3, stride=2, padding=1))
+
+
+@pytest.mark.parametrize("shape", [(2, 64, 32, 32), (3, 8, 6, 10), (1, 512, 14, 14), (2, 256, 8, 8)])
+@pytest.mark.parametrize("pool", [False, True])
+def test_bias_relu_pool_matches_fp32_reference(shape, pool):
+    from hipress_b200.models.layers import FusedBiasReLU
+    torch.manual_seed(0)
+    c = shape[1]
+    x = torch.randn(shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    layer = FusedBiasReLU(c, pool=pool).cuda()
+    with torch.no_grad():
+        layer.bias.uniform_(-0.5, 0.5)
+    xg = x.clone().requires_grad_(True)
+    y = layer(xg)
+    xr = x.float().requires_grad_(True)
+    br = layer.bias.detach().clone().requires_grad_(True)
+    yr = F.relu(xr + br.view(1, -1, 1, 1))
+    if pool:
+        yr = F.max_pool2d(yr, 2, 2)
+    assert y.shape == yr.shape and y.dtype == torch.bfloat16
+    torch.testing.assert_close(y.float(), yr, atol=2e-2, rtol=1e-2)       # one bf16 rounding
+    dy = torch.randn(y.shape, device="cuda").to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+    y.backward(dy)
+    yr.backward(dy.float())
+    # gradients are dy or 0: exact wherever the bf16-rounded output and the fp32 output agree on
+    # y > 0 (an output that rounds to exactly 0 cannot: relu(x + b) > 0 never rounds to 0 in bf16)
+    assert torch.equal(xg.grad.float(), xr.grad)
+    torch.testing.assert_close(layer.bias.grad, br.grad, atol=1e-3, rtol=1e-4)
+
+
+def test_vgg_with_fused_epilogues_trains():
+    from hipress_b200.models import vgg_tiny
+    torch.manual_seed(0)
+    net = vgg_tiny(10).cuda().to(memory_format=torch.channels_last).train()
+    opt = torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9)
+    x = torch.randn(32, 3, 32, 32, device="cuda").contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (32,), device="cuda")
+    losses = []
+    for _ in range(30):
+        opt.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = F.cross_entropy(net(x), y)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < losses[0] - 0.05, losses        # a tiny VGG without normalisation learns slowly
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
