@@ -117,9 +117,10 @@ class OurTrainer:
                                           optimizer="adamw" if args.model == "bert_large" else "sgd",
                                           weight_decay=0.01 if args.model == "bert_large" else 0.0)
         else:
+            whole = bool(args.cuda_graph) and self.algorithm in ("tbq", "terngrad")
             cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
                                     threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=self.bucket_mb,
-                                    num_workers=args.engine_workers)
+                                    num_workers=args.engine_workers, graph_capturable=whole)
             self.model = CompressedDataParallel(net, cfg, lr=self.lr, momentum=0.9, weight_decay=0.0, fused_sgd=True)
 
         self.use_graph = bool(args.cuda_graph)
@@ -143,7 +144,9 @@ class OurTrainer:
             from hipress_b200.parallel.graphed import GraphedTrainStep
             try:
                 self.graphed = GraphedTrainStep(self.model, self._loss, batch)
-                self.graph_note = "forward+backward replayed from one CUDA graph; gradient exchange issued after it"
+                self.graph_note = ("whole step replayed from one CUDA graph (hooks and gradient exchange captured, "
+                                   "epoch kept on the device)" if self.graphed.whole_step else
+                                   "forward+backward replayed from one CUDA graph; gradient exchange issued after it")
             except Exception as exc:  # capture is an optimisation: fall back to eager, and say so
                 self.use_graph = False
                 self.graph_note = f"capture failed, eager: {type(exc).__name__}: {exc}"[:200]

@@ -77,6 +77,7 @@ runtime::EngineConfig config_from(const py::dict& d) {
   c.num_workers = get("num_workers", 1);
   c.defer_recv = get("defer_recv", 0);
   c.clear_grad = get("clear_grad", 0);
+  c.device_epoch = get("device_epoch", 0);
   c.momentum_correction = get("momentum_correction", 0);
   c.dgc_momentum = get("dgc_momentum", 0.9f);
   c.dgc_clip = get("dgc_clip", 0.0f);
@@ -432,7 +433,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("set_adamw", &runtime::DdpEngine::set_adamw, py::arg("lr"), py::arg("beta1") = 0.9f,
            py::arg("beta2") = 0.999f, py::arg("eps") = 1e-8f, py::arg("weight_decay") = 0.0f)
       .def("set_keep_fraction", &runtime::DdpEngine::set_keep_fraction)
-      .def("begin_step", &runtime::DdpEngine::begin_step)
+      .def("begin_step",
+           [](runtime::DdpEngine& e, int device) {
+             if (device < 0) {
+               e.begin_step(nullptr);
+               return;
+             }
+             c10::cuda::CUDAGuard guard(static_cast<c10::DeviceIndex>(device));
+             e.begin_step(at::cuda::getCurrentCUDAStream());
+           },
+           py::arg("device") = -1)
+      .def("end_capture", &runtime::DdpEngine::end_capture)
+      .def("note_replay", &runtime::DdpEngine::note_replay, py::arg("count"), py::arg("launches_per_step"))
       .def("grad_ready",
            [](runtime::DdpEngine& e, int param_index, int device) {
              e.grad_ready(param_index, current_stream(device));

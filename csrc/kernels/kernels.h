@@ -23,13 +23,22 @@ constexpr int kMaxWorld = 8;
 //   flag[p]     flag word of destination p to publish `epoch` to; may be null
 //   done        device counter used to elect the last CTA; must be zero on
 //               entry, is reset to zero by the kernel
+//
+// Steps replayed from a CUDA graph cannot change kernel arguments, so the step's epoch may live
+// on the device instead: when epoch_dev is set, the kernel reads the epoch from it, `payload`
+// holds the addresses for even epochs and odd epochs use the slots parity_stride bytes further
+// (slots are double-buffered by epoch parity), and codecs with a rounding seed add
+// epoch * kEpochSeedStride to it.
 struct PushTargets {
   int world = 0;
   uint8_t* payload[kMaxWorld] = {};
   uint32_t* flag[kMaxWorld] = {};
   uint32_t epoch = 0;
   unsigned int* done = nullptr;
+  const uint32_t* epoch_dev = nullptr;
+  int64_t parity_stride = 0;
 };
+constexpr uint64_t kEpochSeedStride = 0x9E3779B97F4A7C15ull;
 
 // Payloads of all ranks as seen by the receiver, in canonical (ascending rank)
 // accumulation order.
@@ -37,6 +46,8 @@ struct UnpackSources {
   int world = 0;
   const uint8_t* payload[kMaxWorld] = {};
   int64_t payload_bytes[kMaxWorld] = {};  // capacity of each slot (bounds checks)
+  const uint32_t* epoch_dev = nullptr;    // see PushTargets
+  int64_t parity_stride = 0;
 };
 
 // Optional fused SGD-with-momentum update applied to the decoded, averaged
@@ -109,7 +120,9 @@ cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n,
 // Spins (one warp) until flag[r] >= epoch for all r < world, or timeout_ns
 // passes; on timeout writes kFlagTimeout to *status and returns normally.
 cudaError_t wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t timeout_ns,
-                       int* status, cudaStream_t stream);
+                       int* status, cudaStream_t stream, const uint32_t* epoch_dev = nullptr);
+// *epoch_dev += 1: first kernel of a step whose epoch lives on the device (see PushTargets).
+cudaError_t bump_epoch(uint32_t* epoch_dev, cudaStream_t stream);
 // Publishes `epoch` to flag[p] of every destination (release, system scope).
 cudaError_t signal_flags(const PushTargets& dst, cudaStream_t stream);
 

@@ -14,7 +14,8 @@ constexpr int kThreads = 256;
 // time: on expiry the kernel records the failure and returns, the context
 // stays usable and the host decides what to do.
 __global__ void wait_flags_kernel(const uint32_t* flags, int world, uint32_t epoch,
-                                  uint64_t timeout_ns, int* status) {
+                                  const uint32_t* epoch_dev, uint64_t timeout_ns, int* status) {
+  if (epoch_dev != nullptr) epoch = *epoch_dev;
   const int lane = threadIdx.x;
   bool ok = true;
   if (lane < world) {
@@ -35,6 +36,7 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int world, uint32_t epo
 }
 
 __global__ void signal_flags_kernel(PushTargets dst) {
+  resolve_epoch(dst);
   if (threadIdx.x < dst.world && dst.flag[threadIdx.x] != nullptr) {
     __threadfence_system();
     st_release_sys(dst.flag[threadIdx.x], dst.epoch);
@@ -112,9 +114,19 @@ inline int grid_for(int64_t items, int max_blocks) {
 }  // namespace
 
 cudaError_t wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t timeout_ns,
-                       int* status, cudaStream_t stream) {
+                       int* status, cudaStream_t stream, const uint32_t* epoch_dev) {
   if (world < 1 || world > kMaxWorld) return cudaErrorInvalidValue;
-  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, timeout_ns, status);
+  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, epoch_dev, timeout_ns, status);
+  return cudaGetLastError();
+}
+
+namespace {
+__global__ void bump_epoch_kernel(uint32_t* epoch_dev) { *epoch_dev += 1u; }
+}  // namespace
+
+cudaError_t bump_epoch(uint32_t* epoch_dev, cudaStream_t stream) {
+  if (epoch_dev == nullptr) return cudaErrorInvalidValue;
+  bump_epoch_kernel<<<1, 1, 0, stream>>>(epoch_dev);
   return cudaGetLastError();
 }
 

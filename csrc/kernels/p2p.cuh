@@ -36,6 +36,27 @@ __device__ __forceinline__ void store_u32_any(uint8_t* p, uint32_t v) {
   }
 }
 
+// Epoch kept on the device (see PushTargets): fix up the by-value copy of the kernel argument.
+// The counter is written by a kernel earlier in stream order, never concurrently.
+__device__ __forceinline__ void resolve_epoch(PushTargets& t) {
+  if (t.epoch_dev == nullptr) return;
+  const uint32_t e = *t.epoch_dev;
+  t.epoch = e;
+  if (e & 1u) {
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p)
+      if (p < t.world) t.payload[p] += t.parity_stride;
+  }
+}
+__device__ __forceinline__ void resolve_epoch(UnpackSources& s) {
+  if (s.epoch_dev == nullptr) return;
+  if (*s.epoch_dev & 1u) {
+#pragma unroll
+    for (int r = 0; r < kMaxWorld; ++r)
+      if (r < s.world) s.payload[r] += s.parity_stride;
+  }
+}
+
 // The same 4 payload bytes to every destination.
 __device__ __forceinline__ void push_u32(const PushTargets& t, int64_t byte_off, uint32_t v) {
 #pragma unroll

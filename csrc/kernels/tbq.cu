@@ -27,6 +27,7 @@ template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 tbq_compress_kernel(const float* __restrict__ grad, float* __restrict__ residual, int64_t n,
                     float thr, PushTargets dst) {
+  resolve_epoch(dst);
   const int64_t nquads = n >> 2;                    // full bytes
   const int64_t nquads_padded = (nquads + 31) & ~int64_t(31);  // whole warps iterate together
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
@@ -85,6 +86,7 @@ template <bool APPLY>
 __global__ void __launch_bounds__(kUnpackThreads)
 tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
                       float post_scale, SgdApply apply) {
+  resolve_epoch(src);
   // nibble -> 2 decoded values; one 128-byte table shared by all ranks (see unpack_lut.cuh)
   __shared__ __align__(128) float lut[16 * 2];
   uint32_t first[kMaxWorld];

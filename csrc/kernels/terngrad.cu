@@ -39,6 +39,7 @@ template <bool VEC, bool EF>
 __global__ void __launch_bounds__(kThreads)
 minmax_header_kernel(const float* __restrict__ grad, const float* __restrict__ residual, int64_t n,
                      int bw, PushTargets dst, MinMaxScratch* scratch) {
+  resolve_epoch(dst);
   float mn = INFINITY, mx = -INFINITY;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -98,6 +99,8 @@ template <int BW, bool VEC, bool EF>
 __global__ void __launch_bounds__(kThreads)
 tern_quant_kernel(const float* __restrict__ grad, float* __restrict__ residual, int64_t n,
                   int random, uint64_t seed, PushTargets dst, const MinMaxScratch* scratch) {
+  resolve_epoch(dst);
+  if (dst.epoch_dev != nullptr) seed += uint64_t(dst.epoch) * kEpochSeedStride;
   constexpr int DPB = Unit<BW>::DPB, EPT = Unit<BW>::EPT, BPT = Unit<BW>::BPT;
   const float mn = scratch->mn, inv = scratch->inv, gap = scratch->gap;
   const int64_t units = n / EPT;
@@ -221,6 +224,7 @@ template <int BW, bool APPLY>
 __global__ void __launch_bounds__(kUnpackThreads)
 tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
                        float post_scale, SgdApply apply, int* status) {
+  resolve_epoch(src);
   extern __shared__ __align__(16) float lut[];  // [world][256][dpb], byte-table path only
   __shared__ __align__(128) float nib[(BW == 1 || BW == 2 || BW == 4) ? kMaxWorld * 16 * (4 / (BW ? BW : 1)) : 1];
   __shared__ TernHeader hdr[kMaxWorld];

@@ -72,6 +72,14 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   for (auto& e : ready_events_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   check(cudaMalloc(reinterpret_cast<void**>(&status_), 64), "cudaMalloc status");
   check(cudaMemset(status_, 0, 64), "memset status");
+  if (cfg.device_epoch) {
+    if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad)
+      throw std::invalid_argument("device_epoch is implemented for the tbq and terngrad codecs");
+    if (cfg.num_workers >= 1)
+      throw std::invalid_argument("device_epoch needs inline issue (num_workers = 0): a captured step is issued by the capturing thread");
+    check(cudaMalloc(reinterpret_cast<void**>(&epoch_dev_), 64), "cudaMalloc epoch");
+    check(cudaMemset(epoch_dev_, 0, 64), "memset epoch");
+  }
 
   const int nw = cfg.num_workers < 1 ? 1 : cfg.num_workers;
   workers_.resize(static_cast<size_t>(nw));
@@ -85,6 +93,7 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
     check(cudaMalloc(reinterpret_cast<void**>(&w.done), 64), "cudaMalloc counter");
     check(cudaMemset(w.done, 0, 64), "memset counter");
     check(cudaEventCreateWithFlags(&w.tail, cudaEventDisableTiming), "event");
+    check(cudaEventCreateWithFlags(&w.pushed, cudaEventDisableTiming), "event");
   }
   check(cudaDeviceSynchronize(), "sync");
   const int device = cfg.device;
@@ -109,9 +118,11 @@ DdpEngine::~DdpEngine() {
     if (w.scratch) cudaFree(w.scratch);
     if (w.done) cudaFree(w.done);
     if (w.tail) cudaEventDestroy(w.tail);
+    if (w.pushed) cudaEventDestroy(w.pushed);
   }
   for (auto& e : ready_events_) cudaEventDestroy(e);
   if (status_) cudaFree(status_);
+  if (epoch_dev_) cudaFree(epoch_dev_);
 }
 
 void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* momentum, float* aux,
@@ -152,9 +163,16 @@ void DdpEngine::set_keep_fraction(double keep_fraction) {
   keep_fraction_ = keep_fraction;
 }
 
-void DdpEngine::begin_step() {
+void DdpEngine::begin_step(cudaStream_t consumer) {
   if (grad_ == nullptr || bases_.empty()) throw std::runtime_error("hipress engine: buffers not set");
   ++epoch_;
+  launches_at_begin_ = launches_.load();
+  if (epoch_dev_) {
+    // ordered after the previous step (finish_step made `consumer` wait for its last kernels)
+    // and before this step's gradients, whose ready events are recorded on `consumer`
+    check(cuda::bump_epoch(epoch_dev_, consumer), "bump_epoch");
+    launches_ += 1;
+  }
   for (size_t b = 0; b < buckets_.size(); ++b) {
     pending_params_[b].store(buckets_[b].num_params);
     submitted_[b].store(0);
@@ -198,13 +216,29 @@ void DdpEngine::bucket_ready(int b, cudaStream_t producer) {
   });
 }
 
+int64_t DdpEngine::end_capture() {
+  const int64_t per_step = launches_.load() - launches_at_begin_;
+  --epoch_;
+  --steps_;
+  launches_ -= per_step;
+  return per_step;
+}
+
+void DdpEngine::note_replay(int64_t count, int64_t launches_per_step) {
+  epoch_ += static_cast<uint32_t>(count);
+  steps_ += count;
+  launches_ += count * launches_per_step;
+}
+
 cuda::PushTargets DdpEngine::targets_for(int b, WorkerCtx& w) const {
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
-  const int parity = int(epoch_ & 1u);
+  const int parity = epoch_dev_ ? 0 : int(epoch_ & 1u);
   cuda::PushTargets t;
   t.world = cfg_.world;
   t.epoch = epoch_;
   t.done = w.done;
+  t.epoch_dev = epoch_dev_;
+  t.parity_stride = L.slots[1] - L.slots[0];
   for (int p = 0; p < cfg_.world; ++p) {
     uint8_t* base = bases_[static_cast<size_t>(p)];
     t.payload[p] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
@@ -215,9 +249,11 @@ cuda::PushTargets DdpEngine::targets_for(int b, WorkerCtx& w) const {
 
 cuda::UnpackSources DdpEngine::sources_for(int b) const {
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
-  const int parity = int(epoch_ & 1u);
+  const int parity = epoch_dev_ ? 0 : int(epoch_ & 1u);
   cuda::UnpackSources s;
   s.world = cfg_.world;
+  s.epoch_dev = epoch_dev_;
+  s.parity_stride = L.slots[1] - L.slots[0];
   uint8_t* base = bases_[static_cast<size_t>(cfg_.rank)];
   for (int r = 0; r < cfg_.world; ++r) {
     s.payload[r] = base + L.slots[parity] + int64_t(r) * L.slot_bytes + L.shift;
@@ -238,7 +274,9 @@ void DdpEngine::issue_push(int b, int worker) {
   const int64_t n = B.numel;
   float* g = grad_ + B.offset;
   float* res = residual_ ? residual_ + B.offset : nullptr;
-  const uint64_t seed = cfg_.seed + uint64_t(epoch_) * 0x9E3779B97F4A7C15ull + uint64_t(b) * 0x632BE59BD9B4E019ull;
+  // with the epoch on the device the kernel adds the epoch term itself
+  const uint64_t seed = cfg_.seed + (epoch_dev_ ? 0 : uint64_t(epoch_) * cuda::kEpochSeedStride) +
+                        uint64_t(b) * 0x632BE59BD9B4E019ull;
   // ---- push stream: compress and deliver
   check(cudaStreamWaitEvent(w.push, ready_events_[static_cast<size_t>(b)], 0), "wait ready");
   cuda::PushTargets dst = targets_for(b, w);
@@ -298,6 +336,7 @@ void DdpEngine::issue_push(int b, int worker) {
     }
   }
 
+  check(cudaEventRecord(w.pushed, w.push), "record pushed");
   launches_ += launched;
 }
 
@@ -315,13 +354,20 @@ void DdpEngine::issue_recv(int b, int worker) {
     apply.lr = lr_;
     apply.mu = sgd_mu_;
     apply.weight_decay = wd_;
-    apply.first_step = steps_ == 0 ? 1 : 0;
+    // buf = g on the first step equals mu * buf + g with the zero-initialised momentum the
+    // wrappers allocate; a captured step must not bake the first-step flag in
+    apply.first_step = (steps_ == 0 && !epoch_dev_) ? 1 : 0;
     apply.clear_grad = cfg_.clear_grad;
   }
   int launched = 0;
+  // The receive half starts once this rank's own payload and flag are out: the flag wait below
+  // then only ever waits for other GPUs, never for a kernel of this GPU that might not have
+  // been scheduled yet (and, under stream capture, this is what brings the recv stream into
+  // the capture).
+  check(cudaStreamWaitEvent(w.recv, w.pushed, 0), "wait pushed");
   // ---- recv stream: wait for all ranks, decode everything in one pass
   const uint32_t* flags = reinterpret_cast<const uint32_t*>(bases_[static_cast<size_t>(cfg_.rank)] + L.flags);
-  check(cuda::wait_flags(flags, cfg_.world, epoch_, cfg_.flag_timeout_ns, status_, w.recv), "wait_flags");
+  check(cuda::wait_flags(flags, cfg_.world, epoch_, cfg_.flag_timeout_ns, status_, w.recv, epoch_dev_), "wait_flags");
   launched += 1;
   cuda::UnpackSources src = sources_for(b);
   bool applied = false;

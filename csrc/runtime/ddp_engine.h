@@ -64,6 +64,11 @@ struct EngineConfig {
   // The fused optimizer kernel leaves zeros in the gradient bucket instead of the averaged
   // gradient (nobody reads it after a fused update), so no separate clearing pass is needed.
   int clear_grad = 0;
+  // Keep the step's epoch in device memory (TBQ and TernGrad): kernels read the epoch, pick the
+  // slot parity and derive the rounding seed on the device, so that a whole training step --
+  // backward hooks and this engine's launches included -- can be captured once in a CUDA graph
+  // and replayed.  begin_step() then launches a one-thread kernel that advances the counter.
+  int device_epoch = 0;
 };
 
 struct BucketDesc {
@@ -103,7 +108,14 @@ class DdpEngine {
   void set_adamw(float lr, float beta1, float beta2, float eps, float weight_decay);
   void set_keep_fraction(double keep_fraction);
 
-  void begin_step();
+  // `consumer`: the stream the step runs on (only used with device_epoch: the kernel that
+  // advances the epoch is ordered before the step's backward pass on it).
+  void begin_step(cudaStream_t consumer = nullptr);
+  // A step issued while a CUDA graph was being captured did not run: take it back out of the
+  // host-side counters.  Returns the number of kernel launches the captured step holds.
+  int64_t end_capture();
+  // A captured step was replayed `count` times: advance the host-side counters to match.
+  void note_replay(int64_t count, int64_t launches_per_step);
   // Called from a backward hook; `producer` is the stream the gradient was
   // written on.
   void grad_ready(int param_index, cudaStream_t producer);
@@ -132,6 +144,7 @@ class DdpEngine {
     void* scratch = nullptr;       // zeroed; minmax + sparse scratch
     unsigned int* done = nullptr;  // last-CTA counter for publish
     cudaEvent_t tail = nullptr;    // last recorded event on recv
+    cudaEvent_t pushed = nullptr;  // this rank's payload and flag of the latest bucket are out
     bool used = false;
   };
   void issue_bucket(int b, int worker);
@@ -157,6 +170,8 @@ class DdpEngine {
 
   uint32_t epoch_ = 0;
   int64_t steps_ = 0;
+  uint32_t* epoch_dev_ = nullptr;   // device copy of epoch_ (device_epoch mode)
+  int64_t launches_at_begin_ = 0;
   std::vector<std::atomic<int>> pending_params_;
   std::vector<std::atomic<int>> submitted_;
   std::vector<cudaEvent_t> ready_events_;

@@ -53,6 +53,9 @@ class CompressionConfig:
     # itself; -1 = choose (a worker thread once a step has enough launches to be worth moving
     # off the autograd thread, none for a handful of buckets where the hand-off costs more)
     num_workers: int = -1
+    # keep the step's epoch on the device so that the whole step, exchange included, can be
+    # captured in a CUDA graph (tbq / terngrad with the fused SGD; forces inline issue)
+    graph_capturable: bool = False
     # DGC extras (algorithm "dgc"): momentum correction with factor masking, local clipping
     momentum_correction: bool = False
     dgc_momentum: float = 0.9
@@ -180,7 +183,13 @@ class CompressedDataParallel(nn.Module):
         # with a fused optimizer nobody reads the averaged gradient: the kernel that applies the
         # update leaves zeros behind, ready for the next backward pass
         cfg_dict["clear_grad"] = 1 if fused else 0
-        if self.config.num_workers < 0:
+        self.graph_capturable = bool(self.config.graph_capturable)
+        if self.graph_capturable:
+            if self.config.algorithm not in ("tbq", "terngrad") or optimizer != "sgd" or not fused_sgd:
+                raise ValueError("graph_capturable needs tbq or terngrad with the fused SGD")
+            cfg_dict["device_epoch"] = 1
+            cfg_dict["num_workers"] = 0
+        elif self.config.num_workers < 0:
             per_bucket = {"dgc": 12 + world, "graddrop": 10 + world}.get(self.config.algorithm, 4)
             cfg_dict["num_workers"] = 1 if len(self.plan.buckets) * per_bucket > 200 else 0
         self.engine = _C.DdpEngine(cfg_dict, self.plan.buckets, self.plan.param_bucket)
@@ -219,7 +228,7 @@ class CompressedDataParallel(nn.Module):
 
     def begin_step(self) -> None:
         """Arm the engine for one backward pass (called automatically by ``forward``)."""
-        self.engine.begin_step()
+        self.engine.begin_step(self._dev_index)
         self._in_step = True
 
     def step(self) -> None:
@@ -233,6 +242,14 @@ class CompressedDataParallel(nn.Module):
     def zero_grad(self, set_to_none: bool = False) -> None:  # noqa: D401
         """Gradients live in the flat buffer and are views: they are zeroed, never dropped."""
         self.flat_grad.zero_()
+
+    # ---- whole-step CUDA graph capture (GraphedTrainStep)
+    def end_capture(self) -> int:
+        """The step issued during a graph capture did not run: undo its host-side accounting."""
+        return int(self.engine.end_capture())
+
+    def note_replay(self, launches_per_step: int, count: int = 1) -> None:
+        self.engine.note_replay(count, launches_per_step)
 
     def grad_buffers(self):
         """The buffers a backward pass accumulates into (saved and restored around a graph capture)."""

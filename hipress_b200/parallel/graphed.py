@@ -1,15 +1,24 @@
-"""Whole forward + backward of a data-parallel wrapper captured in one CUDA graph.
+"""A training step replayed from one CUDA graph.
 
 At the batch sizes this framework is benchmarked on (64 images or 32 sequences per GPU) a
 B200 finishes the kernels of a training step faster than eager PyTorch can launch them: the
-step time is the host's, not the device's.  ``GraphedTrainStep`` captures the model's forward,
-loss and backward once (static input buffers, gradients accumulating into the wrapper's flat
-gradient buffer exactly as in eager mode) and replays them with a single launch per step.  The
-gradient exchange itself stays outside the graph: its kernels take the step's epoch (flag
-values, slot parity, rounding seed) as arguments, which a replayed graph could not change.
-After the replay every bucket is handed to the engine at once; on NVLink the exchange of a
-whole model is a few hundred microseconds, so losing the overlap with backward costs less
-than the launch gaps it removes.
+step time is the host's, not the device's.  ``GraphedTrainStep`` captures the step once
+(static input buffers, gradients accumulating into the wrapper's flat gradient buffer exactly
+as in eager mode) and replays it with a single launch.
+
+Two capture scopes:
+
+* **Whole step** (wrappers created with ``CompressionConfig(graph_capturable=True)``: TBQ and
+  TernGrad with the fused SGD).  The engine keeps the step's epoch -- flag values, slot parity,
+  rounding seed -- in device memory, advanced by a one-thread kernel at the start of the step,
+  so nothing in its launches changes from step to step.  The capture then contains
+  ``begin_step``, forward, backward *with the gradient hooks firing* and ``step``: every bucket
+  is compressed, pushed to the peers, unpacked and applied on the engine's side streams as soon
+  as its gradients exist, overlapping the rest of backward, exactly as in eager mode.
+* **Forward + backward only** (every other wrapper).  The exchange takes host-side arguments
+  per step and stays outside the graph; all buckets are handed to the engine right after the
+  replay.  On NVLink the exchange of a whole model costs a few hundred microseconds, less than
+  the launch gaps removed.
 
 The reference has no training loop (its caller drives ``submit_task`` per tensor,
 ref hp_cuda.cpp:776-853); this is part of the data-parallel layer built on top of the codecs.
@@ -23,7 +32,7 @@ import torch
 
 class GraphedTrainStep:
     """``loss = step(*inputs)`` runs one full training step: copy the inputs into the captured
-    buffers, replay forward + backward, exchange and apply the gradients.
+    buffers, replay, and (forward + backward scope only) exchange and apply the gradients.
 
     ``fn(module, *inputs)`` must return the scalar loss (it chooses its own autocast).
     ``ddp`` is any wrapper of this package (``begin_step`` / ``step`` / ``grad_buffers``).
@@ -33,6 +42,7 @@ class GraphedTrainStep:
     def __init__(self, ddp, fn: Callable, example_inputs: Sequence[torch.Tensor], warmup: int = 3):
         self.ddp = ddp
         self.fn = fn
+        self.whole_step = bool(getattr(ddp, "graph_capturable", False))
         self.static_inputs = [t.clone() for t in example_inputs]
         saved = [g.clone() for g in ddp.grad_buffers()]
         ddp.hooks_enabled = False
@@ -45,9 +55,19 @@ class GraphedTrainStep:
             torch.cuda.current_stream().wait_stream(side)
             self._restore(saved)
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph):
-                self.loss = fn(ddp.module, *self.static_inputs)
-                self.loss.backward()
+            if self.whole_step:
+                ddp.hooks_enabled = True
+                with torch.cuda.graph(self.graph):
+                    ddp.begin_step()
+                    self.loss = fn(ddp.module, *self.static_inputs)
+                    self.loss.backward()
+                    ddp.step()
+                # nothing ran: the step issued during the capture comes back out of the counters
+                self.launches_per_step = ddp.end_capture()
+            else:
+                with torch.cuda.graph(self.graph):
+                    self.loss = fn(ddp.module, *self.static_inputs)
+                    self.loss.backward()
             self._restore(saved)
         finally:
             ddp.hooks_enabled = True
@@ -60,6 +80,10 @@ class GraphedTrainStep:
     def __call__(self, *inputs: torch.Tensor) -> torch.Tensor:
         for dst, src in zip(self.static_inputs, inputs):
             dst.copy_(src, non_blocking=True)
+        if self.whole_step:
+            self.graph.replay()
+            self.ddp.note_replay(self.launches_per_step)
+            return self.loss
         self.ddp.begin_step()
         self.ddp.hooks_enabled = False       # nothing fires during a replay; guards an eager fallback
         try:

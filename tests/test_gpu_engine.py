@@ -33,6 +33,9 @@ def make_engines(codec, world, n, **kw):
     ("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)),
     ("terngrad", dict(bitwidth=4, enable_random=0, error_feedback=0)),
     ("tbq", dict(threshold=0.01)),
+    # epoch, slot parity and rounding seed resolved on the device (CUDA-graph capturable steps)
+    ("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1, device_epoch=1, num_workers=0)),
+    ("tbq", dict(threshold=0.01, device_epoch=1, num_workers=0)),
     ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05)),
     ("ecq", dict(bitwidth=4, alpha=1.0, beta=0.9)),
     ("dense", dict()),
