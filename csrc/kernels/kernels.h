@@ -193,6 +193,20 @@ cudaError_t bias_relu_backward(const void* dy, const void* y, const uint8_t* idx
                                float* partial, int n, int h, int w, int channels, int pool,
                                cudaStream_t stream);
 
+// ---------------------------------------------------------------- residual add + LayerNorm
+// Rows of `hidden` bf16 features (hidden % 8 == 0, <= 2048), gamma / beta fp32.
+//   forward:  z = bf16(x + delta) (written when delta is given; otherwise z = x), y = LN(z);
+//             mean / rstd: one fp32 value per row, for backward.
+//   backward: dz (= gradient of x and of delta), dgamma, dbeta; partial = add_ln_partial_elems floats.
+bool add_ln_supported(int64_t rows, int hidden);
+int64_t add_ln_partial_elems(int64_t rows, int hidden);
+cudaError_t add_ln_forward(const void* x, const void* delta, const float* gamma, const float* beta, void* y,
+                           void* z, float* mean, float* rstd, int64_t rows, int hidden, float eps,
+                           cudaStream_t stream);
+cudaError_t add_ln_backward(const void* dy, const void* z, const float* mean, const float* rstd,
+                            const float* gamma, void* dz, float* dgamma, float* dbeta, float* partial,
+                            int64_t rows, int hidden, cudaStream_t stream);
+
 // ---------------------------------------------------------------- max pooling
 // 3x3, stride 2, padding 1 over channels-last bf16 [n][h][w][c] (c a multiple of 8).  The forward
 // writes y [n][ho][wo][c] (ho = (h-1)/2 + 1) and one byte per output element: the winning window

@@ -199,5 +199,56 @@ std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const tor
   return {dz, db};
 }
 
+// ---------------------------------------------------------------- residual add + LayerNorm
+namespace {
+int64_t ln_rows(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kBFloat16 && t.is_contiguous() && t.dim() >= 1, name,
+              " must be a contiguous bf16 CUDA tensor");
+  return t.numel() / t.size(-1);
+}
+}  // namespace
+
+bool add_ln_supported(const torch::Tensor& x) {
+  return x.is_cuda() && x.scalar_type() == torch::kBFloat16 && x.is_contiguous() && x.dim() >= 1 &&
+         x.numel() > 0 && cuda::add_ln_supported(x.numel() / x.size(-1), int(x.size(-1)));
+}
+
+std::vector<torch::Tensor> add_ln_forward(const torch::Tensor& x, const c10::optional<torch::Tensor>& delta,
+                                          const torch::Tensor& weight, const torch::Tensor& bias, double eps) {
+  TORCH_CHECK(add_ln_supported(x), "add_layer_norm: unsupported input");
+  const int64_t rows = ln_rows(x, "x");
+  const int hidden = int(x.size(-1));
+  const bool add = delta && delta->defined();
+  if (add) TORCH_CHECK(ln_rows(*delta, "delta") == rows && delta->sizes() == x.sizes(), "delta must have x's shape");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = torch::empty_like(x);
+  torch::Tensor z = add ? torch::empty_like(x) : x;
+  auto stats = torch::empty({2, rows}, x.options().dtype(torch::kFloat32));
+  HP_BN_CHECK(cuda::add_ln_forward(x.data_ptr(), add ? delta->data_ptr() : nullptr, opt_f32(weight, hidden, "weight"),
+                                   opt_f32(bias, hidden, "bias"), y.data_ptr(), add ? z.data_ptr() : nullptr,
+                                   stats.data_ptr<float>(), stats.data_ptr<float>() + rows, rows, hidden, float(eps),
+                                   at::cuda::getCurrentCUDAStream()));
+  return {y, z, stats};
+}
+
+std::vector<torch::Tensor> add_ln_backward(const torch::Tensor& dy, const torch::Tensor& z, const torch::Tensor& stats,
+                                           const torch::Tensor& weight) {
+  const int64_t rows = ln_rows(z, "z");
+  const int hidden = int(z.size(-1));
+  TORCH_CHECK(ln_rows(dy, "dy") == rows && dy.sizes() == z.sizes(), "dy must have z's shape");
+  TORCH_CHECK(stats.is_cuda() && stats.scalar_type() == torch::kFloat32 && stats.is_contiguous() &&
+                  stats.numel() == 2 * rows, "stats must be the tensor returned by add_ln_forward");
+  c10::cuda::CUDAGuard guard(z.device());
+  auto dz = torch::empty_like(z);
+  auto f32 = z.options().dtype(torch::kFloat32);
+  auto dwb = torch::empty({2, hidden}, f32);
+  auto partial = torch::empty({cuda::add_ln_partial_elems(rows, hidden)}, f32);
+  HP_BN_CHECK(cuda::add_ln_backward(dy.data_ptr(), z.data_ptr(), stats.data_ptr<float>(),
+                                    stats.data_ptr<float>() + rows, opt_f32(weight, hidden, "weight"), dz.data_ptr(),
+                                    dwb.data_ptr<float>(), dwb.data_ptr<float>() + hidden, partial.data_ptr<float>(),
+                                    rows, hidden, at::cuda::getCurrentCUDAStream()));
+  return {dz, dwb[0], dwb[1]};
+}
+
 }  // namespace ops
 }  // namespace hipress

@@ -110,6 +110,14 @@ std::vector<torch::Tensor> bias_relu_forward(const torch::Tensor& x, const torch
 std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const torch::Tensor& y,
                                               const c10::optional<torch::Tensor>& idx, bool pool);
 
+// y = LayerNorm(x + delta) over the last dimension of contiguous bf16 tensors (delta optional).
+// forward -> {y, z = bf16(x + delta) (x itself without delta), stats}; backward -> {dz, dweight, dbias}.
+bool add_ln_supported(const torch::Tensor& x);
+std::vector<torch::Tensor> add_ln_forward(const torch::Tensor& x, const c10::optional<torch::Tensor>& delta,
+                                          const torch::Tensor& weight, const torch::Tensor& bias, double eps);
+std::vector<torch::Tensor> add_ln_backward(const torch::Tensor& dy, const torch::Tensor& z, const torch::Tensor& stats,
+                                           const torch::Tensor& weight);
+
 int* status_word_for(const torch::Tensor& like);
 
 }  // namespace ops

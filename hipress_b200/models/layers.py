@@ -2,6 +2,7 @@
 
 ``MaxPool3x3s2`` is the ResNet stem's pooling layer on a gather-style kernel pair.
 ``FusedBiasReLU`` is the epilogue of VGG's convolutions: bias + ReLU (+ 2x2 max pooling).
+``FusedAddLayerNorm`` is BERT's residual add + LayerNorm on a bf16 residual stream.
 
 ``FusedBatchNormAct`` is ``nn.BatchNorm2d`` (same parameters, buffers and state-dict keys)
 whose training-mode forward and backward on channels-last bf16 CUDA activations run on the
@@ -134,3 +135,34 @@ class FusedBiasReLU(nn.Module):
 
     def extra_repr(self) -> str:
         return f"{self.bias.numel()}, pool={self.pool}"
+
+
+class _AddLayerNormFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, delta, weight, bias, eps: float):
+        y, z, stats = _C.add_ln_forward(x, delta, weight, bias, eps)
+        ctx.save_for_backward(z, stats, weight)
+        ctx.has_delta = delta is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        z, stats, weight = ctx.saved_tensors
+        dz, dw, db = _C.add_ln_backward(dy.contiguous(), z, stats, weight)
+        return dz, (dz if ctx.has_delta else None), dw, db, None
+
+
+class FusedAddLayerNorm(nn.LayerNorm):
+    """``LayerNorm(x + delta)`` (``delta`` optional) with ``nn.LayerNorm``'s parameters.  bf16 CUDA
+    inputs run on ``csrc/kernels/layernorm.cu`` and keep the residual stream in bf16 (autocast
+    would run the stock LayerNorm, the add before it and everything between them in fp32);
+    anything else takes the stock path."""
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if (_C is not None and x.is_cuda and x.dtype == torch.bfloat16 and self.elementwise_affine
+                and (delta is None or (delta.dtype == x.dtype and delta.shape == x.shape))):
+            xc = x.contiguous()
+            if _C.add_ln_supported(xc):
+                return _AddLayerNormFunction.apply(xc, None if delta is None else delta.contiguous(),
+                                                   self.weight, self.bias, float(self.eps))
+        return super().forward(x if delta is None else x + delta)
