@@ -8,26 +8,38 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .layers import FusedAddLayerNorm
+
 
 class BertLayer(nn.Module):
+    """Post-LN transformer layer.  Separate query / key / value projections give the attention
+    kernel three dense [batch, seq, heads, head_dim] operands and its output the same layout, so
+    neither forward nor backward needs a permute copy or a concatenation of the three gradients;
+    residual add + LayerNorm run fused on a bf16 residual stream (``layers.FusedAddLayerNorm``)."""
+
     def __init__(self, hidden: int, heads: int, ffn: int, dropout: float):
         super().__init__()
         self.heads = heads
-        self.qkv = nn.Linear(hidden, 3 * hidden)
+        self.q = nn.Linear(hidden, hidden)
+        self.k = nn.Linear(hidden, hidden)
+        self.v = nn.Linear(hidden, hidden)
         self.out = nn.Linear(hidden, hidden)
-        self.ln1 = nn.LayerNorm(hidden, eps=1e-12)
+        self.ln1 = FusedAddLayerNorm(hidden, eps=1e-12)
         self.fc1 = nn.Linear(hidden, ffn)
         self.fc2 = nn.Linear(ffn, hidden)
-        self.ln2 = nn.LayerNorm(hidden, eps=1e-12)
+        self.ln2 = FusedAddLayerNorm(hidden, eps=1e-12)
         self.drop = nn.Dropout(dropout)
 
     def forward(self, x):
         b, s, h = x.shape
-        q, k, v = self.qkv(x).view(b, s, 3, self.heads, h // self.heads).permute(2, 0, 3, 1, 4)
+        shape = (b, s, self.heads, h // self.heads)
+        q = self.q(x).view(shape).transpose(1, 2)
+        k = self.k(x).view(shape).transpose(1, 2)
+        v = self.v(x).view(shape).transpose(1, 2)
         a = F.scaled_dot_product_attention(q, k, v)
         a = a.transpose(1, 2).reshape(b, s, h)
-        x = self.ln1(x + self.drop(self.out(a)))
-        return self.ln2(x + self.drop(self.fc2(F.gelu(self.fc1(x)))))
+        x = self.ln1(x, self.drop(self.out(a)))
+        return self.ln2(x, self.drop(self.fc2(F.gelu(self.fc1(x)))))
 
 
 class BertForMaskedLM(nn.Module):
@@ -37,11 +49,11 @@ class BertForMaskedLM(nn.Module):
         self.tok = nn.Embedding(vocab, hidden)
         self.pos = nn.Embedding(max_pos, hidden)
         self.typ = nn.Embedding(2, hidden)
-        self.ln = nn.LayerNorm(hidden, eps=1e-12)
+        self.ln = FusedAddLayerNorm(hidden, eps=1e-12)
         self.drop = nn.Dropout(dropout)
         self.layers = nn.ModuleList(BertLayer(hidden, heads, ffn, dropout) for _ in range(layers))
         self.head_dense = nn.Linear(hidden, hidden)
-        self.head_ln = nn.LayerNorm(hidden, eps=1e-12)
+        self.head_ln = FusedAddLayerNorm(hidden, eps=1e-12)
         self.head_bias = nn.Parameter(torch.zeros(vocab))
         self.apply(self._init)
 
@@ -55,7 +67,10 @@ class BertForMaskedLM(nn.Module):
     def forward(self, ids: torch.Tensor, labels: torch.Tensor | None = None):
         b, s = ids.shape
         pos = torch.arange(s, device=ids.device)
-        x = self.drop(self.ln(self.tok(ids) + self.pos(pos)[None] + self.typ.weight[0]))
+        emb = self.tok(ids) + self.pos(pos)[None] + self.typ.weight[0]
+        if emb.is_cuda and torch.is_autocast_enabled():
+            emb = emb.to(torch.get_autocast_dtype("cuda"))   # the residual stream runs in the compute dtype
+        x = self.drop(self.ln(emb))
         for layer in self.layers:
             x = layer(x)
         if labels is None:

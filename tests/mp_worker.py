@@ -50,7 +50,7 @@ def check_codec(codec, kw, rank, world, local):
     for step in range(3):
         cpu_grads = [gauss(n, 0.01, 1000 * step + r) for r in range(world)]
         grad.copy_(cpu_grads[rank])
-        eng.begin_step()
+        eng.begin_step(local)
         eng.bucket_ready(0, local)
         eng.finish_step(local)
         torch.cuda.synchronize()
@@ -101,6 +101,11 @@ def main():
         check_codec(codec, kw, rank, world, local)
         if rank == 0:
             print(f"MP_OK codec_{codec}", flush=True)
+    # the same protocol with the epoch, slot parity and seed resolved on the device
+    for codec, kw in [("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)), ("tbq", dict(threshold=0.01))]:
+        check_codec(codec, dict(kw, device_epoch=1, num_workers=0), rank, world, local)
+        if rank == 0:
+            print(f"MP_OK codec_{codec}_device_epoch", flush=True)
 
     # DDP wrapper: replicas stay bit-identical, loss goes down
     torch.manual_seed(0)
@@ -121,6 +126,27 @@ def main():
     assert min(losses[-3:]) < losses[0]
     if rank == 0:
         print("MP_OK ddp_terngrad", flush=True)
+
+    # whole training step (hooks + exchange) replayed from one CUDA graph on every rank
+    from hipress_b200.parallel import GraphedTrainStep
+
+    def loss_fn(module, a, b):
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            return torch.nn.functional.cross_entropy(module(a), b)
+
+    torch.manual_seed(0)
+    net = resnet_tiny(10).cuda().to(memory_format=torch.channels_last)
+    gm = CompressedDataParallel(net, CompressionConfig("terngrad", bucket_mb=0.05, graph_capturable=True),
+                                lr=0.05, momentum=0.9)
+    xc = x.contiguous(memory_format=torch.channels_last)
+    step = GraphedTrainStep(gm, loss_fn, (xc, y))
+    assert step.whole_step
+    losses = [float(step(xc, y).detach()) for _ in range(10)]
+    gm.check()
+    assert same_on_all_ranks(gm.flat_param), "graphed replicas diverged"
+    assert min(losses[-3:]) < losses[0]
+    if rank == 0:
+        print("MP_OK ddp_graphed", flush=True)
 
     torch.manual_seed(0)
     net = vgg_tiny(10).cuda()

@@ -185,3 +185,64 @@ def test_vgg_with_fused_epilogues_trains():
         losses.append(float(loss.detach()))
     assert losses[-1] < losses[0] - 0.05, losses        # a tiny VGG without normalisation learns slowly
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
+
+
+@pytest.mark.parametrize("shape", [(4, 128, 1024), (3, 7, 64), (5, 256), (2, 33, 1536), (1, 9, 2048), (6, 40)])
+@pytest.mark.parametrize("with_delta", [True, False])
+def test_add_layer_norm_matches_fp32_reference(shape, with_delta):
+    from hipress_b200.models.layers import FusedAddLayerNorm
+    torch.manual_seed(0)
+    h = shape[-1]
+    x = (torch.randn(shape, device="cuda") * 1.3 + 0.2).to(torch.bfloat16)
+    d = torch.randn(shape, device="cuda").to(torch.bfloat16) if with_delta else None
+    layer = FusedAddLayerNorm(h, eps=1e-12).cuda()
+    with torch.no_grad():
+        layer.weight.uniform_(0.5, 1.5)
+        layer.bias.uniform_(-0.5, 0.5)
+    xg = x.clone().requires_grad_(True)
+    dg = d.clone().requires_grad_(True) if with_delta else None
+    y = layer(xg, dg)
+    assert y.dtype == torch.bfloat16 and y.shape == x.shape
+    dy = torch.randn(shape, device="cuda").to(torch.bfloat16)
+    y.backward(dy)
+
+    # restatement: the sum rounded to bf16 (what the kernel normalises), everything else fp32
+    z = (x.float() + d.float()).to(torch.bfloat16).float() if with_delta else x.float()
+    zr = z.detach().requires_grad_(True)
+    wr, br = layer.weight.detach().clone().requires_grad_(True), layer.bias.detach().clone().requires_grad_(True)
+    yr = F.layer_norm(zr, (h,), wr, br, 1e-12)
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, atol=3e-2, rtol=2e-2)
+    torch.testing.assert_close(xg.grad.float(), zr.grad, atol=3e-2, rtol=3e-2)
+    if with_delta:
+        assert torch.equal(dg.grad, xg.grad)
+    rows = x.numel() // h
+    torch.testing.assert_close(layer.weight.grad, wr.grad, atol=2e-3 * rows ** 0.5 + 1e-3, rtol=1e-3)
+    torch.testing.assert_close(layer.bias.grad, br.grad, atol=2e-3 * rows ** 0.5 + 1e-3, rtol=1e-3)
+
+
+def test_add_layer_norm_stock_path_for_fp32():
+    from hipress_b200.models.layers import FusedAddLayerNorm
+    layer = FusedAddLayerNorm(48).cuda()
+    x, d = torch.randn(4, 48, device="cuda"), torch.randn(4, 48, device="cuda")
+    torch.testing.assert_close(layer(x, d), F.layer_norm(x + d, (48,), layer.weight, layer.bias, layer.eps))
+
+
+def test_bert_tiny_trains_on_bf16_residual_stream():
+    from hipress_b200.models import bert_tiny
+    torch.manual_seed(0)
+    net = bert_tiny().cuda().train()
+    opt = torch.optim.AdamW(net.parameters(), lr=1e-3)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 1000, (8, 32), generator=g).cuda()
+    labels = torch.where(torch.rand(8, 32, generator=g) < 0.15, ids.cpu(), torch.full((8, 32), -100)).cuda()
+    losses = []
+    for _ in range(30):
+        opt.zero_grad()
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = net(ids, labels)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss.detach()))
+    assert losses[-1] < losses[0] - 0.5, losses
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
