@@ -174,6 +174,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_ln_forward", &ops::add_ln_forward, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("bias"),
         py::arg("eps"));
   m.def("add_ln_backward", &ops::add_ln_backward, py::arg("dy"), py::arg("z"), py::arg("stats"), py::arg("weight"));
+  m.def("colsum_supported", &ops::colsum_supported, py::arg("dy"));
+  m.def("colsum", &ops::colsum, py::arg("dy"));
   m.def("psgd_kpad", &cuda::psgd_kpad, py::arg("k"));
   m.def("gram_schmidt", &ops::gram_schmidt, py::arg("P"), py::arg("eps") = 1e-8);
   m.def("psgd_expand_feedback", &ops::psgd_expand_feedback, py::arg("P"), py::arg("Q"), py::arg("M"),

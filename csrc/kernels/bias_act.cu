@@ -160,6 +160,38 @@ bias_relu_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* 
   if (int(threadIdx.x) < ct) partial[int64_t(blockIdx.y) * C + blockIdx.x * ct + threadIdx.x] = S;
 }
 
+// Column sums of a [rows][C] bf16 matrix (the bias gradient of a linear layer): per-CTA partial
+// sums here, colsum_finalize_kernel after.
+__global__ void __launch_bounds__(kBnThreads)
+colsum_partial_kernel(const __nv_bfloat16* __restrict__ dy, float* __restrict__ partial, int64_t M, int C,
+                      int tx_count, int64_t rows_per_block) {
+  __shared__ float sh[2 * kBnThreads * kBnVec];
+  const Lane l = lane_of(tx_count, M, rows_per_block);
+  float s[kBnVec], unused[kBnVec];
+#pragma unroll
+  for (int k = 0; k < kBnVec; ++k) s[k] = unused[k] = 0.f;
+  int64_t r = l.r_begin + l.ty;
+  for (; r + 3 * l.TY < l.r_end; r += 4 * l.TY) {
+    float g[4][kBnVec];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) load8(dy + (r + u * l.TY) * C + l.c0, g[u]);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+#pragma unroll
+      for (int k = 0; k < kBnVec; ++k) s[k] += g[u][k];
+  }
+  for (; r < l.r_end; r += l.TY) {
+    float g[kBnVec];
+    load8(dy + r * C + l.c0, g);
+#pragma unroll
+    for (int k = 0; k < kBnVec; ++k) s[k] += g[k];
+  }
+  float S, ignored;
+  reduce_rows(s, unused, tx_count, sh, S, ignored);
+  const int ct = tx_count * kBnVec;
+  if (int(threadIdx.x) < ct) partial[int64_t(blockIdx.y) * C + blockIdx.x * ct + threadIdx.x] = S;
+}
+
 constexpr int kSumThreads = 1024;
 constexpr int kSumWarps = kSumThreads / 32;
 
@@ -200,6 +232,17 @@ int64_t bias_relu_partial_elems(int64_t rows, int channels) {
   Geom g;
   if (!geometry(rows, channels, &g)) return 0;
   return int64_t(g.row_blocks) * channels;
+}
+
+cudaError_t colsum_bf16(const void* dy, float* out, float* partial, int64_t rows, int channels,
+                        cudaStream_t stream) {
+  Geom g;
+  if (!dy || !out || !partial || !geometry(rows, channels, &g)) return cudaErrorInvalidValue;
+  const dim3 grid(static_cast<unsigned>(g.tiles), static_cast<unsigned>(g.row_blocks), 1);
+  colsum_partial_kernel<<<grid, kBnThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(dy), partial, rows,
+                                                         channels, g.tx, g.rows_per_block);
+  colsum_finalize_kernel<<<(channels + 31) / 32, kSumThreads, 0, stream>>>(partial, g.row_blocks, channels, out);
+  return cudaGetLastError();
 }
 
 cudaError_t bias_relu_forward(const void* x, const float* bias, void* y, uint8_t* idx, int n, int h, int w,

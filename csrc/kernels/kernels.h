@@ -188,6 +188,10 @@ bool bias_relu_supported(int64_t rows, int channels);
 int64_t bias_relu_partial_elems(int64_t rows, int channels);
 cudaError_t bias_relu_forward(const void* x, const float* bias, void* y, uint8_t* idx, int n, int h, int w,
                               int channels, int pool, cudaStream_t stream);
+// out[c] = sum over rows of dy[row][c] (bf16 in, fp32 out): the bias gradient of a linear layer.
+// partial = bias_relu_partial_elems(rows, c) floats of scratch.
+cudaError_t colsum_bf16(const void* dy, float* out, float* partial, int64_t rows, int channels,
+                        cudaStream_t stream);
 // dz [n][h][w][c] = gradient w.r.t. the convolution output, dbias [c] fp32.
 cudaError_t bias_relu_backward(const void* dy, const void* y, const uint8_t* idx, void* dz, float* dbias,
                                float* partial, int n, int h, int w, int channels, int pool,

@@ -199,6 +199,25 @@ std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const tor
   return {dz, db};
 }
 
+// ---------------------------------------------------------------- column sums (bias gradients)
+bool colsum_supported(const torch::Tensor& dy) {
+  return dy.is_cuda() && dy.scalar_type() == torch::kBFloat16 && dy.is_contiguous() && dy.dim() >= 2 &&
+         dy.numel() > 0 && cuda::bias_relu_supported(dy.numel() / dy.size(-1), int(dy.size(-1)));
+}
+
+torch::Tensor colsum(const torch::Tensor& dy) {
+  TORCH_CHECK(colsum_supported(dy), "colsum: needs a contiguous bf16 CUDA tensor whose last dimension / 8 is a power of two up to 32 or a multiple of 32");
+  const int64_t rows = dy.numel() / dy.size(-1);
+  const int c = int(dy.size(-1));
+  c10::cuda::CUDAGuard guard(dy.device());
+  auto f32 = dy.options().dtype(torch::kFloat32);
+  auto out = torch::empty({c}, f32);
+  auto partial = torch::empty({cuda::bias_relu_partial_elems(rows, c)}, f32);
+  HP_BN_CHECK(cuda::colsum_bf16(dy.data_ptr(), out.data_ptr<float>(), partial.data_ptr<float>(), rows, c,
+                                at::cuda::getCurrentCUDAStream()));
+  return out;
+}
+
 // ---------------------------------------------------------------- residual add + LayerNorm
 namespace {
 int64_t ln_rows(const torch::Tensor& t, const char* name) {

@@ -110,6 +110,10 @@ std::vector<torch::Tensor> bias_relu_forward(const torch::Tensor& x, const torch
 std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const torch::Tensor& y,
                                               const c10::optional<torch::Tensor>& idx, bool pool);
 
+// Sum over all leading dimensions of a contiguous bf16 tensor -> fp32 [last dim] (bias gradients).
+bool colsum_supported(const torch::Tensor& dy);
+torch::Tensor colsum(const torch::Tensor& dy);
+
 // y = LayerNorm(x + delta) over the last dimension of contiguous bf16 tensors (delta optional).
 // forward -> {y, z = bf16(x + delta) (x itself without delta), stats}; backward -> {dz, dweight, dbias}.
 bool add_ln_supported(const torch::Tensor& x);

@@ -8,7 +8,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .layers import FusedAddLayerNorm
+from .layers import FusedAddLayerNorm, FusedLinear
 
 
 class BertLayer(nn.Module):
@@ -20,13 +20,13 @@ class BertLayer(nn.Module):
     def __init__(self, hidden: int, heads: int, ffn: int, dropout: float):
         super().__init__()
         self.heads = heads
-        self.q = nn.Linear(hidden, hidden)
-        self.k = nn.Linear(hidden, hidden)
-        self.v = nn.Linear(hidden, hidden)
-        self.out = nn.Linear(hidden, hidden)
+        self.q = FusedLinear(hidden, hidden)
+        self.k = FusedLinear(hidden, hidden)
+        self.v = FusedLinear(hidden, hidden)
+        self.out = FusedLinear(hidden, hidden)
         self.ln1 = FusedAddLayerNorm(hidden, eps=1e-12)
-        self.fc1 = nn.Linear(hidden, ffn)
-        self.fc2 = nn.Linear(ffn, hidden)
+        self.fc1 = FusedLinear(hidden, ffn)
+        self.fc2 = FusedLinear(ffn, hidden)
         self.ln2 = FusedAddLayerNorm(hidden, eps=1e-12)
         self.drop = nn.Dropout(dropout)
 
@@ -52,7 +52,7 @@ class BertForMaskedLM(nn.Module):
         self.ln = FusedAddLayerNorm(hidden, eps=1e-12)
         self.drop = nn.Dropout(dropout)
         self.layers = nn.ModuleList(BertLayer(hidden, heads, ffn, dropout) for _ in range(layers))
-        self.head_dense = nn.Linear(hidden, hidden)
+        self.head_dense = FusedLinear(hidden, hidden)
         self.head_ln = FusedAddLayerNorm(hidden, eps=1e-12)
         self.head_bias = nn.Parameter(torch.zeros(vocab))
         self.apply(self._init)

@@ -246,3 +246,27 @@ def test_bert_tiny_trains_on_bf16_residual_stream():
         losses.append(float(loss.detach()))
     assert losses[-1] < losses[0] - 0.5, losses
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in net.parameters())
+
+
+@pytest.mark.parametrize("shape,out", [((4, 128, 1024), 1024), ((3, 7, 64), 256), ((40, 64), 8), ((2, 5, 96), 100)])
+def test_fused_linear_matches_autocast_linear(shape, out):
+    from hipress_b200.models.layers import FusedLinear
+    torch.manual_seed(0)
+    fused = FusedLinear(shape[-1], out).cuda()
+    stock = torch.nn.Linear(shape[-1], out).cuda()
+    stock.load_state_dict(fused.state_dict())
+    x = torch.randn(shape, device="cuda").to(torch.bfloat16)
+    dy = torch.randn(*shape[:-1], out, device="cuda").to(torch.bfloat16)
+    xa, xb = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        ya, yb = fused(xa), stock(xb)
+    assert ya.dtype == torch.bfloat16
+    torch.testing.assert_close(ya, yb, atol=2e-2, rtol=2e-2)
+    ya.backward(dy)
+    yb.backward(dy)
+    assert fused.weight.grad.dtype == torch.float32 and fused.bias.grad.dtype == torch.float32
+    torch.testing.assert_close(xa.grad, xb.grad, atol=5e-2, rtol=2e-2)
+    # fp32 accumulation and output here, bf16-rounded output in the stock path
+    ref_w = dy.reshape(-1, out).float().t() @ x.reshape(-1, shape[-1]).float()
+    torch.testing.assert_close(fused.weight.grad, ref_w, atol=2e-2 * ref_w.abs().max().item(), rtol=2e-2)
+    torch.testing.assert_close(fused.bias.grad, dy.reshape(-1, out).float().sum(0), atol=1e-2, rtol=1e-3)
