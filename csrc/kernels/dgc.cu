@@ -29,7 +29,13 @@ sumsq_kernel(const float* __restrict__ g, int64_t n, float* __restrict__ out) {
   __shared__ float sh[kThreads / 32];
   float acc = 0.f;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) acc += g[i] * g[i];
+  const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nv = (reinterpret_cast<uintptr_t>(g) & 15) == 0 ? (n >> 2) : 0;  // 16-byte loads when aligned
+  for (int64_t i = tid; i < nv; i += stride) {
+    const float4 a = reinterpret_cast<const float4*>(g)[i];
+    acc += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+  }
+  for (int64_t i = (nv << 2) + tid; i < n; i += stride) acc += g[i] * g[i];
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = acc;
   __syncthreads();
@@ -50,7 +56,26 @@ dgc_accumulate_kernel(const float* __restrict__ g, float* __restrict__ u, float*
     s = fminf(1.0f, clip / (norm + 1e-6f));
   }
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+  const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(u) |
+                     reinterpret_cast<uintptr_t>(v)) & 15) == 0;
+  const int64_t nv = vec ? (n >> 2) : 0;
+  for (int64_t i = tid; i < nv; i += stride) {
+    const float4 g4 = reinterpret_cast<const float4*>(g)[i];
+    float4 u4 = reinterpret_cast<float4*>(u)[i];
+    float4 v4 = reinterpret_cast<float4*>(v)[i];
+    u4.x = momentum * u4.x + s * g4.x;
+    u4.y = momentum * u4.y + s * g4.y;
+    u4.z = momentum * u4.z + s * g4.z;
+    u4.w = momentum * u4.w + s * g4.w;
+    v4.x += u4.x;
+    v4.y += u4.y;
+    v4.z += u4.z;
+    v4.w += u4.w;
+    reinterpret_cast<float4*>(u)[i] = u4;
+    reinterpret_cast<float4*>(v)[i] = v4;
+  }
+  for (int64_t i = (nv << 2) + tid; i < n; i += stride) {
     const float uu = momentum * u[i] + s * g[i];
     u[i] = uu;
     v[i] += uu;

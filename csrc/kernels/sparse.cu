@@ -199,16 +199,24 @@ count_kernel(const float* __restrict__ grad, float* __restrict__ R, int64_t n, i
   const int64_t begin = int64_t(blockIdx.x) * chunk;
   const int64_t end = begin + chunk < n ? begin + chunk : n;
   unsigned int mine = 0;
-  for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
-    float r = R[i];
-    if (accumulate) {
-      r = hp_add(grad[i], r);
+  if (!accumulate) {
+    // read-only pass (DGC: the velocity was accumulated by its own kernel): 16-byte loads
+    for_each_value(R, begin, end, [&](float r) {
+      const uint32_t key = abs_key(r);
+      if (key > thr_key) {
+        ++mine;
+        atomicAdd(&sh[digit_of(key, 0)], 1u);
+      }
+    });
+  } else {
+    for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
+      const float r = hp_add(grad[i], R[i]);
       R[i] = r;
-    }
-    const uint32_t key = abs_key(r);
-    if (key > thr_key) {
-      ++mine;
-      atomicAdd(&sh[digit_of(key, 0)], 1u);
+      const uint32_t key = abs_key(r);
+      if (key > thr_key) {
+        ++mine;
+        atomicAdd(&sh[digit_of(key, 0)], 1u);
+      }
     }
   }
   atomicAdd(&blk_cnt, mine);
