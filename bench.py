@@ -263,7 +263,7 @@ class ReferenceTrainer:
 def reference_unavailable_reason():
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not any(f.startswith("hp_cuda") and f.endswith(".so") for f in (os.listdir(ref_dir) if os.path.isdir(ref_dir) else [])):
-        return "baseline/_ref has no built hp_cuda extension (install the reference first, see DESIGN.md)"
+        return "baseline/_ref has no built hp_cuda extension (pip install the reference sources with --target baseline/_ref first)"
     return None
 
 

@@ -25,7 +25,7 @@ from hipress_b200 import ops  # noqa: E402
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference-dir", default=os.environ.get("HIPRESS_REFERENCE_DIR", "/root/reference"))
+    ap.add_argument("--reference-dir", default=os.environ.get("HIPRESS_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference")))
     ap.add_argument("--n", type=int, default=1 << 22)
     ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()

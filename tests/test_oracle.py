@@ -23,7 +23,7 @@ from hipress_b200 import ops
 import hipress_b200 as hp
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.environ.get("HIPRESS_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("HIPRESS_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))  # a sibling checkout
 GOLDEN = os.path.join(ROOT, "tests", "golden", "roundtrip_config.json")
 
 
