@@ -47,7 +47,9 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="terngrad",
                     choices=["terngrad", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q",
-                             "psgd_expand", "sgd", "adamw", "terngrad_unpack_apply", "bn_fwd", "bn_bwd"])
+                             "psgd_expand", "sgd", "adamw", "terngrad_unpack_apply", "bn_fwd", "bn_bwd",
+                             "bias_relu_pool_fwd", "bias_relu_pool_bwd", "add_ln_fwd", "add_ln_bwd", "maxpool_fwd",
+                             "maxpool_bwd"])
     ap.add_argument("--mb", type=float, default=64.0)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--world", type=int, default=8, help="payload count for the unpack kernels")
@@ -142,6 +144,51 @@ def main():
             dy = torch.randn(shape, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
             fn = lambda: hp._C.bn_backward(dy, x, y, w, stats, True, True)
             traffic = nbytes * 8          # reduce: dy, x, y; elemt: dy, x, y -> dx, dres
+        n = x.numel()
+    elif k in ("bias_relu_pool_fwd", "bias_relu_pool_bwd", "maxpool_fwd", "maxpool_bwd"):
+        # a VGG-19 block-1 / ResNet stem activation: [N, 64, 224, 224] (or 112) bf16 channels-last, --mb = its size
+        import hipress_b200 as hp
+        c, hw = 64, (224 if k.startswith("bias") else 112)
+        imgs = max(1, int(args.mb * (1 << 20) / 2 / (c * hw * hw)))
+        x = torch.randn(imgs, c, hw, hw, device=dev).to(torch.bfloat16).contiguous(memory_format=torch.channels_last)
+        nbytes = x.numel() * 2
+        if k.startswith("bias"):
+            b = torch.randn(c, device=dev)
+            y, idx = hp._C.bias_relu_forward(x, b, True)
+            dy = torch.randn_like(y)
+            if k.endswith("fwd"):
+                fn = lambda: hp._C.bias_relu_forward(x, b, True)
+                traffic = nbytes * (1 + 0.25 + 0.125)          # read x, write y (1/4) and one index byte per output
+            else:
+                fn = lambda: hp._C.bias_relu_backward(dy, y, idx, True)
+                traffic = nbytes * (0.25 + 0.25 + 0.125 + 1)   # read dy, y, idx; write dz
+        else:
+            y, idx = hp._C.maxpool3x3s2_forward(x)
+            dy = torch.randn_like(y)
+            if k.endswith("fwd"):
+                fn = lambda: hp._C.maxpool3x3s2_forward(x)
+                traffic = nbytes * (1 + 0.25 + 0.125)
+            else:
+                fn = lambda: hp._C.maxpool3x3s2_backward(dy, idx, hw, hw)
+                traffic = nbytes * (0.25 + 0.125 + 1)
+        n = x.numel()
+    elif k in ("add_ln_fwd", "add_ln_bwd"):
+        # BERT-large residual stream: [tokens, 1024] bf16, --mb = its size (8 MB = the benchmark's 4096 tokens)
+        import hipress_b200 as hp
+        hsz = 1024
+        rows = max(1, int(args.mb * (1 << 20) / 2 / hsz))
+        x = torch.randn(rows, hsz, device=dev).to(torch.bfloat16)
+        d = torch.randn(rows, hsz, device=dev).to(torch.bfloat16)
+        w, b = torch.ones(hsz, device=dev), torch.zeros(hsz, device=dev)
+        y, z, stats = hp._C.add_ln_forward(x, d, w, b, 1e-12)
+        dy = torch.randn_like(y)
+        nbytes = x.numel() * 2
+        if k.endswith("fwd"):
+            fn = lambda: hp._C.add_ln_forward(x, d, w, b, 1e-12)
+            traffic = nbytes * 4          # read x, delta; write z, y
+        else:
+            fn = lambda: hp._C.add_ln_backward(dy, z, stats, w)
+            traffic = nbytes * 3          # read dy, z; write dz
         n = x.numel()
     elif k == "adamw":
         import hipress_b200 as hp

@@ -8,12 +8,16 @@
 // the residual stream in fp32 because autocast pins LayerNorm to fp32: a cast, an fp32 add, an
 // fp32 LayerNorm, a cast back, and in backward a separate (slow) gamma/beta reduction -- about
 // a fifth of the step for tensors of 8 MB.  Here one warp owns a row (16-byte accesses, row
-// held in registers, two-pass variance), and gamma/beta gradients are accumulated per lane over
-// the rows a warp visits, combined per CTA in shared memory and finished by a small column-sum
-// kernel (fixed order, deterministic).  The reference has no model code.
+// held in registers, two-pass variance).  Backward is two light kernels: the input gradient row
+// by row, and the gamma / beta sums column by column (a thread owns 8 columns and walks a range
+// of rows, geometry of nhwc.cuh) finished by a small column-sum kernel in fixed order.  A first
+// version did both in one kernel with per-lane gamma / beta accumulators: 196 registers, one
+// CTA per SM, 0.34 of the copy bandwidth; it remains as the path for feature counts the column
+// geometry does not cover.  The reference has no model code.
 #include <cuda_bf16.h>
 
 #include "kernels.h"
+#include "nhwc.cuh"
 
 namespace hipress {
 namespace cuda {
@@ -196,6 +200,101 @@ add_ln_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __r
   }
 }
 
+// Input gradient only (no gamma / beta accumulators: a third of the registers of the combined
+// kernel above, so several CTAs share an SM).  Used together with ln_wgrad_partial_kernel.
+template <int CHUNKS>
+__global__ void __launch_bounds__(kLnThreads)
+add_ln_dz_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
+                 const float* __restrict__ mean, const float* __restrict__ rstd,
+                 const float* __restrict__ gamma, __nv_bfloat16* __restrict__ dz, int64_t rows, int H) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_h = 1.0f / float(H);
+  for (int64_t r = int64_t(blockIdx.x) * kLnWarps + warp; r < rows; r += int64_t(gridDim.x) * kLnWarps) {
+    const float mu = mean[r], rs = rstd[r];
+    float g[CHUNKS][8], xh[CHUNKS][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < H) {
+        ln_load8(dy + r * H + col, g[c]);
+        ln_load8(z + r * H + col, xh[c]);
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + col);
+        const float4 g1 = *reinterpret_cast<const float4*>(gamma + col + 4);
+        const float gam[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          xh[c][k] = (xh[c][k] - mu) * rs;
+          g[c][k] *= gam[k];
+          s1 += g[c][k];
+          s2 += g[c][k] * xh[c][k];
+        }
+      }
+    }
+    const float c1 = warp_sum(s1) * inv_h, c2 = warp_sum(s2) * inv_h;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < H) {
+        float o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = rs * (g[c][k] - c1 - xh[c][k] * c2);
+        *reinterpret_cast<uint4*>(dz + r * H + col) = ln_pack8(o);
+      }
+    }
+  }
+}
+
+// Column sums for dgamma (dy * xhat) and dbeta (dy): a thread owns 8 columns and walks a range of
+// rows (geometry of nhwc.cuh), per-CTA partials in the layout ln_colsum_kernel reads.
+__global__ void __launch_bounds__(kBnThreads)
+ln_wgrad_partial_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ z,
+                        const float* __restrict__ mean, const float* __restrict__ rstd,
+                        float* __restrict__ partial, int64_t rows, int H, int tx_count, int64_t rows_per_block) {
+  __shared__ float sh[2 * kBnThreads * kBnVec];
+  const Lane l = lane_of(tx_count, rows, rows_per_block);
+  float dg[kBnVec], db[kBnVec];
+#pragma unroll
+  for (int k = 0; k < kBnVec; ++k) dg[k] = db[k] = 0.f;
+  int64_t r = l.r_begin + l.ty;
+  for (; r + l.TY < l.r_end; r += 2 * l.TY) {
+    float g[2][kBnVec], v[2][kBnVec], mu[2], rs[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      load8(dy + (r + u * l.TY) * H + l.c0, g[u]);
+      load8(z + (r + u * l.TY) * H + l.c0, v[u]);
+      mu[u] = mean[r + u * l.TY];
+      rs[u] = rstd[r + u * l.TY];
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int k = 0; k < kBnVec; ++k) {
+        db[k] += g[u][k];
+        dg[k] += g[u][k] * (v[u][k] - mu[u]) * rs[u];
+      }
+  }
+  for (; r < l.r_end; r += l.TY) {
+    float g[kBnVec], v[kBnVec];
+    load8(dy + r * H + l.c0, g);
+    load8(z + r * H + l.c0, v);
+    const float mu = mean[r], rs = rstd[r];
+#pragma unroll
+    for (int k = 0; k < kBnVec; ++k) {
+      db[k] += g[k];
+      dg[k] += g[k] * (v[k] - mu) * rs;
+    }
+  }
+  float DG, DB;
+  reduce_rows(dg, db, tx_count, sh, DG, DB);
+  const int ct = tx_count * kBnVec;
+  if (int(threadIdx.x) < ct) {
+    const int col = blockIdx.x * ct + threadIdx.x;
+    partial[(int64_t(blockIdx.y) * 2 + 0) * H + col] = DG;
+    partial[(int64_t(blockIdx.y) * 2 + 1) * H + col] = DB;
+  }
+}
+
 constexpr int kLnSumThreads = 1024;
 constexpr int kLnSumWarps = kLnSumThreads / 32;
 
@@ -237,7 +336,11 @@ int ln_grid(int64_t rows) {
 
 bool add_ln_supported(int64_t rows, int hidden) { return rows >= 1 && hidden >= 8 && hidden % 8 == 0 && hidden <= 2048; }
 
-int64_t add_ln_partial_elems(int64_t rows, int hidden) { return int64_t(ln_grid(rows)) * 2 * hidden; }
+int64_t add_ln_partial_elems(int64_t rows, int hidden) {
+  Geom g;
+  const int64_t blocks = geometry(rows, hidden, &g) && g.row_blocks > ln_grid(rows) ? g.row_blocks : ln_grid(rows);
+  return blocks * 2 * hidden;
+}
 
 cudaError_t add_ln_forward(const void* x, const void* delta, const float* gamma, const float* beta, void* y,
                            void* z, float* mean, float* rstd, int64_t rows, int hidden, float eps,
@@ -271,8 +374,27 @@ cudaError_t add_ln_backward(const void* dy, const void* z, const float* mean, co
   const auto* gb = static_cast<const __nv_bfloat16*>(dy);
   const auto* zb = static_cast<const __nv_bfloat16*>(z);
   auto* ob = static_cast<__nv_bfloat16*>(dz);
-  const int grid = ln_grid(rows);
   const int chunks = (hidden + 255) / 256;
+  Geom g;
+  if (geometry(rows, hidden, &g)) {
+    // two light kernels: the input gradient row by row, the gamma / beta sums column by column
+    int64_t dz_blocks = (rows + kLnWarps - 1) / kLnWarps;
+    if (dz_blocks > 148 * 8) dz_blocks = 148 * 8;
+    const int dz_grid = int(dz_blocks);
+#define HP_LN_DZ(C) add_ln_dz_kernel<C><<<dz_grid, kLnThreads, 0, stream>>>(gb, zb, mean, rstd, gamma, ob, rows, hidden)
+    if (chunks <= 1) HP_LN_DZ(1);
+    else if (chunks <= 2) HP_LN_DZ(2);
+    else if (chunks <= 4) HP_LN_DZ(4);
+    else HP_LN_DZ(8);
+#undef HP_LN_DZ
+    ln_wgrad_partial_kernel<<<dim3(static_cast<unsigned>(g.tiles), static_cast<unsigned>(g.row_blocks), 1), kBnThreads, 0,
+                              stream>>>(gb, zb, mean, rstd, partial, rows, hidden, g.tx, g.rows_per_block);
+    ln_colsum_kernel<<<dim3(static_cast<unsigned>((hidden + 31) / 32), 2, 1), kLnSumThreads, 0, stream>>>(
+        partial, g.row_blocks, hidden, dgamma, dbeta);
+    return cudaGetLastError();
+  }
+  // feature counts the column geometry does not cover: one combined kernel
+  const int grid = ln_grid(rows);
 #define HP_LN_BWD(C) add_ln_bwd_kernel<C><<<grid, kLnThreads, 0, stream>>>(gb, zb, mean, rstd, gamma, ob, partial, rows, hidden)
   if (chunks <= 1) HP_LN_BWD(1);
   else if (chunks <= 2) HP_LN_BWD(2);
