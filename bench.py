@@ -44,6 +44,8 @@ def parse():
                     help="gradient bucket size (default 25; 128 for the sparse codecs, whose per-bucket cost is a dozen launches)")
     ap.add_argument("--cuda-graph", type=int, default=1,
                     help="1 = replay forward+backward from one CUDA graph (ours only), 0 = eager")
+    ap.add_argument("--dgc-whole-step", type=int, default=0,
+                    help="1 = capture DGC's exchange and AdamW inside the CUDA graph too (device-resident epoch)")
     ap.add_argument("--dgc-start-step", type=int, default=400,
                     help="position in DGC's 400-step sparsity warm-up at which the run starts (400 = steady state)")
     return ap.parse_args()
@@ -110,7 +112,8 @@ class OurTrainer:
             from hipress_b200.parallel.dgc import DGCDataParallel
             # measured in the steady state: the 400-step sparsity warm-up is skipped, not shortened
             self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4, bucket_mb=self.bucket_mb,
-                                         start_step=args.dgc_start_step)
+                                         start_step=args.dgc_start_step,
+                                         graph_capturable=bool(args.cuda_graph and args.dgc_whole_step))
         elif self.algorithm == "nccl":
             from hipress_b200.parallel.baseline import NcclDataParallel
             self.model = NcclDataParallel(net, lr=self.lr, momentum=0.9, bucket_mb=self.bucket_mb,
@@ -281,7 +284,10 @@ def run(args):
     pinned = make_batches(args.model, batch, rank)
     resident = [tuple(t.to(dev) for t in b) for b in pinned.batches]
 
-    # ---- warm-up (untimed)
+    # ---- warm-up (untimed).  The clock sampler starts here, ahead of the timed region, so that
+    # nvidia-smi is up and sampling when the (short) region begins; its marks delimit the region.
+    clocks = ClockSampler(local)
+    clocks.__enter__()
     for i in range(max(args.warmup, 3)):
         trainer.step(resident[i % len(resident)])
     barrier()
@@ -289,13 +295,17 @@ def run(args):
     # ---- device-timed region: exactly K steps, inputs resident (per-step working set >> L2)
     launches0 = trainer.launches()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    try:
         barrier()
+        clocks.mark_start()
         start.record()
         for i in range(args.steps):
             trainer.step(resident[i % len(resident)])
         stop.record()
         barrier()
+        clocks.mark_end()
+    finally:
+        clocks.__exit__(None, None, None)
     ms = max_over_ranks(start.elapsed_time(stop), dev)
     launches1 = trainer.launches()
     clock_summary = clocks.summary()
@@ -353,7 +363,8 @@ def run(args):
                    "cuda_graph": getattr(trainer, "graph_note", "off"),
                    "cache": "inputs+activations per step exceed the 126 MB L2; 4 distinct batches rotate"},
         "clocks": {"sm_mhz": clock_summary["sm_mhz"], "sm_max_mhz": clock_summary["sm_max_mhz"],
-                   "reasons": clock_summary["reasons"]},
+                   "reasons": clock_summary["reasons"], "samples": clock_summary.get("samples", 0),
+                   "window": clock_summary.get("window", "")},
         "e2e": {"value": round(e2e_value, 2), "unit": unit, "h2d_bytes_per_step": pinned.bytes_per_batch,
                 "d2h_bytes_per_step": 4, "last_loss": last},
         "gpu_launches": (launches1 - launches0) if launches0 is not None else None,

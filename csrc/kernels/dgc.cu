@@ -85,7 +85,8 @@ dgc_accumulate_kernel(const float* __restrict__ g, float* __restrict__ u, float*
 // u[idx] = 0 for every index of a sparse payload; also clears the clip scratch.
 __global__ void __launch_bounds__(kThreads)
 dgc_mask_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restrict__ u, int64_t n,
-                float* __restrict__ sumsq) {
+                float* __restrict__ sumsq, const uint32_t* epoch_dev, int64_t parity_stride) {
+  if (epoch_dev != nullptr && (*epoch_dev & 1u)) payload += parity_stride;  // see PushTargets
   uint32_t total = 0;
   for (int k = 0; k < 4; ++k) total |= uint32_t(payload[k]) << (8 * k);
   if (blockIdx.x == 0 && threadIdx.x == 0 && sumsq != nullptr) *sumsq = 0.f;
@@ -112,8 +113,9 @@ __device__ __forceinline__ void adamw_one(const AdamWApply& a, float bc1, float 
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 adamw_kernel(float* __restrict__ grad, float scale, AdamWApply a, int64_t n) {
-  const float bc1 = 1.0f - powf(a.beta1, float(a.step));
-  const float rsqrt_bc2 = 1.0f / sqrtf(1.0f - powf(a.beta2, float(a.step)));
+  const float step = float(a.step_dev != nullptr ? int(*a.step_dev) : a.step);
+  const float bc1 = 1.0f - powf(a.beta1, step);
+  const float rsqrt_bc2 = 1.0f / sqrtf(1.0f - powf(a.beta2, step));
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   const int64_t nv = VEC ? (n >> 2) : 0;
@@ -156,11 +158,12 @@ cudaError_t dgc_accumulate(const float* grad, float* u, float* v, int64_t n, flo
 }
 
 cudaError_t dgc_mask(const uint8_t* payload, int64_t payload_capacity, float* u, int64_t n,
-                     float* sumsq_scratch, cudaStream_t stream) {
+                     float* sumsq_scratch, cudaStream_t stream, const uint32_t* epoch_dev,
+                     int64_t parity_stride) {
   if (n <= 0 || (reinterpret_cast<uintptr_t>(payload) & 3)) return cudaErrorInvalidValue;
   const int64_t kmax = (payload_capacity - 4) / 8;
   dgc_mask_kernel<<<grid_for(kmax, 148 * 4), kThreads, 0, stream>>>(payload, payload_capacity, u, n,
-                                                                    sumsq_scratch);
+                                                                    sumsq_scratch, epoch_dev, parity_stride);
   return cudaGetLastError();
 }
 

@@ -146,7 +146,8 @@ cudaError_t dgc_accumulate(const float* grad, float* u, float* v, int64_t n, flo
                            float clip, float* sumsq_scratch, cudaStream_t stream);
 // Momentum factor masking: u[idx] = 0 for every index in the sparse payload.
 cudaError_t dgc_mask(const uint8_t* payload, int64_t payload_capacity, float* u, int64_t n,
-                     float* sumsq_scratch, cudaStream_t stream);
+                     float* sumsq_scratch, cudaStream_t stream, const uint32_t* epoch_dev = nullptr,
+                     int64_t parity_stride = 0);
 struct AdamWApply {
   float* param = nullptr;
   float* exp_avg = nullptr;
@@ -154,6 +155,7 @@ struct AdamWApply {
   float lr = 0.f, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0.f;
   int step = 1;  // 1-based
   int clear_grad = 0;  // write zeros over grad after reading it (see SgdApply::clear_grad)
+  const uint32_t* step_dev = nullptr;  // when set, the step count is read from the device (graph replays)
 };
 // Fused AdamW (decoupled weight decay, bias correction) on g = scale*grad.
 cudaError_t adamw_apply_dense(float* grad, float scale, const AdamWApply& apply, int64_t n,

@@ -154,7 +154,8 @@ template <int ROUND>
 __global__ void __launch_bounds__(kThreads)
 sample_round_kernel(const float* __restrict__ grad, const float* __restrict__ R, int64_t n,
                     int64_t sample_cnt, unsigned int rank0, uint64_t seed, int accumulate,
-                    SparseScratch* s) {
+                    SparseScratch* s, const uint32_t* epoch_dev) {
+  if (epoch_dev != nullptr) seed += uint64_t(*epoch_dev) * kEpochSeedStride;  // see PushTargets
   __shared__ unsigned int sh[kBins];
   for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
   uint32_t prefix = 0;
@@ -301,6 +302,7 @@ recount_kernel(const float* __restrict__ R, int64_t n, int64_t chunk, unsigned i
 // ---- one CTA: offsets, k, header, housekeeping
 __global__ void __launch_bounds__(1024)
 scan_kernel(int blocks, PushTargets dst, SparseScratch* s) {
+  resolve_epoch(dst);
   __shared__ unsigned int a[1024], b[1024];
   const int t = threadIdx.x;
   a[t] = t < blocks ? s->cnt_gt[t] : 0;
@@ -337,6 +339,7 @@ scan_kernel(int blocks, PushTargets dst, SparseScratch* s) {
 __global__ void __launch_bounds__(kThreads)
 write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
              const SparseScratch* s) {
+  resolve_epoch(dst);
   __shared__ unsigned int warp_k[kThreads / 32], warp_e[kThreads / 32];
   __shared__ unsigned int run_k, run_e;
   const uint32_t cut = s->cut_key;
@@ -451,7 +454,8 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
 
 __global__ void __launch_bounds__(kThreads)
 scatter_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restrict__ out, int64_t n,
-               float post_scale, int* status) {
+               float post_scale, int* status, const uint32_t* epoch_dev, int64_t parity_stride) {
+  if (epoch_dev != nullptr && (*epoch_dev & 1u)) payload += parity_stride;  // see UnpackSources
   uint32_t total = 0;
   for (int k = 0; k < 4; ++k) total |= uint32_t(payload[k]) << (8 * k);
   if (total < 4 || int64_t(total) > cap) {
@@ -509,9 +513,9 @@ cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sampl
   if (sample_cnt > 0) {
     int64_t sb = (sample_cnt + kThreads - 1) / kThreads;
     if (sb > kMaxBlocks) sb = kMaxBlocks;
-    sample_round_kernel<0><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s);
-    sample_round_kernel<1><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s);
-    sample_round_kernel<2><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s);
+    sample_round_kernel<0><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s, dst.epoch_dev);
+    sample_round_kernel<1><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s, dst.epoch_dev);
+    sample_round_kernel<2><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s, dst.epoch_dev);
   }
   count_kernel<<<pl.blocks, kThreads, 0, stream>>>(grad, R, n, pl.chunk, sample_cnt, unsigned(rank0), accumulate, s);
   trim_round_kernel<1><<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
@@ -539,7 +543,8 @@ cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n,
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 8) blocks = 148 * 8;
     scatter_kernel<<<int(blocks), kThreads, 0, stream>>>(src.payload[r], src.payload_bytes[r], out,
-                                                        n, post_scale, status);
+                                                        n, post_scale, status, src.epoch_dev,
+                                                        src.parity_stride);
   }
   return cudaGetLastError();
 }

@@ -73,8 +73,8 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   check(cudaMalloc(reinterpret_cast<void**>(&status_), 64), "cudaMalloc status");
   check(cudaMemset(status_, 0, 64), "memset status");
   if (cfg.device_epoch) {
-    if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad)
-      throw std::invalid_argument("device_epoch is implemented for the tbq and terngrad codecs");
+    if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad && cfg.codec != Codec::kSparse)
+      throw std::invalid_argument("device_epoch is implemented for the tbq, terngrad, graddrop and dgc codecs");
     if (cfg.num_workers >= 1)
       throw std::invalid_argument("device_epoch needs inline issue (num_workers = 0): a captured step is issued by the capturing thread");
     check(cudaMalloc(reinterpret_cast<void**>(&epoch_dev_), 64), "cudaMalloc epoch");
@@ -312,7 +312,7 @@ void DdpEngine::issue_push(int b, int worker) {
       launched += 9;
       if (cfg_.momentum_correction) {
         check(cuda::dgc_mask(dst.payload[cfg_.rank], L.slot_bytes - L.shift, aux_ + B.offset, n, sumsq,
-                             w.push),
+                             w.push, dst.epoch_dev, dst.parity_stride),
               "dgc_mask");
         launched += 1;
       }
@@ -416,6 +416,7 @@ void DdpEngine::issue_recv(int b, int worker) {
     aw.eps = eps_;
     aw.weight_decay = wd_;
     aw.step = int(steps_) + 1;
+    aw.step_dev = epoch_dev_;   // one epoch per step: the device counter is the 1-based step count
     aw.clear_grad = cfg_.clear_grad;
     check(cuda::adamw_apply_dense(g, 1.0f, aw, n, w.recv), "adamw_apply_dense");
     launched += 1;

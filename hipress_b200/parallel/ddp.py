@@ -54,7 +54,8 @@ class CompressionConfig:
     # off the autograd thread, none for a handful of buckets where the hand-off costs more)
     num_workers: int = -1
     # keep the step's epoch on the device so that the whole step, exchange included, can be
-    # captured in a CUDA graph (tbq / terngrad with the fused SGD; forces inline issue)
+    # captured in a CUDA graph (tbq / terngrad / graddrop / dgc with a fused optimizer; forces
+    # inline issue)
     graph_capturable: bool = False
     # DGC extras (algorithm "dgc"): momentum correction with factor masking, local clipping
     momentum_correction: bool = False
@@ -185,8 +186,8 @@ class CompressedDataParallel(nn.Module):
         cfg_dict["clear_grad"] = 1 if fused else 0
         self.graph_capturable = bool(self.config.graph_capturable)
         if self.graph_capturable:
-            if self.config.algorithm not in ("tbq", "terngrad") or optimizer != "sgd" or not fused_sgd:
-                raise ValueError("graph_capturable needs tbq or terngrad with the fused SGD")
+            if self.config.algorithm not in ("tbq", "terngrad", "graddrop", "dgc") or not fused:
+                raise ValueError("graph_capturable needs tbq, terngrad, graddrop or dgc with a fused optimizer")
             cfg_dict["device_epoch"] = 1
             cfg_dict["num_workers"] = 0
         elif self.config.num_workers < 0:

@@ -35,7 +35,8 @@ class DGCDataParallel(CompressedDataParallel):
     def __init__(self, module: nn.Module, keep_fraction: float = 0.001, *, sample_rate: float = 0.01,
                  warmup_steps: int = 400, momentum_correction: float = 0.9, clip_norm: float = 1.0,
                  lr: float = 1e-4, weight_decay: float = 0.01, optimizer: str = "adamw",
-                 bucket_mb: float = 25.0, seed: int = 1, start_step: int = 0, **kw):
+                 bucket_mb: float = 25.0, seed: int = 1, start_step: int = 0,
+                 graph_capturable: bool = False, **kw):
         # start_step: position in the warm-up schedule of the first step (resuming a run, or
         # measuring the steady state without running the warm-up first)
         self.start_step = int(start_step)
@@ -43,7 +44,8 @@ class DGCDataParallel(CompressedDataParallel):
         max_keep = max(k for _, k in self.schedule)
         cfg = CompressionConfig("dgc", keep_fraction=max_keep, sample_rate=sample_rate, bucket_mb=bucket_mb,
                                 seed=seed, momentum_correction=momentum_correction > 0,
-                                dgc_momentum=momentum_correction, clip_norm=clip_norm)
+                                dgc_momentum=momentum_correction, clip_norm=clip_norm,
+                                graph_capturable=graph_capturable)
         super().__init__(module, cfg, lr=lr, momentum=0.0, weight_decay=weight_decay, fused_sgd=True,
                          optimizer=optimizer, **kw)
         self.target_keep = keep_fraction
@@ -62,3 +64,12 @@ class DGCDataParallel(CompressedDataParallel):
     def begin_step(self) -> None:
         self._apply_schedule(self.start_step + self.engine.steps)
         super().begin_step()
+
+    def end_capture(self) -> int:
+        """A captured step keeps the sparsity it was captured with: only the steady state (after the
+        warm-up schedule) may be replayed from a graph."""
+        step = self.start_step + self.engine.steps - 1      # the step that was just captured
+        if self.keep_fraction_at(step) != self.target_keep:
+            raise RuntimeError("DGC: capture the training step after the sparsity warm-up "
+                               f"(step {step} of {self.schedule[-1][0]})")
+        return super().end_capture()

@@ -36,6 +36,7 @@ def make_engines(codec, world, n, **kw):
     # epoch, slot parity and rounding seed resolved on the device (CUDA-graph capturable steps)
     ("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1, device_epoch=1, num_workers=0)),
     ("tbq", dict(threshold=0.01, device_epoch=1, num_workers=0)),
+    ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05, device_epoch=1, num_workers=0)),
     ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05)),
     ("ecq", dict(bitwidth=4, alpha=1.0, beta=0.9)),
     ("dense", dict()),

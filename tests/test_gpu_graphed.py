@@ -115,3 +115,31 @@ def test_whole_step_capture_matches_eager(algorithm):
     assert (graphed.flat_param - eager.flat_param).abs().mean().item() < 2e-3
     assert int(graphed.flat_grad.abs().sum()) == 0           # left cleared by the fused update
     assert all(l == l for l in losses)
+
+
+def test_whole_step_capture_dgc_adamw():
+    """DGC (momentum correction, clipping) with the fused AdamW: exchange and optimizer captured
+    with the step; the step count of the bias correction comes from the device epoch."""
+    from hipress_b200.parallel.dgc import DGCDataParallel
+    torch.manual_seed(0)
+    base = resnet_tiny(10).cuda().train()
+    data = batches(6)
+
+    def make(capturable):
+        return DGCDataParallel(copy.deepcopy(base), keep_fraction=0.05, sample_rate=0.1, warmup_steps=0, lr=1e-3,
+                               bucket_mb=0.05, graph_capturable=capturable)
+
+    eager, graphed = make(False), make(True)
+    for x, y in data:
+        image_loss(eager, x, y).backward()
+        eager.step()
+    step = GraphedTrainStep(graphed, image_loss, data[0])
+    assert step.whole_step
+    losses = [float(step(x, y).detach()) for x, y in data]
+    eager.check()
+    graphed.check()
+    assert graphed.engine.steps == eager.engine.steps == len(data)
+    assert all(l == l for l in losses)
+    # same selection rule, seeds and optimizer maths; cuDNN algorithm choice is the only freedom
+    torch.testing.assert_close(graphed.flat_param, eager.flat_param, atol=2e-2, rtol=0)
+    assert (graphed.flat_param - eager.flat_param).abs().mean().item() < 1e-3

@@ -28,3 +28,34 @@ def test_time_cost_checkpoints():
     assert [k for k, _ in iv] == ["a", "b"]
     assert 8 <= iv[0][1] < 200 and 15 <= iv[1][1] < 300
     assert "[a]" in t.print_by_us() and "ms" in t.print_by_ms() and "s" in t.print_by_s()
+
+
+def test_clock_sampler_windows_samples_with_a_fake_nvidia_smi(tmp_path, monkeypatch):
+    """The sampler reads nvidia-smi's CSV; a fake one on PATH prints timestamped rows.  Samples
+    inside the marks are reported; when none fall inside, the whole span is, and the summary says so."""
+    import os
+    import stat
+    import time
+    from hipress_b200.utils import ClockSampler
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/bash\n"
+                    "for i in $(seq 1 200); do\n"
+                    "  echo \"$(date +'%Y/%m/%d %H:%M:%S.%3N'), 0, 1800, 1965, 650.0, 0x0, Not Active, Not Active, Not Active, Active\"\n"
+                    "  sleep 0.02\n"
+                    "done\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", str(tmp_path) + os.pathsep + os.environ["PATH"])
+    with ClockSampler(0) as c:
+        time.sleep(0.3)
+        c.mark_start()
+        time.sleep(0.3)
+        c.mark_end()
+        time.sleep(0.1)
+    s = c.summary()
+    assert s["sm_mhz"] == 1800 and s["sm_max_mhz"] == 1965 and s["reasons"] == ["sw_power_cap"]
+    assert s["window"] == "timed region" and 3 <= s["samples"] <= 30
+    total = len(c.rows())
+    assert total > s["samples"]                       # samples outside the marks were left out
+    c.t_start, c.t_end = time.time() + 100, time.time() + 101   # a region nothing fell into
+    s2 = c.summary()
+    assert s2["samples"] == total and "no sample fell inside" in s2["window"]
