@@ -44,7 +44,7 @@ def parse():
                     help="gradient bucket size (default 25; 128 for the sparse codecs, whose per-bucket cost is a dozen launches)")
     ap.add_argument("--cuda-graph", type=int, default=1,
                     help="1 = replay forward+backward from one CUDA graph (ours only), 0 = eager")
-    ap.add_argument("--dgc-whole-step", type=int, default=0,
+    ap.add_argument("--dgc-whole-step", type=int, default=1,
                     help="1 = capture DGC's exchange and AdamW inside the CUDA graph too (device-resident epoch)")
     ap.add_argument("--dgc-start-step", type=int, default=400,
                     help="position in DGC's 400-step sparsity warm-up at which the run starts (400 = steady state)")

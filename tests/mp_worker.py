@@ -148,6 +148,21 @@ def main():
     if rank == 0:
         print("MP_OK ddp_graphed", flush=True)
 
+    # DGC (momentum correction, clipping, fused AdamW) with the exchange captured in the graph
+    from hipress_b200.parallel.dgc import DGCDataParallel
+    torch.manual_seed(0)
+    net = resnet_tiny(10).cuda().to(memory_format=torch.channels_last)
+    dm = DGCDataParallel(net, keep_fraction=0.05, sample_rate=0.1, warmup_steps=0, lr=1e-3, bucket_mb=0.05,
+                         graph_capturable=True)
+    dstep = GraphedTrainStep(dm, loss_fn, (xc, y))
+    assert dstep.whole_step
+    dlosses = [float(dstep(xc, y).detach()) for _ in range(10)]
+    dm.check()
+    assert same_on_all_ranks(dm.flat_param), "graphed DGC replicas diverged"
+    assert all(v == v for v in dlosses)
+    if rank == 0:
+        print("MP_OK ddp_graphed_dgc", flush=True)
+
     torch.manual_seed(0)
     net = vgg_tiny(10).cuda()
     pm = PowerSGDDataParallel(net, rank_r=2, lr=0.05, momentum=0.9)
