@@ -8,10 +8,11 @@ as in eager mode) and replays it with a single launch.
 
 Two capture scopes:
 
-* **Whole step** (wrappers created with ``CompressionConfig(graph_capturable=True)``: TBQ and
-  TernGrad with the fused SGD).  The engine keeps the step's epoch -- flag values, slot parity,
-  rounding seed -- in device memory, advanced by a one-thread kernel at the start of the step,
-  so nothing in its launches changes from step to step.  The capture then contains
+* **Whole step** (wrappers created with ``CompressionConfig(graph_capturable=True)``: TBQ,
+  TernGrad, GradDrop and DGC with a fused optimizer).  The engine keeps the step's epoch -- flag
+  values, slot parity, rounding / sampling seed, AdamW's step count -- in device memory, advanced
+  by a one-thread kernel at the start of the step, so nothing in its launches changes from step
+  to step.  The capture then contains
   ``begin_step``, forward, backward *with the gradient hooks firing* and ``step``: every bucket
   is compressed, pushed to the peers, unpacked and applied on the engine's side streams as soon
   as its gradients exist, overlapping the rest of backward, exactly as in eager mode.
@@ -69,6 +70,15 @@ class GraphedTrainStep:
                     self.loss = fn(ddp.module, *self.static_inputs)
                     self.loss.backward()
             self._restore(saved)
+        except BaseException:
+            # a failed capture must leave the wrapper usable for eager steps
+            if hasattr(ddp, "_in_step"):
+                ddp._in_step = False
+            try:
+                self._restore(saved)
+            except RuntimeError:
+                pass                    # the original error is the one to report
+            raise
         finally:
             ddp.hooks_enabled = True
 
