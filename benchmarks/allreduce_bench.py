@@ -11,6 +11,8 @@ rank are synchronised (sum / W on every rank) by
 * ``tbq``       threshold 2e-3,
 * ``terngrad``  2-bit, stochastic, error feedback,
 * ``dgc``       top-k 0.1 % with 1 % sample threshold estimation,
+* ``tbq_sharded`` / ``terngrad_sharded``  the same codecs as a compressed reduce-scatter to shard
+  owners followed by a compressed all-gather of the re-quantised averages (``--codecs ... tbq_sharded``),
 
 each as ONE fused pipeline per step: compress kernels that store the packed payload straight
 into every peer's receive slot over NVLink, a bounded flag wait, and a one-pass unpack +
@@ -50,6 +52,11 @@ def measured_hbm_gbs() -> float:
 
 def hbm_bytes_per_elem(codec: str, world: int) -> float:
     """Algorithmic HBM traffic of the fused pipeline per fp32 element."""
+    if codec.endswith("_sharded"):
+        # phase 1 compresses everything once (payload written once); the owner decodes `world`
+        # payloads of 1/world of the elements and re-compresses them; phase 3 decodes one payload
+        first = {"tbq": 4 + 8 + 0.25, "terngrad": 8 + 8 + 4 + 0.25}[codec[:-8]]
+        return first + (0.25 * world + 4 + first) / world + 0.25 + 4
     if codec == "tbq":       # compress: R grad + RW residual + W payload ; unpack: R payloads + W dense
         return 4 + 8 + 0.25 * world + 0.25 * world + 4
     if codec == "terngrad":  # min/max pass (grad + residual) then quantise pass
@@ -62,6 +69,8 @@ def hbm_bytes_per_elem(codec: str, world: int) -> float:
 
 
 def wire_bytes(codec: str, n: int, world: int) -> float:
+    if codec.endswith("_sharded"):  # one payload's worth out to the owners, one shard payload to everyone
+        return 2.0 * wire_bytes(codec[:-8], n, 2) * (world - 1) / world
     per = {"tbq": n / 4, "terngrad": 10 + n / 4, "dgc": 4 + 8 * max(1, int(n * 0.001 + 0.999)),
            "dense": 0.0}[codec]
     if codec == "dense":
@@ -120,8 +129,10 @@ def main():
                 nccl_ms = ms
                 launches = None
             else:
-                cfg = dict(rank=rank, world=world, device=local, codec=codec, threshold=2e-3, bitwidth=2,
-                           enable_random=1, error_feedback=1, keep_fraction=0.001, sample_rate=0.01, seed=1)
+                sharded = codec.endswith("_sharded")
+                cfg = dict(rank=rank, world=world, device=local, codec=codec[:-8] if sharded else codec,
+                           threshold=2e-3, bitwidth=2, enable_random=1, error_feedback=1, keep_fraction=0.001,
+                           sample_rate=0.01, seed=1, sharded=1 if sharded else 0)
                 eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
                 sym = SymmetricMemory(eng.symmetric_bytes, dev)
                 resid = torch.zeros(n, device=dev)

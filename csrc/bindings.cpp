@@ -78,6 +78,7 @@ runtime::EngineConfig config_from(const py::dict& d) {
   c.defer_recv = get("defer_recv", 0);
   c.clear_grad = get("clear_grad", 0);
   c.device_epoch = get("device_epoch", 0);
+  c.sharded = get("sharded", 0);
   c.momentum_correction = get("momentum_correction", 0);
   c.dgc_momentum = get("dgc_momentum", 0.9f);
   c.dgc_clip = get("dgc_clip", 0.0f);
@@ -449,6 +450,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              e.begin_step(at::cuda::getCurrentCUDAStream());
            },
            py::arg("device") = -1)
+      .def("reduce_step", &runtime::DdpEngine::reduce_step)
       .def("end_capture", &runtime::DdpEngine::end_capture)
       .def("note_replay", &runtime::DdpEngine::note_replay, py::arg("count"), py::arg("launches_per_step"))
       .def("grad_ready",

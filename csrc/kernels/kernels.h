@@ -37,6 +37,9 @@ struct PushTargets {
   unsigned int* done = nullptr;
   const uint32_t* epoch_dev = nullptr;
   int64_t parity_stride = 0;
+  // A single destination is normally this GPU's own slot (device-scope fences are enough);
+  // set when the single destination is a peer, so that the payload is fenced at system scope.
+  int remote = 0;
 };
 constexpr uint64_t kEpochSeedStride = 0x9E3779B97F4A7C15ull;
 

@@ -88,7 +88,7 @@ __device__ __forceinline__ void publish_when_grid_done(const PushTargets& t) {
   if (t.done == nullptr) return;
   __syncthreads();
   if (threadIdx.x == 0) {
-    const bool remote = t.world > 1;
+    const bool remote = t.world > 1 || t.remote != 0;
     if (remote) __threadfence_system(); else __threadfence();
     const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
     const unsigned int prev = atomicAdd(t.done, 1u);

@@ -46,23 +46,51 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   for (int pb : param_bucket)
     if (pb < 0 || pb >= static_cast<int>(buckets.size())) throw std::invalid_argument("bad param->bucket map");
 
+  if (cfg.sharded) {
+    if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad)
+      throw std::invalid_argument("the sharded exchange is implemented for the tbq and terngrad codecs");
+    if (cfg.device_epoch) throw std::invalid_argument("sharded and device_epoch cannot be combined yet");
+  }
   // symmetric layout: [flags of all buckets][slots parity 0][slots parity 1] per bucket
   int64_t off = 0;
   layouts_.resize(buckets.size());
   for (size_t b = 0; b < buckets.size(); ++b) {
     layouts_[b].flags = off;
     off += round_up(int64_t(cfg.world) * 4, 128);
+    if (cfg.sharded) {
+      layouts_[b].flags2 = off;
+      off += round_up(int64_t(cfg.world) * 4, 128);
+    }
   }
   off = round_up(off, 1024);
+  int64_t res2 = 0;
+  residual2_off_.assign(buckets.size(), 0);
   for (size_t b = 0; b < buckets.size(); ++b) {
     BucketLayout& L = layouts_[b];
     // header-bearing payloads start 6 bytes into the slot so that the data
     // region after the 10-byte header is 16-byte aligned for vector stores
     L.shift = (cfg.codec == Codec::kTernGrad || cfg.codec == Codec::kEcq) ? 6 : 0;
-    L.slot_bytes = round_up(payload_capacity(int(b)) + L.shift, 256);
+    if (cfg.sharded) {
+      // shards of a multiple of 64 elements: every shard starts 16-byte aligned in the dense
+      // buffers and its packed bytes fill whole 16-byte groups
+      L.shard_elems = round_up((buckets[b].numel + cfg.world - 1) / cfg.world, 64);
+      const int64_t cap = cfg.codec == Codec::kTbq ? tbq_payload_bytes(L.shard_elems)
+                                                   : tern_payload_bytes(L.shard_elems, cfg.bitwidth);
+      L.slot_bytes = round_up(cap + L.shift, 256);
+      residual2_off_[b] = res2;
+      res2 += L.shard_elems;
+    } else {
+      L.slot_bytes = round_up(payload_capacity(int(b)) + L.shift, 256);
+    }
     for (int p = 0; p < 2; ++p) {
       L.slots[p] = off;
       off += L.slot_bytes * cfg.world;
+    }
+    if (cfg.sharded) {
+      for (int p = 0; p < 2; ++p) {
+        L.slots2[p] = off;
+        off += L.slot_bytes * cfg.world;
+      }
     }
   }
   symmetric_bytes_ = round_up(off, 1024);
@@ -72,6 +100,10 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   for (auto& e : ready_events_) check(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "event");
   check(cudaMalloc(reinterpret_cast<void**>(&status_), 64), "cudaMalloc status");
   check(cudaMemset(status_, 0, 64), "memset status");
+  if (cfg.sharded && res2 > 0) {
+    check(cudaMalloc(reinterpret_cast<void**>(&residual2_), size_t(res2) * sizeof(float)), "cudaMalloc residual2");
+    check(cudaMemset(residual2_, 0, size_t(res2) * sizeof(float)), "memset residual2");
+  }
   if (cfg.device_epoch) {
     if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad && cfg.codec != Codec::kSparse)
       throw std::invalid_argument("device_epoch is implemented for the tbq, terngrad, graddrop and dgc codecs");
@@ -123,6 +155,7 @@ DdpEngine::~DdpEngine() {
   for (auto& e : ready_events_) cudaEventDestroy(e);
   if (status_) cudaFree(status_);
   if (epoch_dev_) cudaFree(epoch_dev_);
+  if (residual2_) cudaFree(residual2_);
 }
 
 void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* momentum, float* aux,
@@ -263,8 +296,175 @@ cuda::UnpackSources DdpEngine::sources_for(int b) const {
 }
 
 void DdpEngine::issue_bucket(int b, int worker) {
+  if (cfg_.sharded) {
+    issue_shard_push(b, worker);
+    if (!cfg_.defer_recv) {
+      issue_shard_reduce(b, worker);
+      issue_shard_final(b, worker);
+    }
+    return;
+  }
   issue_push(b, worker);
   if (!cfg_.defer_recv) issue_recv(b, worker);
+}
+
+// ------------------------------------------------------------------ sharded exchange
+int64_t DdpEngine::shard_len(int b, int j) const {
+  const int64_t S = layouts_[static_cast<size_t>(b)].shard_elems;
+  const int64_t left = buckets_[static_cast<size_t>(b)].numel - int64_t(j) * S;
+  return left <= 0 ? 0 : (left < S ? left : S);
+}
+
+void DdpEngine::issue_shard_push(int b, int worker) {
+  WorkerCtx& w = workers_[static_cast<size_t>(worker)];
+  const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int parity = int(epoch_ & 1u);
+  check(cudaStreamWaitEvent(w.push, ready_events_[static_cast<size_t>(b)], 0), "wait ready");
+  int launched = 0;
+  for (int j = 0; j < cfg_.world; ++j) {
+    const int64_t nj = shard_len(b, j);
+    const int64_t off = B.offset + int64_t(j) * L.shard_elems;
+    // one destination: my slot in the receive area of the shard's owner
+    cuda::PushTargets dst;
+    dst.world = 1;
+    dst.epoch = epoch_;
+    dst.done = w.done;
+    dst.remote = j != cfg_.rank ? 1 : 0;
+    uint8_t* base = bases_[static_cast<size_t>(j)];
+    dst.payload[0] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
+    dst.flag[0] = reinterpret_cast<uint32_t*>(base + L.flags) + cfg_.rank;
+    if (nj == 0) {  // nothing of this bucket falls into shard j: only tell the owner
+      check(cuda::signal_flags(dst, w.push), "signal_flags");
+      launched += 1;
+      continue;
+    }
+    const uint64_t seed = cfg_.seed + uint64_t(epoch_) * cuda::kEpochSeedStride +
+                          uint64_t(b) * 0x632BE59BD9B4E019ull + uint64_t(j) * 0xD6E8FEB86659FD93ull;
+    float* res = residual_ ? residual_ + off : nullptr;
+    if (cfg_.codec == Codec::kTbq) {
+      if (!res) throw std::runtime_error("tbq needs a residual buffer");
+      check(cuda::tbq_compress(grad_ + off, res, nj, cfg_.threshold, dst, w.push), "tbq_compress");
+      launched += 1;
+    } else {
+      check(cuda::terngrad_compress(grad_ + off, cfg_.error_feedback ? res : nullptr, nj, cfg_.bitwidth,
+                                    cfg_.enable_random, seed, dst, w.scratch, w.push),
+            "terngrad_compress");
+      launched += 2;
+    }
+  }
+  check(cudaEventRecord(w.pushed, w.push), "record pushed");
+  launches_ += launched;
+}
+
+void DdpEngine::issue_shard_reduce(int b, int worker) {
+  WorkerCtx& w = workers_[static_cast<size_t>(worker)];
+  const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int parity = int(epoch_ & 1u);
+  const int me = cfg_.rank;
+  const int64_t n_me = shard_len(b, me);
+  const int64_t off = B.offset + int64_t(me) * L.shard_elems;
+  uint8_t* mine = bases_[static_cast<size_t>(me)];
+  int launched = 0;
+  check(cudaStreamWaitEvent(w.recv, w.pushed, 0), "wait pushed");
+  // every rank's payload of my shard has arrived
+  check(cuda::wait_flags(reinterpret_cast<const uint32_t*>(mine + L.flags), cfg_.world, epoch_,
+                         cfg_.flag_timeout_ns, status_, w.recv),
+        "wait_flags");
+  launched += 1;
+  // where the averaged, re-compressed shard goes: slot [me] of every rank's phase-2 area
+  cuda::PushTargets dst;
+  dst.world = cfg_.world;
+  dst.epoch = epoch_;
+  dst.done = w.done + 4;  // its own last-CTA counter: the push stream may be compressing the next bucket
+  for (int p = 0; p < cfg_.world; ++p) {
+    uint8_t* base = bases_[static_cast<size_t>(p)];
+    dst.payload[p] = base + L.slots2[parity] + int64_t(me) * L.slot_bytes + L.shift;
+    dst.flag[p] = reinterpret_cast<uint32_t*>(base + L.flags2) + me;
+  }
+  if (n_me == 0) {
+    check(cuda::signal_flags(dst, w.recv), "signal_flags");
+    launches_ += launched + 1;
+    return;
+  }
+  cuda::UnpackSources src;
+  src.world = cfg_.world;
+  for (int r = 0; r < cfg_.world; ++r) {
+    src.payload[r] = mine + L.slots[parity] + int64_t(r) * L.slot_bytes + L.shift;
+    src.payload_bytes[r] = L.slot_bytes - L.shift;
+  }
+  const float post = cfg_.average ? 1.0f / float(cfg_.world) : 1.0f;
+  float* g = grad_ + off;
+  float* res2 = residual2_ + residual2_off_[static_cast<size_t>(b)];
+  const uint64_t seed = cfg_.seed + uint64_t(epoch_) * cuda::kEpochSeedStride +
+                        uint64_t(b) * 0x632BE59BD9B4E019ull + 0xA24BAED4963EE407ull;
+  if (cfg_.codec == Codec::kTbq) {
+    check(cuda::tbq_unpack_accum(src, cfg_.threshold, g, n_me, 0, post, cuda::SgdApply{}, w.recv), "tbq_unpack");
+    check(cuda::tbq_compress(g, res2, n_me, cfg_.threshold, dst, w.recv), "tbq_compress");
+    launched += 2;
+  } else {
+    check(cuda::terngrad_unpack_accum(src, g, n_me, 0, post, cuda::SgdApply{}, status_, w.recv, cfg_.bitwidth),
+          "tern_unpack");
+    // its own scratch region: the push stream may be reducing the next bucket's min/max
+    void* scratch2 = static_cast<uint8_t*>(w.scratch) + 131072;
+    check(cuda::terngrad_compress(g, cfg_.error_feedback ? res2 : nullptr, n_me, cfg_.bitwidth,
+                                  cfg_.enable_random, seed, dst, scratch2, w.recv),
+          "terngrad_compress");
+    launched += 3;
+  }
+  launches_ += launched;
+}
+
+void DdpEngine::issue_shard_final(int b, int worker) {
+  WorkerCtx& w = workers_[static_cast<size_t>(worker)];
+  const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+  const BucketLayout& L = layouts_[static_cast<size_t>(b)];
+  const int parity = int(epoch_ & 1u);
+  uint8_t* mine = bases_[static_cast<size_t>(cfg_.rank)];
+  int launched = 0;
+  check(cuda::wait_flags(reinterpret_cast<const uint32_t*>(mine + L.flags2), cfg_.world, epoch_,
+                         cfg_.flag_timeout_ns, status_, w.recv),
+        "wait_flags");
+  launched += 1;
+  for (int j = 0; j < cfg_.world; ++j) {
+    const int64_t nj = shard_len(b, j);
+    if (nj == 0) continue;
+    const int64_t off = B.offset + int64_t(j) * L.shard_elems;
+    cuda::UnpackSources src;
+    src.world = 1;
+    src.payload[0] = mine + L.slots2[parity] + int64_t(j) * L.slot_bytes + L.shift;
+    src.payload_bytes[0] = L.slot_bytes - L.shift;
+    cuda::SgdApply apply;
+    if (fused_sgd_) {
+      apply.param = param_ + off;
+      apply.momentum = momentum_ + off;
+      apply.lr = lr_;
+      apply.mu = sgd_mu_;
+      apply.weight_decay = wd_;
+      apply.first_step = steps_ == 0 ? 1 : 0;
+      apply.clear_grad = cfg_.clear_grad;
+    }
+    if (cfg_.codec == Codec::kTbq)
+      check(cuda::tbq_unpack_accum(src, cfg_.threshold, grad_ + off, nj, 0, 1.0f, apply, w.recv), "tbq_unpack");
+    else
+      check(cuda::terngrad_unpack_accum(src, grad_ + off, nj, 0, 1.0f, apply, status_, w.recv, cfg_.bitwidth),
+            "tern_unpack");
+    launched += 1;
+  }
+  check(cudaEventRecord(w.tail, w.recv), "record tail");
+  w.used = true;
+  launches_ += launched;
+}
+
+void DdpEngine::reduce_step() {
+  if (!cfg_.sharded || !cfg_.defer_recv) return;
+  for (size_t b = 0; b < buckets_.size(); ++b) {
+    const int worker = int(b) % static_cast<int>(workers_.size());
+    if (pool_) pool_->submit_to(worker, [this, b](int w) { issue_shard_reduce(int(b), w); });
+    else issue_shard_reduce(int(b), worker);
+  }
+  if (pool_) pool_->drain();
 }
 
 void DdpEngine::issue_push(int b, int worker) {
@@ -437,8 +637,14 @@ void DdpEngine::finish_step(cudaStream_t consumer) {
   if (cfg_.defer_recv) {
     for (size_t b = 0; b < buckets_.size(); ++b) {
       const int worker = int(b) % static_cast<int>(workers_.size());
-      if (pool_) pool_->submit_to(worker, [this, b](int w) { issue_recv(int(b), w); });
-      else issue_recv(int(b), worker);
+      if (cfg_.sharded) {
+        if (pool_) pool_->submit_to(worker, [this, b](int w) { issue_shard_final(int(b), w); });
+        else issue_shard_final(int(b), worker);
+      } else if (pool_) {
+        pool_->submit_to(worker, [this, b](int w) { issue_recv(int(b), w); });
+      } else {
+        issue_recv(int(b), worker);
+      }
     }
     if (pool_) pool_->drain();
   }

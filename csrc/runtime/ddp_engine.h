@@ -69,6 +69,16 @@ struct EngineConfig {
   // backward hooks and this engine's launches included -- can be captured once in a CUDA graph
   // and replayed.  begin_step() then launches a one-thread kernel that advances the counter.
   int device_epoch = 0;
+  // Sharded exchange (TBQ, TernGrad): rank j owns shard j (1/world) of every bucket.  Phase 1:
+  // every rank compresses each shard and stores it into the owner's slot (compressed
+  // reduce-scatter).  Phase 2: the owner decodes the world payloads of its shard, averages,
+  // re-compresses the average with its own residual and stores it to every rank (compressed
+  // all-gather).  Phase 3: every rank decodes the world shard payloads (one per owner) and applies
+  // the update.  A rank sends 2 x (world-1)/world of one payload instead of world-1 payloads and
+  // decodes 2 table look-ups per element instead of world; the price is a second quantisation
+  // (the reference's root does the same: decompress-accumulate, then re-compress,
+  // ref hp_cuda.cpp:241-271).
+  int sharded = 0;
 };
 
 struct BucketDesc {
@@ -83,6 +93,10 @@ struct BucketLayout {
   int64_t slots[2] = {0, 0};   // offset of slot array [world][slot_bytes] per parity
   int64_t flags = 0;           // offset of `world` uint32 flags
   int64_t shift = 0;           // payload starts at slot + shift (aligns the data region)
+  // sharded exchange only
+  int64_t shard_elems = 0;     // elements per shard (multiple of 64)
+  int64_t slots2[2] = {0, 0};  // phase-2 slot array [world owners][slot_bytes] per parity
+  int64_t flags2 = 0;          // phase-2 flags
 };
 
 class DdpEngine {
@@ -124,6 +138,10 @@ class DdpEngine {
   // `consumer` wait for the device work.  Buckets whose hooks never fired
   // (unused parameters) are flushed here.
   void finish_step(cudaStream_t consumer);
+  // defer_recv + sharded: issues phase 2 (owner reduce + re-compress) of every bucket.  The
+  // caller emulating several ranks on one device calls it for every rank between a device
+  // synchronise after the pushes and another before finish_step().
+  void reduce_step();
   // Blocks until every job handed to the workers so far has been issued to the device.
   void drain() { if (pool_) pool_->drain(); }
 
@@ -150,6 +168,11 @@ class DdpEngine {
   void issue_bucket(int b, int worker);
   void issue_push(int b, int worker);
   void issue_recv(int b, int worker);
+  // sharded exchange: the three phases of one bucket
+  void issue_shard_push(int b, int worker);
+  void issue_shard_reduce(int b, int worker);
+  void issue_shard_final(int b, int worker);
+  int64_t shard_len(int b, int j) const;
   cuda::PushTargets targets_for(int b, WorkerCtx& w) const;
   cuda::UnpackSources sources_for(int b) const;
 
@@ -171,6 +194,8 @@ class DdpEngine {
   uint32_t epoch_ = 0;
   int64_t steps_ = 0;
   uint32_t* epoch_dev_ = nullptr;   // device copy of epoch_ (device_epoch mode)
+  float* residual2_ = nullptr;      // sharded: residual of the owner's re-compression, per bucket shard
+  std::vector<int64_t> residual2_off_;
   int64_t launches_at_begin_ = 0;
   std::vector<std::atomic<int>> pending_params_;
   std::vector<std::atomic<int>> submitted_;

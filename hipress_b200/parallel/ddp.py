@@ -57,6 +57,9 @@ class CompressionConfig:
     # captured in a CUDA graph (tbq / terngrad / graddrop / dgc with a fused optimizer; forces
     # inline issue)
     graph_capturable: bool = False
+    # sharded exchange (tbq / terngrad): rank j owns 1/world of every bucket; compressed
+    # reduce-scatter to the owners, then compressed all-gather of the re-quantised averages
+    sharded: bool = False
     # DGC extras (algorithm "dgc"): momentum correction with factor masking, local clipping
     momentum_correction: bool = False
     dgc_momentum: float = 0.9
@@ -184,6 +187,7 @@ class CompressedDataParallel(nn.Module):
         # with a fused optimizer nobody reads the averaged gradient: the kernel that applies the
         # update leaves zeros behind, ready for the next backward pass
         cfg_dict["clear_grad"] = 1 if fused else 0
+        cfg_dict["sharded"] = 1 if self.config.sharded else 0
         self.graph_capturable = bool(self.config.graph_capturable)
         if self.graph_capturable:
             if self.config.algorithm not in ("tbq", "terngrad", "graddrop", "dgc") or not fused:

@@ -89,6 +89,36 @@ def check_codec(codec, kw, rank, world, local):
     del eng, sym
 
 
+def check_sharded(codec, kw, rank, world, local):
+    """Compressed reduce-scatter + compressed all-gather across real GPUs against the CPU restatement."""
+    from sharded_ref import expected, shard_elems
+    n = 300000 + 8
+    cfg = dict(rank=rank, world=world, device=local, codec=codec, seed=5, flag_timeout_s=10.0, sharded=1,
+               num_workers=0, **kw)
+    eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
+    sym = SymmetricMemory(eng.symmetric_bytes, torch.device("cuda", local))
+    grad = torch.zeros(n, device="cuda")
+    resid = torch.zeros(n, device="cuda")
+    eng.set_buffers(grad, resid, None, None)
+    eng.set_symmetric(sym.buf)
+    eng.set_sgd(0.0, 0.0, 0.0, False)
+    cpu_resid = [torch.zeros(n) for _ in range(world)]
+    cpu_resid2 = [torch.zeros(shard_elems(n, world)) for _ in range(world)]
+    for step in range(3):
+        cpu_grads = [gauss(n, 0.01, 1000 * step + r) for r in range(world)]
+        grad.copy_(cpu_grads[rank])
+        eng.begin_step(local)
+        eng.bucket_ready(0, local)
+        eng.finish_step(local)
+        torch.cuda.synchronize()
+        assert eng.check_status() == 0
+        want = expected(codec, kw, 5, step + 1, cpu_grads, cpu_resid, cpu_resid2, world)
+        assert torch.equal(grad.cpu(), want), f"sharded {codec} rank {rank} step {step}"
+        assert torch.equal(resid.cpu(), cpu_resid[rank]), f"sharded {codec} residual rank {rank} step {step}"
+    dist.barrier()
+    del eng, sym
+
+
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -106,6 +136,11 @@ def main():
         check_codec(codec, dict(kw, device_epoch=1, num_workers=0), rank, world, local)
         if rank == 0:
             print(f"MP_OK codec_{codec}_device_epoch", flush=True)
+
+    for codec, kw in [("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)), ("tbq", dict(threshold=0.01))]:
+        check_sharded(codec, kw, rank, world, local)
+        if rank == 0:
+            print(f"MP_OK sharded_{codec}", flush=True)
 
     # DDP wrapper: replicas stay bit-identical, loss goes down
     torch.manual_seed(0)
