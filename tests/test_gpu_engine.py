@@ -137,12 +137,14 @@ def test_plan_buckets_reverse_order_and_alignment():
     assert plan.total == sum(b[1] for b in plan.buckets)
 
 
-@pytest.mark.parametrize("algorithm", ["terngrad", "tbq", "graddrop", "ecq", "dense"])
+@pytest.mark.parametrize("algorithm", ["terngrad", "tbq", "graddrop", "ecq", "dense", "terngrad_sharded", "tbq_sharded"])
 def test_ddp_wrapper_world1_trains(algorithm):
     torch.manual_seed(0)
     net = resnet_tiny(10).cuda().to(memory_format=torch.channels_last)
+    sharded = algorithm.endswith("_sharded")       # owner reduce + re-compress + fused SGD in the last phase
+    algorithm = algorithm[:-8] if sharded else algorithm
     cfg = CompressionConfig(algorithm, bucket_mb=0.05, threshold=1e-3, keep_fraction=0.05, sample_rate=0.05,
-                            bitwidth=4 if algorithm == "ecq" else 2)
+                            bitwidth=4 if algorithm == "ecq" else 2, sharded=sharded)
     model = CompressedDataParallel(net, cfg, lr=0.05, momentum=0.9)
     assert len(model.plan.buckets) > 1
     x = torch.randn(16, 3, 32, 32, device="cuda")
@@ -153,7 +155,7 @@ def test_ddp_wrapper_world1_trains(algorithm):
             loss = torch.nn.functional.cross_entropy(model(x), y)
         loss.backward()
         model.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     model.check()
     assert all(l == l for l in losses)
     assert min(losses[-4:]) < losses[0], losses
