@@ -169,6 +169,7 @@ void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* m
 }
 
 void DdpEngine::set_adamw(float lr, float beta1, float beta2, float eps, float weight_decay) {
+  if (cfg_.sharded) throw std::invalid_argument("the sharded exchange applies the fused SGD only (no AdamW yet)");
   lr_ = lr;
   beta1_ = beta1;
   beta2_ = beta2;
