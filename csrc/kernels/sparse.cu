@@ -405,7 +405,23 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
 
   // ---- first walk: how many elements above / at the cut does this warp hold
   unsigned int my_gt = 0, my_eq = 0;
-  for (int64_t base = wbegin; base < wend; base += 128) {
+  int64_t base = wbegin;
+  if (vec_ok) {
+    // four steps per iteration with their loads issued together: one load in flight per lane
+    // left this walk waiting on DRAM latency
+    for (; base + 512 <= wend; base += 512) {
+      float4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const float4*>(R + base + u * 128 + lane * 4);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t k0 = abs_key(q[u].x), k1 = abs_key(q[u].y), k2 = abs_key(q[u].z), k3 = abs_key(q[u].w);
+        my_gt += (k0 > cut) + (k1 > cut) + (k2 > cut) + (k3 > cut);
+        my_eq += (k0 == cut) + (k1 == cut) + (k2 == cut) + (k3 == cut);
+      }
+    }
+  }
+  for (; base < wend; base += 128) {
     float v[4];
     uint32_t key[4];
     load4(base + lane * 4, v, key);
@@ -434,8 +450,8 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
 
   // ---- second walk: emit
   if (my_gt != 0 || (ties > 0 && my_eq != 0)) {
-    for (int64_t base = wbegin; base < wend; base += 128) {
-      const int64_t e0 = base + lane * 4;
+    for (int64_t step = wbegin; step < wend; step += 128) {
+      const int64_t e0 = step + lane * 4;
       float v[4];
       uint32_t key[4];
       load4(e0, v, key);
