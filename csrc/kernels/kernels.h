@@ -37,6 +37,7 @@ struct PushTargets {
   unsigned int* done = nullptr;
   const uint32_t* epoch_dev = nullptr;
   int64_t parity_stride = 0;
+  int64_t parity_off = 0;  // set on the device by resolve_epoch(): 0 or parity_stride
   // A single destination is normally this GPU's own slot (device-scope fences are enough);
   // set when the single destination is a peer, so that the payload is fenced at system scope.
   int remote = 0;
@@ -51,6 +52,7 @@ struct UnpackSources {
   int64_t payload_bytes[kMaxWorld] = {};  // capacity of each slot (bounds checks)
   const uint32_t* epoch_dev = nullptr;    // see PushTargets
   int64_t parity_stride = 0;
+  int64_t parity_off = 0;                 // set on the device by resolve_epoch()
 };
 
 // Optional fused SGD-with-momentum update applied to the decoded, averaged

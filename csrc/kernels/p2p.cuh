@@ -37,41 +37,38 @@ __device__ __forceinline__ void store_u32_any(uint8_t* p, uint32_t v) {
 }
 
 // Epoch kept on the device (see PushTargets): fix up the by-value copy of the kernel argument.
-// The counter is written by a kernel earlier in stream order, never concurrently.
+// Only scalars are written and every access to the pointer arrays uses a compile-time index
+// (unrolled loops with a guard): rewriting the arrays, or indexing them with a run-time value,
+// makes the compiler keep the whole struct in local memory, which cost the compress kernels a
+// fifth of their bandwidth.  The counter is written by a kernel earlier in stream order.
 __device__ __forceinline__ void resolve_epoch(PushTargets& t) {
   if (t.epoch_dev == nullptr) return;
   const uint32_t e = *t.epoch_dev;
   t.epoch = e;
-  if (e & 1u) {
-#pragma unroll
-    for (int p = 0; p < kMaxWorld; ++p)
-      if (p < t.world) t.payload[p] += t.parity_stride;
-  }
+  t.parity_off = (e & 1u) ? t.parity_stride : 0;
 }
 __device__ __forceinline__ void resolve_epoch(UnpackSources& s) {
   if (s.epoch_dev == nullptr) return;
-  if (*s.epoch_dev & 1u) {
-#pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r)
-      if (r < s.world) s.payload[r] += s.parity_stride;
-  }
+  s.parity_off = (*s.epoch_dev & 1u) ? s.parity_stride : 0;
 }
 
 // The same 4 payload bytes to every destination.
 __device__ __forceinline__ void push_u32(const PushTargets& t, int64_t byte_off, uint32_t v) {
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p)
-    if (p < t.world) store_u32_any(t.payload[p] + byte_off, v);
+    if (p < t.world) store_u32_any(t.payload[p] + t.parity_off + byte_off, v);
 }
 __device__ __forceinline__ void push_u8(const PushTargets& t, int64_t byte_off, uint8_t v) {
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p)
-    if (p < t.world) t.payload[p][byte_off] = v;
+    if (p < t.world) t.payload[p][t.parity_off + byte_off] = v;
 }
 __device__ __forceinline__ void push_bytes(const PushTargets& t, int64_t byte_off,
                                            const uint8_t* src, int count) {
-  for (int p = 0; p < t.world; ++p)
-    for (int i = 0; i < count; ++i) t.payload[p][byte_off + i] = src[i];
+#pragma unroll
+  for (int p = 0; p < kMaxWorld; ++p)
+    if (p < t.world)
+      for (int i = 0; i < count; ++i) t.payload[p][t.parity_off + byte_off + i] = src[i];
 }
 
 // Called by every thread at the end of a compressing kernel.  Elects the last
@@ -95,8 +92,9 @@ __device__ __forceinline__ void publish_when_grid_done(const PushTargets& t) {
     if (prev == total - 1) {
       if (remote) __threadfence_system(); else __threadfence();
       *t.done = 0u;
-      for (int p = 0; p < t.world; ++p)
-        if (t.flag[p] != nullptr) st_release_sys(t.flag[p], t.epoch);
+#pragma unroll
+      for (int p = 0; p < kMaxWorld; ++p)
+        if (p < t.world && t.flag[p] != nullptr) st_release_sys(t.flag[p], t.epoch);
     }
   }
 }

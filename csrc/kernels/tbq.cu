@@ -90,13 +90,13 @@ tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int
   // nibble -> 2 decoded values; one 128-byte table shared by all ranks (see unpack_lut.cuh)
   __shared__ __align__(128) float lut[16 * 2];
   uint32_t first[kMaxWorld];
-  unpack_nibble_prefetch<2>(src, 0, n, first);
+  unpack_nibble_prefetch<2>(src, 0, src.parity_off, n, first);
   if (threadIdx.x < 32) lut[threadIdx.x] = tbq_dequant((uint32_t(threadIdx.x) >> 1 >> (2 * (threadIdx.x & 1))) & 3u, thr);
   __syncthreads();
   if (unpack_coalesced_ok(src, out, APPLY, apply))
-    unpack_nibble_body_coalesced2<APPLY, true>(lut, first, src, 0, out, n, add, post_scale, apply);
+    unpack_nibble_body_coalesced2<APPLY, true>(lut, first, src, src.parity_off, out, n, add, post_scale, apply);
   else
-    unpack_nibble_body<2, APPLY, true>(lut, first, src, 0, out, n, add, post_scale, apply);
+    unpack_nibble_body<2, APPLY, true>(lut, first, src, src.parity_off, out, n, add, post_scale, apply);
 }
 
 inline int grid_for(int64_t items, int threads, int max_blocks) {

@@ -230,12 +230,15 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
   __shared__ TernHeader hdr[kMaxWorld];
   __shared__ int all_ok;
   uint32_t first[kMaxWorld];
-  if constexpr (BW == 1 || BW == 2 || BW == 4) unpack_nibble_prefetch<BW>(src, kTernHeaderBytes, n, first);
+  if constexpr (BW == 1 || BW == 2 || BW == 4) unpack_nibble_prefetch<BW>(src, kTernHeaderBytes, src.parity_off, n, first);
   if (threadIdx.x == 0) all_ok = 1;
   __syncthreads();
-  if (threadIdx.x < src.world) {
-    hdr[threadIdx.x] = read_header(src.payload[threadIdx.x], src.payload_bytes[threadIdx.x], n);
-    if (!hdr[threadIdx.x].ok) all_ok = 0;
+#pragma unroll
+  for (int r = 0; r < kMaxWorld; ++r) {   // thread r reads header r; compile-time index into src
+    if (int(threadIdx.x) == r && r < src.world) {
+      hdr[r] = read_header(src.payload[r] + src.parity_off, src.payload_bytes[r], n);
+      if (!hdr[r].ok) all_ok = 0;
+    }
   }
   __syncthreads();
   const int bw = BW > 0 ? BW : hdr[0].bw;
@@ -258,11 +261,11 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
     __syncthreads();
     if constexpr (BW == 2) {
       if (unpack_coalesced_ok(src, out, APPLY, apply)) {
-        unpack_nibble_body_coalesced2<APPLY, false>(nib, first, src, kTernHeaderBytes, out, n, add, post_scale, apply);
+        unpack_nibble_body_coalesced2<APPLY, false>(nib, first, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply);
         return;
       }
     }
-    unpack_nibble_body<BW, APPLY, false>(nib, first, src, kTernHeaderBytes, out, n, add, post_scale, apply);
+    unpack_nibble_body<BW, APPLY, false>(nib, first, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply);
     return;
   }
   const int dpb = 8 / bw;
@@ -275,13 +278,13 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
   }
   __syncthreads();
   if (BW > 0) {
-    unpack_lut_body<8 / (BW > 0 ? BW : 1), APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply);
+    unpack_lut_body<8 / (BW > 0 ? BW : 1), APPLY>(lut, 256, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply);
   } else {
     switch (bw) {
-      case 1: unpack_lut_body<8, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
-      case 2: unpack_lut_body<4, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
-      case 4: unpack_lut_body<2, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
-      default: unpack_lut_body<1, APPLY>(lut, 256, src, kTernHeaderBytes, out, n, add, post_scale, apply); break;
+      case 1: unpack_lut_body<8, APPLY>(lut, 256, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply); break;
+      case 2: unpack_lut_body<4, APPLY>(lut, 256, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply); break;
+      case 4: unpack_lut_body<2, APPLY>(lut, 256, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply); break;
+      default: unpack_lut_body<1, APPLY>(lut, 256, src, kTernHeaderBytes + src.parity_off, out, n, add, post_scale, apply); break;
     }
   }
 }

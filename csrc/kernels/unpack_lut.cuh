@@ -52,7 +52,7 @@ __device__ __forceinline__ uint32_t lut_row(uint32_t v) { return v ^ ((v >> 3) &
 // data_offset: bytes to skip at the start of each payload (header size).
 template <int DPB, bool APPLY>
 __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_stride,
-                                                const UnpackSources& src, int data_offset,
+                                                const UnpackSources& src, int64_t data_offset,
                                                 float* __restrict__ out, int64_t n, int add,
                                                 float post_scale, const SgdApply& apply) {
   constexpr int EPG = 4 * DPB;  // elements per group of 4 payload bytes
@@ -137,7 +137,9 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     for (int64_t e = full_groups * EPG; e < n; ++e) {
       float acc = add ? out[e] : 0.f;
-      for (int r = 0; r < src.world; ++r) {
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r >= src.world) break;
         const uint32_t byte = src.payload[r][data_offset + e / DPB];
         const float v = lut[(size_t(r) * rank_stride + lut_row(byte)) * DPB + int(e % DPB)];
         acc = (r == 0 && !add) ? v : hp_add(v, acc);
@@ -164,15 +166,18 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
 // kernel reads headers and builds its tables, so that the DRAM latency of the first loads and
 // the dependent loads of the prologue overlap instead of adding up.  A word is only requested
 // when it lies inside the slot (payload_bytes), whatever the header will turn out to say.
+// header_bytes: bytes before the packed data inside a slot; slot_shift: where this step's slot
+// starts relative to src.payload[r] (the epoch-parity offset; 0 unless the epoch lives on the device).
 template <int BW>
-__device__ __forceinline__ void unpack_nibble_prefetch(const UnpackSources& src, int data_offset, int64_t n,
+__device__ __forceinline__ void unpack_nibble_prefetch(const UnpackSources& src, int header_bytes,
+                                                       int64_t slot_shift, int64_t n,
                                                        uint32_t (&w)[kMaxWorld]) {
   constexpr int EPG = 8 * (4 / BW);
   const int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
 #pragma unroll
   for (int r = 0; r < kMaxWorld; ++r)
-    w[r] = (r < src.world && grp < n / EPG && data_offset + (grp + 1) * 4 <= src.payload_bytes[r])
-               ? load_u32_any(src.payload[r] + data_offset + grp * 4)
+    w[r] = (r < src.world && grp < n / EPG && header_bytes + (grp + 1) * 4 <= src.payload_bytes[r])
+               ? load_u32_any(src.payload[r] + slot_shift + header_bytes + grp * 4)
                : 0u;
 }
 
@@ -180,7 +185,7 @@ __device__ __forceinline__ void unpack_nibble_prefetch(const UnpackSources& src,
 // after rank r-1's.  w: the words unpack_nibble_prefetch returned for this thread.
 template <int BW, bool APPLY, bool SHARED>
 __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&w)[kMaxWorld],
-                                                   const UnpackSources& src, int data_offset,
+                                                   const UnpackSources& src, int64_t data_offset,
                                                    float* __restrict__ out, int64_t n, int add,
                                                    float post_scale, const SgdApply& apply) {
   static_assert(BW == 1 || BW == 2 || BW == 4, "nibble tables cover bitwidths 1, 2 and 4");
@@ -264,7 +269,9 @@ __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&
     for (int64_t e = full_groups * EPG; e < n; ++e) {
       float acc = add ? out[e] : 0.f;
       const int in_byte = int(e % DPB);
-      for (int r = 0; r < src.world; ++r) {
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r >= src.world) break;
         const uint32_t byte = src.payload[r][data_offset + e / DPB];
         const uint32_t nib = (byte >> (4 * (in_byte / DPN))) & 15u;
         const float v = lut[(size_t(r) * rank_stride + nib) * DPN + in_byte % DPN];
@@ -287,7 +294,7 @@ __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&
 // 32-bit word per lane; bytes reach their lanes by shuffle.
 template <bool APPLY, bool SHARED>
 __device__ __forceinline__ void unpack_nibble_body_coalesced2(const float* lut, uint32_t (&w)[kMaxWorld],
-                                                              const UnpackSources& src, int data_offset,
+                                                              const UnpackSources& src, int64_t data_offset,
                                                               float* __restrict__ out, int64_t n, int add,
                                                               float post_scale, const SgdApply& apply) {
   constexpr int rank_stride_bytes = SHARED ? 0 : 16 * 2 * 4;
@@ -340,7 +347,9 @@ __device__ __forceinline__ void unpack_nibble_body_coalesced2(const float* lut, 
   if (blockIdx.x == 0) {
     for (int64_t e = full_chunks * 512 + threadIdx.x; e < n; e += blockDim.x) {
       float acc = add ? out[e] : 0.f;
-      for (int r = 0; r < src.world; ++r) {
+#pragma unroll
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r >= src.world) break;
         const uint32_t byte = src.payload[r][data_offset + (e >> 2)];
         const uint32_t nib = (byte >> (4 * ((e & 3) >> 1))) & 15u;
         const float v = lut[(size_t(SHARED ? 0 : r) * 16 + nib) * 2 + (e & 1)];
