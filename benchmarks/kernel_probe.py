@@ -46,7 +46,7 @@ def timed(fn, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="terngrad",
-                    choices=["terngrad", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q",
+                    choices=["terngrad", "terngrad_words", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q",
                              "psgd_expand", "sgd", "adamw", "terngrad_unpack_apply", "bn_fwd", "bn_bwd",
                              "bias_relu_pool_fwd", "bias_relu_pool_bwd", "add_ln_fwd", "add_ln_bwd", "maxpool_fwd",
                              "maxpool_bwd"])
@@ -61,8 +61,13 @@ def main():
     r = torch.zeros(n, device=dev)
     hbm = peak_hbm()
     k = args.kernel
-    if k == "terngrad":
-        out = torch.empty(ops.terngrad_payload_bytes(n, 2), dtype=torch.uint8, device=dev)
+    if k in ("terngrad", "terngrad_words"):
+        # the engine places a payload 6 bytes into its slot so that the packed data behind the
+        # 10-byte header is 16-byte aligned (chunked path, 16-byte stores); "terngrad_words" keeps
+        # the payload at the start of a tensor, which takes the 4-byte-store path
+        shift = 6 if k == "terngrad" else 0
+        nbytes = ops.terngrad_payload_bytes(n, 2)
+        out = torch.empty(nbytes + 16, dtype=torch.uint8, device=dev)[shift:shift + nbytes]
         fn = lambda: ops.terngrad_compress(g, 2, True, 1, residual=r, out=out)
         traffic = n * (8 + 8 + 4 + 0.25)
     elif k == "terngrad_unpack":

@@ -79,6 +79,7 @@ runtime::EngineConfig config_from(const py::dict& d) {
   c.clear_grad = get("clear_grad", 0);
   c.device_epoch = get("device_epoch", 0);
   c.sharded = get("sharded", 0);
+  c.trace = get("trace", 0);
   c.momentum_correction = get("momentum_correction", 0);
   c.dgc_momentum = get("dgc_momentum", 0.9f);
   c.dgc_clip = get("dgc_clip", 0.0f);
@@ -467,6 +468,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            })
       .def("drain", [](runtime::DdpEngine& e) { py::gil_scoped_release nogil; e.drain(); })
       .def("check_status", &runtime::DdpEngine::check_status)
+      .def("set_progress", &runtime::DdpEngine::set_progress, py::arg("steps"), py::arg("epoch"))
+      .def("residual2",
+           [](runtime::DdpEngine& e, int device) -> c10::optional<torch::Tensor> {
+             if (e.residual2() == nullptr) return c10::nullopt;
+             // a view of the engine's buffer: valid while the engine lives
+             return torch::from_blob(e.residual2(), {e.residual2_elems()},
+                                     torch::TensorOptions().dtype(torch::kFloat32).device(torch::kCUDA, device));
+           },
+           py::arg("device"))
+      .def("wait_stats", &runtime::DdpEngine::wait_stats)
+      .def("stage_times", &runtime::DdpEngine::stage_times)
       .def_property_readonly("epoch", &runtime::DdpEngine::epoch)
       .def_property_readonly("steps", &runtime::DdpEngine::steps)
       .def_property_readonly("launches", &runtime::DdpEngine::launches)

@@ -18,6 +18,25 @@
 
 namespace hipress {
 
+// ---------------------------------------------------------------- accumulation order
+// Canonical order in which the decoded values of W ranks are summed: adjacent pairs, level by
+// level -- ((v0+v1)+(v2+v3))+((v4+v5)+(v6+v7)) for eight ranks; a rank without a partner moves
+// up a level unchanged, so three ranks give (v0+v1)+v2.  fp32 sums depend on the order; every
+// replica, the CPU codec and the kernels use this one, which keeps replicas bit-identical and
+// lets the kernels read the sum of a pair of ranks from one table entry.  With one payload the
+// sum is the decoded value itself; `decoded + out` of the accumulate mode (ref tbq_body.h:53,
+// terngrad_body.h:157) is applied to the finished sum.  Overwrites v; v[0] is also returned.
+template <int MAXW>
+HP_HD float tree_sum(float (&v)[MAXW], int world) {
+#pragma unroll
+  for (int width = 1; width < MAXW; width <<= 1) {
+#pragma unroll
+    for (int i = 0; i + width < MAXW; i += 2 * width)
+      if (i + width < world) v[i] = hp_add(v[i], v[i + width]);
+  }
+  return v[0];
+}
+
 // ---------------------------------------------------------------- TBQ
 // One element of threshold quantisation with residual feedback
 // (ref tbq_body.h:75-85).  Updates `r` in place, returns the 2-bit field.

@@ -113,6 +113,8 @@ __device__ __forceinline__ void adamw_one(const AdamWApply& a, float bc1, float 
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 adamw_kernel(float* __restrict__ grad, float scale, AdamWApply a, int64_t n) {
+  // an earlier kernel of the step recorded a failure: leave parameters and moments untouched
+  if (a.guard != nullptr && *reinterpret_cast<const volatile int*>(a.guard) != 0) return;
   const float step = float(a.step_dev != nullptr ? int(*a.step_dev) : a.step);
   const float bc1 = 1.0f - powf(a.beta1, step);
   const float rsqrt_bc2 = 1.0f / sqrtf(1.0f - powf(a.beta2, step));

@@ -41,8 +41,17 @@ struct PushTargets {
   // A single destination is normally this GPU's own slot (device-scope fences are enough);
   // set when the single destination is a peer, so that the payload is fenced at system scope.
   int remote = 0;
+  // Scatter mode (sharded exchange, > 0): the tensor is cut into shards of shard_elems elements
+  // (a multiple of 2048); shard j is compressed as a payload of its own -- own header, byte
+  // indices and rounding seed (seed + j * kShardSeedStride) -- and stored into payload[j] only.
+  // Flags of all `world` destinations are published once the whole grid is done.
+  int64_t shard_elems = 0;
+  // Device status word: when set and non-zero on entry (an earlier wait of this step timed out
+  // or a payload was malformed) the kernel returns without storing or publishing anything.
+  const int* guard = nullptr;
 };
 constexpr uint64_t kEpochSeedStride = 0x9E3779B97F4A7C15ull;
+constexpr uint64_t kShardSeedStride = 0xD6E8FEB86659FD93ull;
 
 // Payloads of all ranks as seen by the receiver, in canonical (ascending rank)
 // accumulation order.
@@ -53,6 +62,14 @@ struct UnpackSources {
   const uint32_t* epoch_dev = nullptr;    // see PushTargets
   int64_t parity_stride = 0;
   int64_t parity_off = 0;                 // set on the device by resolve_epoch()
+  // Concatenation mode (sharded exchange, > 0; a multiple of 2048): the dense tensor is the
+  // concatenation of `world` shards of shard_elems elements and payload[j] encodes shard j
+  // alone, so every element is decoded from exactly one payload (nothing is summed).
+  int64_t shard_elems = 0;
+  // Device status word: when set and non-zero on entry the kernel returns without writing (a
+  // wait earlier in the step timed out, or a payload was malformed: the slots may hold stale or
+  // partial bytes, and parameters, momentum and residuals must stay as they are).
+  const int* guard = nullptr;
 };
 
 // Optional fused SGD-with-momentum update applied to the decoded, averaged
@@ -66,6 +83,7 @@ struct SgdApply {
   // zeros where it would have written the gradient, which leaves the buffer ready for the next
   // backward pass and saves the separate clearing pass.
   int clear_grad = 0;
+  const int* guard = nullptr;  // see UnpackSources::guard (checked by sgd_apply_dense)
 };
 
 // Error codes written to a device status word by bounded waits / bounds checks.
@@ -124,8 +142,14 @@ cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n,
 // ---------------------------------------------------------------- flags
 // Spins (one warp) until flag[r] >= epoch for all r < world, or timeout_ns
 // passes; on timeout writes kFlagTimeout to *status and returns normally.
+// wait_stats (optional): three 64-bit device counters the kernel adds to -- {nanoseconds spent
+// waiting, longest single wait in ns, number of waits} -- so that time lost to slower peers can
+// be told apart from time spent computing, also when the step is replayed from a CUDA graph.
 cudaError_t wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t timeout_ns,
-                       int* status, cudaStream_t stream, const uint32_t* epoch_dev = nullptr);
+                       int* status, cudaStream_t stream, const uint32_t* epoch_dev = nullptr,
+                       unsigned long long* wait_stats = nullptr);
+// *slot = device wall clock (globaltimer, ns): a one-thread kernel that marks a point of a stream.
+cudaError_t stamp_time(unsigned long long* slot, cudaStream_t stream);
 // *epoch_dev += 1: first kernel of a step whose epoch lives on the device (see PushTargets).
 cudaError_t bump_epoch(uint32_t* epoch_dev, cudaStream_t stream);
 // Publishes `epoch` to flag[p] of every destination (release, system scope).
@@ -161,6 +185,7 @@ struct AdamWApply {
   int step = 1;  // 1-based
   int clear_grad = 0;  // write zeros over grad after reading it (see SgdApply::clear_grad)
   const uint32_t* step_dev = nullptr;  // when set, the step count is read from the device (graph replays)
+  const int* guard = nullptr;          // see UnpackSources::guard
 };
 // Fused AdamW (decoupled weight decay, bias correction) on g = scale*grad.
 cudaError_t adamw_apply_dense(float* grad, float scale, const AdamWApply& apply, int64_t n,

@@ -14,12 +14,13 @@ constexpr int kThreads = 256;
 // time: on expiry the kernel records the failure and returns, the context
 // stays usable and the host decides what to do.
 __global__ void wait_flags_kernel(const uint32_t* flags, int world, uint32_t epoch,
-                                  const uint32_t* epoch_dev, uint64_t timeout_ns, int* status) {
+                                  const uint32_t* epoch_dev, uint64_t timeout_ns, int* status,
+                                  unsigned long long* wait_stats) {
   if (epoch_dev != nullptr) epoch = *epoch_dev;
   const int lane = threadIdx.x;
   bool ok = true;
+  const uint64_t t0 = globaltimer_ns();
   if (lane < world) {
-    const uint64_t t0 = globaltimer_ns();
     ok = false;
     for (;;) {
       const uint32_t v = ld_acquire_sys(flags + lane);
@@ -33,7 +34,15 @@ __global__ void wait_flags_kernel(const uint32_t* flags, int world, uint32_t epo
   }
   const unsigned int all = __ballot_sync(0xffffffffu, ok);
   if (lane == 0 && all != 0xffffffffu && status != nullptr) atomicExch(status, int(kFlagTimeout));
+  if (lane == 0 && wait_stats != nullptr) {
+    const unsigned long long waited = globaltimer_ns() - t0;   // every lane is done after the ballot
+    atomicAdd(wait_stats, waited);
+    atomicMax(wait_stats + 1, waited);
+    atomicAdd(wait_stats + 2, 1ull);
+  }
 }
+
+__global__ void stamp_time_kernel(unsigned long long* slot) { *slot = globaltimer_ns(); }
 
 __global__ void signal_flags_kernel(PushTargets dst) {
   resolve_epoch(dst);
@@ -46,6 +55,8 @@ __global__ void signal_flags_kernel(PushTargets dst) {
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
 sgd_dense_kernel(float* __restrict__ grad, float scale, SgdApply a, int64_t n) {
+  // an earlier kernel of the step recorded a failure: leave parameters and momentum untouched
+  if (a.guard != nullptr && *reinterpret_cast<const volatile int*>(a.guard) != 0) return;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   const int64_t tid = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (VEC) {
@@ -114,9 +125,16 @@ inline int grid_for(int64_t items, int max_blocks) {
 }  // namespace
 
 cudaError_t wait_flags(const uint32_t* flags, int world, uint32_t epoch, uint64_t timeout_ns,
-                       int* status, cudaStream_t stream, const uint32_t* epoch_dev) {
+                       int* status, cudaStream_t stream, const uint32_t* epoch_dev,
+                       unsigned long long* wait_stats) {
   if (world < 1 || world > kMaxWorld) return cudaErrorInvalidValue;
-  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, epoch_dev, timeout_ns, status);
+  wait_flags_kernel<<<1, 32, 0, stream>>>(flags, world, epoch, epoch_dev, timeout_ns, status, wait_stats);
+  return cudaGetLastError();
+}
+
+cudaError_t stamp_time(unsigned long long* slot, cudaStream_t stream) {
+  if (slot == nullptr) return cudaErrorInvalidValue;
+  stamp_time_kernel<<<1, 1, 0, stream>>>(slot);
   return cudaGetLastError();
 }
 

@@ -8,6 +8,7 @@
 
 #include "../common/codec_math.h"
 #include "kernels.h"
+#include "reduce.cuh"
 
 namespace {
 
@@ -44,7 +45,8 @@ extern "C" int hipress_terngrad_compress_noalloc(const float* grad, float* resid
                                                  int bitwidth, int enable_random,
                                                  unsigned long long seed, unsigned char* out,
                                                  long long out_bytes, void* stream) {
-  static_assert(HIPRESS_NOALLOC_SCRATCH_BYTES >= 0, "");
+  static_assert(sizeof(hipress::cuda::MinMaxScratch) <= HIPRESS_NOALLOC_SCRATCH_BYTES,
+                "the built-in scratch must hold the min/max reduction state");
   if (grad == nullptr || out == nullptr || n <= 0 || !hipress::tern_bitwidth_ok(bitwidth)) {
     t_last_error = "bad argument";
     return HIPRESS_ERR_ARGUMENT;

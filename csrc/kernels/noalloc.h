@@ -11,8 +11,9 @@
 // ctypes and owns every buffer itself.  Such callers bring the input, the
 // optional residual and the output buffer; the only other memory the TernGrad
 // compressor needs is its small min/max reduction scratch, and that lives in
-// a fixed device array inside this library (about 8 KB per GPU that loads the
-// library, held until the process exits).
+// a fixed device array inside this library (16 KB per GPU that loads the
+// library, of which the reduction state uses about 8 KB; held until the process
+// exits).
 //
 // Rules of use:
 //  * The first call on each device looks up the device address of the built-in

@@ -63,12 +63,77 @@ __device__ __forceinline__ void push_u8(const PushTargets& t, int64_t byte_off, 
   for (int p = 0; p < kMaxWorld; ++p)
     if (p < t.world) t.payload[p][t.parity_off + byte_off] = v;
 }
+// 16 payload bytes to every destination; byte_off and the destinations 16-byte aligned
+// (push_aligned16).  Peer stores of this width cross NVLink as full 128-byte+ runs per warp
+// instead of one 32-byte sector per warp and destination.
+__device__ __forceinline__ void push_u128(const PushTargets& t, int64_t byte_off, uint4 v) {
+#pragma unroll
+  for (int p = 0; p < kMaxWorld; ++p)
+    if (p < t.world) *reinterpret_cast<uint4*>(t.payload[p] + t.parity_off + byte_off) = v;
+}
+// True when payload + data_off is 16-byte aligned in every destination.
+__device__ __forceinline__ bool push_aligned16(const PushTargets& t, int64_t data_off) {
+  uintptr_t bits = 0;
+#pragma unroll
+  for (int p = 0; p < kMaxWorld; ++p)
+    if (p < t.world) bits |= reinterpret_cast<uintptr_t>(t.payload[p] + t.parity_off + data_off);
+  return (bits & 15) == 0;
+}
+// payload[j] (+ parity offset) for a run-time j: selects over compile-time indices, so that the
+// kernel argument stays in parameter space (see resolve_epoch).
+__device__ __forceinline__ uint8_t* select_dest(const PushTargets& t, int j) {
+  uint8_t* d = t.payload[0];
+#pragma unroll
+  for (int p = 1; p < kMaxWorld; ++p)
+    if (p == j) d = t.payload[p];
+  return d + t.parity_off;
+}
+// True when an earlier kernel of the step recorded a failure (see PushTargets::guard).
+__device__ __forceinline__ bool status_guarded(const int* guard) {
+  return guard != nullptr && *reinterpret_cast<const volatile int*>(guard) != 0;
+}
+__device__ __forceinline__ bool push_guarded(const PushTargets& t) { return status_guarded(t.guard); }
+// Elements of shard j when n elements are cut into shards of S.
+__device__ __forceinline__ int64_t shard_len(int64_t n, int64_t S, int j) {
+  const int64_t left = n - int64_t(j) * S;
+  return left <= 0 ? 0 : (left < S ? left : S);
+}
+
+// Where the bytes of the tensor part being compressed go: every destination (all-gather form)
+// or, in scatter mode, the one destination that owns the current shard.
+struct PushCursor {
+  uint8_t* one;  // scatter mode: payload of the current shard's owner; null otherwise
+};
+__device__ __forceinline__ void put_u128(const PushTargets& t, const PushCursor& c, int64_t off, uint4 v) {
+  if (c.one) *reinterpret_cast<uint4*>(c.one + off) = v;
+  else push_u128(t, off, v);
+}
+__device__ __forceinline__ void put_u32(const PushTargets& t, const PushCursor& c, int64_t off, uint32_t v);
+__device__ __forceinline__ void put_u8(const PushTargets& t, const PushCursor& c, int64_t off, uint8_t v);
+
 __device__ __forceinline__ void push_bytes(const PushTargets& t, int64_t byte_off,
                                            const uint8_t* src, int count) {
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p)
     if (p < t.world)
       for (int i = 0; i < count; ++i) t.payload[p][t.parity_off + byte_off + i] = src[i];
+}
+
+__device__ __forceinline__ void put_u32(const PushTargets& t, const PushCursor& c, int64_t off, uint32_t v) {
+  if (c.one) store_u32_any(c.one + off, v);
+  else push_u32(t, off, v);
+}
+__device__ __forceinline__ void put_u8(const PushTargets& t, const PushCursor& c, int64_t off, uint8_t v) {
+  if (c.one) c.one[off] = v;
+  else push_u8(t, off, v);
+}
+__device__ __forceinline__ void put_bytes(const PushTargets& t, const PushCursor& c, int64_t off,
+                                          const uint8_t* src, int count) {
+  if (c.one) {
+    for (int i = 0; i < count; ++i) c.one[off + i] = src[i];
+  } else {
+    push_bytes(t, off, src, count);
+  }
 }
 
 // Called by every thread at the end of a compressing kernel.  Elects the last

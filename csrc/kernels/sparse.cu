@@ -499,7 +499,9 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
 
 __global__ void __launch_bounds__(kThreads)
 scatter_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restrict__ out, int64_t n,
-               float post_scale, int* status, const uint32_t* epoch_dev, int64_t parity_stride) {
+               float post_scale, int* status, const uint32_t* epoch_dev, int64_t parity_stride,
+               const int* guard) {
+  if (status_guarded(guard)) return;
   if (epoch_dev != nullptr && (*epoch_dev & 1u)) payload += parity_stride;  // see UnpackSources
   uint32_t total = 0;
   for (int k = 0; k < 4; ++k) total |= uint32_t(payload[k]) << (8 * k);
@@ -589,7 +591,7 @@ cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n,
     if (blocks > 148 * 8) blocks = 148 * 8;
     scatter_kernel<<<int(blocks), kThreads, 0, stream>>>(src.payload[r], src.payload_bytes[r], out,
                                                         n, post_scale, status, src.epoch_dev,
-                                                        src.parity_stride);
+                                                        src.parity_stride, src.guard);
   }
   return cudaGetLastError();
 }

@@ -1,16 +1,20 @@
-// One-pass decode + accumulate of up to 8 packed payloads through a
-// shared-memory byte table.
+// One-pass decode + accumulate of up to 8 packed payloads through shared-memory tables.
 //
-// A payload byte holds DPB = 8/bitwidth quantised elements.  Instead of
-// extracting and dequantising every field with integer and floating-point
-// instructions (which made the first version of these kernels issue-bound at
-// ~136 instructions per element for 8 ranks), each CTA first builds, per rank,
-// a table  byte value -> DPB decoded floats  (256 x DPB entries, computed with
-// the same contraction-free arithmetic as the CPU codec), and the main loop
-// then needs one 32-bit payload load per 4 bytes and one vector shared-memory
-// load per byte, plus the adds.  Accumulation order is the canonical one
-// (ascending rank, acc = decoded + acc), so results are bit-identical to
-// decoding the payloads one after another.
+// A payload byte holds DPB = 8/bitwidth quantised elements.  Instead of extracting and
+// dequantising every field with integer and floating-point instructions (which made the first
+// version of these kernels issue-bound at ~136 instructions per element for 8 ranks), each CTA
+// first builds decode tables with the same contraction-free arithmetic as the CPU codec, and
+// the main loop needs one 32-bit payload load per 4 bytes and rank plus table reads and adds.
+//
+// The decoded values of the ranks are summed in the canonical pairwise order (tree_sum in
+// codec_math.h), so the result is bit-identical to the CPU codec on every replica.  Three table
+// forms, fastest first:
+//   pair tables     2-bit payloads, 16-byte aligned dense arrays: ranks (2s, 2s+1) share a table
+//                   indexed by one nibble of each, whose entry already holds the pair's sum
+//                   (the first level of the canonical order), so eight ranks cost four
+//                   shared-memory reads and three adds per two elements
+//   nibble tables   bitwidths 1, 2, 4 at any alignment
+//   byte tables     bitwidth 8 or unknown
 #pragma once
 #include "../common/codec_math.h"
 #include "kernels.h"
@@ -41,26 +45,81 @@ __device__ __forceinline__ void sgd_update4(const SgdApply& a, int64_t i, const 
   *reinterpret_cast<float4*>(a.param + i) = make_float4(p[0], p[1], p[2], p[3]);
 }
 
+// True when an earlier kernel of the step recorded a failure: the caller returns without writing.
+__device__ __forceinline__ bool unpack_guarded(const UnpackSources& src) {
+  return src.guard != nullptr && *reinterpret_cast<const volatile int*>(src.guard) != 0;
+}
+
+// payload[j] for a run-time j without indexing the kernel-parameter array dynamically (which
+// would move the whole struct into local memory): a chain of selects over compile-time indices.
+__device__ __forceinline__ const uint8_t* select_payload(const UnpackSources& src, int j) {
+  const uint8_t* p = src.payload[0];
+#pragma unroll
+  for (int r = 1; r < kMaxWorld; ++r)
+    if (r == j) p = src.payload[r];
+  return p;
+}
+__device__ __forceinline__ int64_t select_payload_bytes(const UnpackSources& src, int j) {
+  int64_t b = src.payload_bytes[0];
+#pragma unroll
+  for (int r = 1; r < kMaxWorld; ++r)
+    if (r == j) b = src.payload_bytes[r];
+  return b;
+}
+
+// Elements of shard j when a tensor of n elements is cut into shards of S.
+__device__ __forceinline__ int64_t shard_count(int64_t n, int64_t S, int j) {
+  const int64_t left = n - int64_t(j) * S;
+  return left <= 0 ? 0 : (left < S ? left : S);
+}
+
+// Finish one group of 4 consecutive elements: accumulate mode, scale, store, fused update.
+template <bool APPLY>
+__device__ __forceinline__ void unpack_finish4(float (&acc)[4], float* __restrict__ out, int64_t e, int add,
+                                               float post_scale, const SgdApply& apply) {
+  if (add) {
+    const float4 o = *reinterpret_cast<const float4*>(out + e);
+    acc[0] = hp_add(acc[0], o.x); acc[1] = hp_add(acc[1], o.y);
+    acc[2] = hp_add(acc[2], o.z); acc[3] = hp_add(acc[3], o.w);
+  }
+  if (post_scale != 1.0f) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] = hp_mul(acc[k], post_scale);
+  }
+  const bool clear = APPLY && apply.clear_grad;
+  *reinterpret_cast<float4*>(out + e) =
+      clear ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(acc[0], acc[1], acc[2], acc[3]);
+  if (APPLY) sgd_update4(apply, e, acc);
+}
+template <bool APPLY>
+__device__ __forceinline__ void unpack_finish1(float acc, float* __restrict__ out, int64_t e, int add,
+                                               float post_scale, const SgdApply& apply) {
+  if (add) acc = hp_add(acc, out[e]);
+  if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
+  out[e] = (APPLY && apply.clear_grad) ? 0.f : acc;
+  if (APPLY) sgd_update(apply, e, acc);
+}
+
 // Table row of byte value v.  Gradient payloads are dominated by a few byte values (fields
 // near the middle levels); with rows stored in natural order those values fall on only four
 // of the eight 16-byte bank groups and every table read is a multi-way bank conflict.  XOR-ing
 // two higher bits into the low bits spreads them over all eight groups (a bijection on 0..255).
 __device__ __forceinline__ uint32_t lut_row(uint32_t v) { return v ^ ((v >> 3) & 5u); }
 
-// lut: shared memory, entry (rank r, byte v, slot j) at lut[(r*rank_stride + lut_row(v))*DPB + j];
-// rank_stride is 256 for per-rank tables and 0 when all ranks share one table.
-// data_offset: bytes to skip at the start of each payload (header size).
+// ---------------------------------------------------------------- byte tables
+// lut: shared memory, entry (rank r, byte v, slot j) at lut[(r*256 + lut_row(v))*DPB + j].
+// data_offset: bytes to skip at the start of each payload (header size + slot shift).
 template <int DPB, bool APPLY>
-__device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_stride,
-                                                const UnpackSources& src, int64_t data_offset,
+__device__ __forceinline__ void unpack_lut_body(const float* lut, const UnpackSources& src, int64_t data_offset,
                                                 float* __restrict__ out, int64_t n, int add,
                                                 float post_scale, const SgdApply& apply) {
   constexpr int EPG = 4 * DPB;  // elements per group of 4 payload bytes
+  constexpr int VW = DPB >= 4 ? 4 : DPB;  // values fetched per table read
   const int64_t full_groups = n / EPG;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  const bool out_vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-  const bool apply_vec = APPLY && ((reinterpret_cast<uintptr_t>(apply.param) |
-                                    reinterpret_cast<uintptr_t>(apply.momentum)) & 15) == 0;
+  const bool vec = ((reinterpret_cast<uintptr_t>(out) |
+                     (APPLY ? (reinterpret_cast<uintptr_t>(apply.param) |
+                               reinterpret_cast<uintptr_t>(apply.momentum)) : uintptr_t(0))) & 15) == 0;
   int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   // payload words of the group being decoded; the next group's words are requested before
   // the current ones are used, so their latency hides behind the decode
@@ -75,59 +134,36 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r)
       wn[r] = (r < src.world && nxt < full_groups) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
-    float acc[EPG];
-    if (add) {
 #pragma unroll
-      for (int k = 0; k < EPG; ++k) acc[k] = out[e0 + k];
-    }
+    for (int b = 0; b < 4; ++b) {
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r < src.world) {
-        const float* table = lut + size_t(r) * rank_stride * DPB;
+      for (int q = 0; q < DPB / VW; ++q) {
+        float v[VW][kMaxWorld];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) {
-          const float* e = table + lut_row((w[r] >> (8 * b)) & 255u) * DPB;
-          float v[DPB];
-          if (DPB % 4 == 0) {
-#pragma unroll
-            for (int q = 0; q < DPB / 4; ++q) {
-              const float4 t = reinterpret_cast<const float4*>(e)[q];
-              v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+        for (int r = 0; r < kMaxWorld; ++r) {
+          if (r < src.world) {
+            const float* e = lut + (size_t(r) * 256 + lut_row((w[r] >> (8 * b)) & 255u)) * DPB + q * VW;
+            if (VW == 4) {
+              const float4 t = *reinterpret_cast<const float4*>(e);
+              v[0][r] = t.x; v[1][r] = t.y; v[2][r] = t.z; v[3][r] = t.w;
+            } else if (VW == 2) {
+              const float2 t = *reinterpret_cast<const float2*>(e);
+              v[0][r] = t.x; v[1][r] = t.y;
+            } else {
+              v[0][r] = e[0];
             }
-          } else if (DPB == 2) {
-            const float2 t = *reinterpret_cast<const float2*>(e);
-            v[0] = t.x; v[1] = t.y;
-          } else {
-            v[0] = e[0];
           }
-#pragma unroll
-          for (int j = 0; j < DPB; ++j)
-            acc[b * DPB + j] = (r == 0 && !add) ? v[j] : hp_add(v[j], acc[b * DPB + j]);
         }
-      }
-    }
-    if (post_scale != 1.0f) {
+        float acc[VW];
 #pragma unroll
-      for (int k = 0; k < EPG; ++k) acc[k] = hp_mul(acc[k], post_scale);
-    }
-    const bool clear = APPLY && apply.clear_grad;
-    if (out_vec) {
+        for (int k = 0; k < VW; ++k) acc[k] = tree_sum(v[k], src.world);
+        const int64_t e = e0 + b * DPB + q * VW;
+        if (VW == 4 && vec) {
+          unpack_finish4<APPLY>(*reinterpret_cast<float(*)[4]>(acc), out, e, add, post_scale, apply);
+        } else {
 #pragma unroll
-      for (int q = 0; q < EPG / 4; ++q)
-        reinterpret_cast<float4*>(out + e0)[q] =
-            clear ? make_float4(0.f, 0.f, 0.f, 0.f)
-                  : make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-    } else {
-#pragma unroll
-      for (int k = 0; k < EPG; ++k) out[e0 + k] = clear ? 0.f : acc[k];
-    }
-    if (APPLY) {
-      if (apply_vec) {
-#pragma unroll
-        for (int q = 0; q < EPG / 4; ++q) sgd_update4(apply, e0 + 4 * q, acc + 4 * q);
-      } else {
-#pragma unroll
-        for (int k = 0; k < EPG; ++k) sgd_update(apply, e0 + k, acc[k]);
+          for (int k = 0; k < VW; ++k) unpack_finish1<APPLY>(acc[k], out, e + k, add, post_scale, apply);
+        }
       }
     }
 #pragma unroll
@@ -136,17 +172,15 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
   // fewer than EPG leftover elements: one thread, element by element
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     for (int64_t e = full_groups * EPG; e < n; ++e) {
-      float acc = add ? out[e] : 0.f;
+      float v[kMaxWorld];
 #pragma unroll
       for (int r = 0; r < kMaxWorld; ++r) {
-        if (r >= src.world) break;
-        const uint32_t byte = src.payload[r][data_offset + e / DPB];
-        const float v = lut[(size_t(r) * rank_stride + lut_row(byte)) * DPB + int(e % DPB)];
-        acc = (r == 0 && !add) ? v : hp_add(v, acc);
+        if (r < src.world) {
+          const uint32_t byte = src.payload[r][data_offset + e / DPB];
+          v[r] = lut[(size_t(r) * 256 + lut_row(byte)) * DPB + int(e % DPB)];
+        }
       }
-      if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
-      out[e] = (APPLY && apply.clear_grad) ? 0.f : acc;
-      if (APPLY) sgd_update(apply, e, acc);
+      unpack_finish1<APPLY>(tree_sum(v, src.world), out, e, add, post_scale, apply);
     }
   }
 }
@@ -157,8 +191,7 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, int rank_strid
 // per quarter-warp read for 2-bit gradient payloads).  For bitwidths 1, 2 and 4 the table can
 // instead be indexed by a 4-bit nibble: 16 rows of 4/BW floats.  At 2 bits a rank's table is
 // exactly 128 bytes -- one row of all 32 banks -- so any two lanes either read the same row
-// (a broadcast) or different banks: the reads are conflict free whatever the data, the table
-// needs no swizzle, and building it is 16 entries per rank instead of 256.
+// (a broadcast) or different banks: the reads are conflict free whatever the data.
 //
 // lut: entry (rank r, nibble v, slot j) at lut[(r*16 + v)*DPN + j], DPN = 4/BW (r = 0 when shared).
 //
@@ -195,9 +228,6 @@ __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&
   constexpr int rank_stride = SHARED ? 0 : 16;
   const int64_t full_groups = n / EPG;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  const bool out_vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-  const bool apply_vec = APPLY && ((reinterpret_cast<uintptr_t>(apply.param) |
-                                    reinterpret_cast<uintptr_t>(apply.momentum)) & 15) == 0;
   int64_t grp = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   for (; grp < full_groups; grp += stride) {
     const int64_t e0 = grp * EPG;
@@ -206,59 +236,30 @@ __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r)
       wn[r] = (r < src.world && nxt < full_groups) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
-    float acc[EPG];
-    if (add) {
 #pragma unroll
-      for (int k = 0; k < EPG; ++k) acc[k] = out[e0 + k];
-    }
+    for (int k = 0; k < 8; ++k) {
+      float v[DPN][kMaxWorld];
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r < src.world) {
-        const char* table = reinterpret_cast<const char*>(lut) + r * rank_stride * DPN * 4;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
+      for (int r = 0; r < kMaxWorld; ++r) {
+        if (r < src.world) {
+          const char* table = reinterpret_cast<const char*>(lut) + r * rank_stride * DPN * 4;
           // byte offset of the row of nibble k: ((w >> 4k) & 15) << ROW_SHIFT in one shift + mask
           const uint32_t off = (4 * k >= ROW_SHIFT ? (w[r] >> (4 * k - ROW_SHIFT)) : (w[r] << (ROW_SHIFT - 4 * k))) &
                                (15u << ROW_SHIFT);
-          float v[DPN];
           if (DPN == 4) {
             const float4 t = *reinterpret_cast<const float4*>(table + off);
-            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+            v[0][r] = t.x; v[1 % DPN][r] = t.y; v[2 % DPN][r] = t.z; v[3 % DPN][r] = t.w;
           } else if (DPN == 2) {
             const float2 t = *reinterpret_cast<const float2*>(table + off);
-            v[0] = t.x; v[1] = t.y;
+            v[0][r] = t.x; v[1 % DPN][r] = t.y;
           } else {
-            v[0] = *reinterpret_cast<const float*>(table + off);
+            v[0][r] = *reinterpret_cast<const float*>(table + off);
           }
-#pragma unroll
-          for (int j = 0; j < DPN; ++j)
-            acc[k * DPN + j] = (r == 0 && !add) ? v[j] : hp_add(v[j], acc[k * DPN + j]);
         }
       }
-    }
-    if (post_scale != 1.0f) {
 #pragma unroll
-      for (int k = 0; k < EPG; ++k) acc[k] = hp_mul(acc[k], post_scale);
-    }
-    const bool clear = APPLY && apply.clear_grad;
-    if (out_vec) {
-#pragma unroll
-      for (int q = 0; q < EPG / 4; ++q)
-        reinterpret_cast<float4*>(out + e0)[q] =
-            clear ? make_float4(0.f, 0.f, 0.f, 0.f)
-                  : make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
-    } else {
-#pragma unroll
-      for (int k = 0; k < EPG; ++k) out[e0 + k] = clear ? 0.f : acc[k];
-    }
-    if (APPLY) {
-      if (apply_vec) {
-#pragma unroll
-        for (int q = 0; q < EPG / 4; ++q) sgd_update4(apply, e0 + 4 * q, acc + 4 * q);
-      } else {
-#pragma unroll
-        for (int k = 0; k < EPG; ++k) sgd_update(apply, e0 + k, acc[k]);
-      }
+      for (int j = 0; j < DPN; ++j)
+        unpack_finish1<APPLY>(tree_sum(v[j], src.world), out, e0 + k * DPN + j, add, post_scale, apply);
     }
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r) w[r] = wn[r];
@@ -267,42 +268,76 @@ __device__ __forceinline__ void unpack_nibble_body(const float* lut, uint32_t (&
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     constexpr int DPB = 8 / BW;
     for (int64_t e = full_groups * EPG; e < n; ++e) {
-      float acc = add ? out[e] : 0.f;
       const int in_byte = int(e % DPB);
+      float v[kMaxWorld];
 #pragma unroll
       for (int r = 0; r < kMaxWorld; ++r) {
-        if (r >= src.world) break;
-        const uint32_t byte = src.payload[r][data_offset + e / DPB];
-        const uint32_t nib = (byte >> (4 * (in_byte / DPN))) & 15u;
-        const float v = lut[(size_t(r) * rank_stride + nib) * DPN + in_byte % DPN];
-        acc = (r == 0 && !add) ? v : hp_add(v, acc);
+        if (r < src.world) {
+          const uint32_t byte = src.payload[r][data_offset + e / DPB];
+          const uint32_t nib = (byte >> (4 * (in_byte / DPN))) & 15u;
+          v[r] = lut[(size_t(r) * rank_stride + nib) * DPN + in_byte % DPN];
+        }
       }
-      if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
-      out[e] = (APPLY && apply.clear_grad) ? 0.f : acc;
-      if (APPLY) sgd_update(apply, e, acc);
+      unpack_finish1<APPLY>(tree_sum(v, src.world), out, e, add, post_scale, apply);
     }
   }
 }
 
-// ---------------------------------------------------------------- one or two payloads, 2 bits
-// With one or two payloads the kernel is bound by the dense traffic (gradient out, parameters
-// and momentum in and out), not by the decode, and the mapping above -- a thread owning 64
-// contiguous bytes of every dense array -- makes each 16-byte access of a warp touch 32
-// different sectors.  Here lane L of a warp handles payload byte j*32 + L (j = 0..3) of the
-// warp's 128-byte payload chunk, i.e. elements (j*32 + L)*4 .. +3 of the chunk's 512: every
-// dense access is a 512-byte contiguous run across the warp.  The payload is still loaded one
-// 32-bit word per lane; bytes reach their lanes by shuffle.
+// ---------------------------------------------------------------- pair tables, 2 bits
+// Slot s covers ranks (2s, 2s+1).  Its table has 256 rows of two floats: row (b << 4) | a holds
+// decode_{2s}(a) + decode_{2s+1}(b) for the two elements of nibbles a and b, i.e. the first
+// level of the canonical sum is read, not computed.  A last rank without a partner uses rows
+// 0..15 of its slot (b = 0), which hold its decoded values alone.
+//
+// Index words: for payload words wa, wb of the two ranks, lo = (wa & 0x0f0f0f0f) | ((wb << 4) &
+// 0xf0f0f0f0) packs the four row numbers of the even nibbles into the bytes of one register and
+// hi = ((wa >> 4) & 0x0f0f0f0f) | (wb & 0xf0f0f0f0) those of the odd nibbles: eight look-ups
+// cost four logic instructions to prepare.  Rows are stored swizzled, row ^ ((row >> 4) & 5):
+// gradient nibbles are mostly 5, 6, 9 or 10 (both fields on a middle level), and without the
+// swizzle two lanes that agree in a and differ in b hit the same bank on different rows.
+//
+// Mapping: lane L of a warp handles payload byte j*32 + L (j = 0..3) of the warp's 128-byte
+// chunk, i.e. elements (j*32 + L)*4 .. +3 of the chunk's 512: every dense access is a 512-byte
+// contiguous run across the warp.  Payloads are loaded one 32-bit word per lane and rank; index
+// words reach their lanes by shuffle.
+constexpr int kPairRows = 256;
+__device__ __forceinline__ uint32_t pair_swizzle(uint32_t packed_rows) {
+  return packed_rows ^ ((packed_rows >> 4) & 0x05050505u);
+}
+
+// value(r, nibble, which): decoded value of element `which` (0/1) of a nibble of rank r.
+// tables: [slots][256][2] floats; slots = (world + 1) / 2, or one table when SHARED (all ranks
+// decode alike, and the lone rank of an odd world reads the pair rows of a partner that decodes
+// to zero: lone_nibble is that partner's nibble).
+template <bool SHARED, typename Value>
+__device__ __forceinline__ void build_pair_tables(float* tables, int world, Value value) {
+  const int slots = SHARED ? 1 : (world + 1) / 2;
+  for (int i = threadIdx.x; i < slots * kPairRows; i += blockDim.x) {
+    const int s = i >> 8, row = i & 255, a = row & 15, b = row >> 4;
+    const int ra = 2 * s, rb = 2 * s + 1;
+    const bool lone = !SHARED && rb >= world;
+    if (lone && b != 0) continue;
+    float x = value(ra, a, 0), y = value(ra, a, 1);
+    if (!lone) {
+      x = hp_add(x, value(rb, b, 0));
+      y = hp_add(y, value(rb, b, 1));
+    }
+    const int at = row ^ ((row >> 4) & 5);
+    reinterpret_cast<float2*>(tables)[s * kPairRows + at] = make_float2(x, y);
+  }
+}
+
 template <bool APPLY, bool SHARED>
-__device__ __forceinline__ void unpack_nibble_body_coalesced2(const float* lut, uint32_t (&w)[kMaxWorld],
-                                                              const UnpackSources& src, int64_t data_offset,
-                                                              float* __restrict__ out, int64_t n, int add,
-                                                              float post_scale, const SgdApply& apply) {
-  constexpr int rank_stride_bytes = SHARED ? 0 : 16 * 2 * 4;
-  const int64_t full_groups = n / 16;            // complete 32-bit payload words
-  const int64_t full_chunks = full_groups / 32;  // complete 128-byte warp chunks
+__device__ __forceinline__ void unpack_pair_body(const float* tables, uint32_t lone_word, uint32_t (&w)[kMaxWorld],
+                                                 const UnpackSources& src, int64_t data_offset,
+                                                 float* __restrict__ out, int64_t n, int add,
+                                                 float post_scale, const SgdApply& apply) {
+  constexpr int kSlots = kMaxWorld / 2;
+  const int slots = (src.world + 1) / 2;
+  const int64_t full_chunks = n / 512;  // complete 128-byte warp chunks
   const int lane = threadIdx.x & 31;
+  const uint32_t sel = 0x4440u | uint32_t(lane & 3);  // byte (lane & 3) of a register, zero-extended
   const int64_t warps = int64_t(gridDim.x) * (blockDim.x >> 5);
-  const bool clear = APPLY && apply.clear_grad;
   int64_t chunk = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   for (; chunk < full_chunks; chunk += warps) {
     const int64_t nxt = (chunk + warps) * 32 + lane;
@@ -310,65 +345,107 @@ __device__ __forceinline__ void unpack_nibble_body_coalesced2(const float* lut, 
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r)
       wn[r] = (r < src.world && chunk + warps < full_chunks) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
+    uint32_t lo[kSlots], hi[kSlots];
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+      if (s < slots) {
+        const uint32_t wa = w[2 * s];
+        const uint32_t wb = (2 * s + 1 < src.world) ? w[2 * s + 1] : lone_word;
+        lo[s] = pair_swizzle((wa & 0x0f0f0f0fu) | ((wb << 4) & 0xf0f0f0f0u));
+        hi[s] = pair_swizzle(((wa >> 4) & 0x0f0f0f0fu) | (wb & 0xf0f0f0f0u));
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int64_t e = chunk * 512 + int64_t(j * 32 + lane) * 4;
-      float acc[4];
-      if (add) {
-        const float4 o = *reinterpret_cast<const float4*>(out + e);
-        acc[0] = o.x; acc[1] = o.y; acc[2] = o.z; acc[3] = o.w;
-      }
+      const int from = j * 8 + (lane >> 2);
+      float v[4][kSlots];
 #pragma unroll
-      for (int r = 0; r < kMaxWorld; ++r) {
-        if (r < src.world) {
-          const uint32_t word = __shfl_sync(0xffffffffu, w[r], j * 8 + (lane >> 2));
-          const uint32_t byte = (word >> (8 * (lane & 3))) & 255u;
-          const char* table = reinterpret_cast<const char*>(lut) + r * rank_stride_bytes;
-          const float2 lo = *reinterpret_cast<const float2*>(table + ((byte & 15u) << 3));
-          const float2 hi = *reinterpret_cast<const float2*>(table + ((byte >> 4) << 3));
-          const float v[4] = {lo.x, lo.y, hi.x, hi.y};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) acc[k] = (r == 0 && !add) ? v[k] : hp_add(v[k], acc[k]);
+      for (int s = 0; s < kSlots; ++s) {
+        if (s < slots) {
+          const uint32_t l = __shfl_sync(0xffffffffu, lo[s], from);
+          const uint32_t h = __shfl_sync(0xffffffffu, hi[s], from);
+          const char* table = reinterpret_cast<const char*>(tables) + (SHARED ? 0 : s * kPairRows * 8);
+          const float2 a = *reinterpret_cast<const float2*>(table + (__byte_perm(l, 0u, sel) << 3));
+          const float2 b = *reinterpret_cast<const float2*>(table + (__byte_perm(h, 0u, sel) << 3));
+          v[0][s] = a.x; v[1][s] = a.y; v[2][s] = b.x; v[3][s] = b.y;
         }
       }
-      if (post_scale != 1.0f) {
+      float acc[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) acc[k] = hp_mul(acc[k], post_scale);
-      }
-      *reinterpret_cast<float4*>(out + e) =
-          clear ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(acc[0], acc[1], acc[2], acc[3]);
-      if (APPLY) sgd_update4(apply, e, acc);
+      for (int k = 0; k < 4; ++k) acc[k] = tree_sum(v[k], slots);
+      unpack_finish4<APPLY>(acc, out, chunk * 512 + int64_t(j * 32 + lane) * 4, add, post_scale, apply);
     }
 #pragma unroll
     for (int r = 0; r < kMaxWorld; ++r) w[r] = wn[r];
   }
-  // payload words past the last complete chunk (fewer than 32) and the elements past the last
-  // complete word (fewer than 16): block 0, element by element
+  // elements past the last complete chunk (fewer than 512): block 0, element by element,
+  // through the same tables (rank pairs, then the canonical order over the slots)
   if (blockIdx.x == 0) {
+    const uint32_t lone_nib = lone_word & 15u;
     for (int64_t e = full_chunks * 512 + threadIdx.x; e < n; e += blockDim.x) {
-      float acc = add ? out[e] : 0.f;
+      float v[kSlots];
 #pragma unroll
-      for (int r = 0; r < kMaxWorld; ++r) {
-        if (r >= src.world) break;
-        const uint32_t byte = src.payload[r][data_offset + (e >> 2)];
-        const uint32_t nib = (byte >> (4 * ((e & 3) >> 1))) & 15u;
-        const float v = lut[(size_t(SHARED ? 0 : r) * 16 + nib) * 2 + (e & 1)];
-        acc = (r == 0 && !add) ? v : hp_add(v, acc);
+      for (int s = 0; s < kSlots; ++s) {
+        if (s < slots) {
+          const int sh = 4 * int((e & 3) >> 1);
+          const uint32_t a = (uint32_t(src.payload[2 * s][data_offset + (e >> 2)]) >> sh) & 15u;
+          uint32_t b = lone_nib;
+          if (2 * s + 1 < src.world) b = (uint32_t(src.payload[2 * s + 1][data_offset + (e >> 2)]) >> sh) & 15u;
+          const uint32_t row = (b << 4) | a;
+          v[s] = tables[((SHARED ? 0 : s) * kPairRows + (row ^ ((row >> 4) & 5u))) * 2 + (e & 1)];
+        }
       }
-      if (post_scale != 1.0f) acc = hp_mul(acc, post_scale);
-      out[e] = clear ? 0.f : acc;
-      if (APPLY) sgd_update(apply, e, acc);
+      unpack_finish1<APPLY>(tree_sum(v, slots), out, e, add, post_scale, apply);
     }
   }
 }
 
-// True when unpack_nibble_body_coalesced2 applies: 2-bit payloads of at most two ranks and
-// 16-byte aligned dense arrays.
-__device__ __forceinline__ bool unpack_coalesced_ok(const UnpackSources& src, const float* out, bool apply_on,
-                                                    const SgdApply& apply) {
+// ---------------------------------------------------------------- concatenated shards, 2 bits
+// Sharded exchange, last phase: payload[j] encodes shard j alone.  nib: [world or 1][16][2]
+// nibble tables (rank j's at nib + j*32 floats; one table when SHARED).  Same lane mapping as
+// the pair body; a 512-element chunk never straddles two shards (shard_elems % 2048 == 0).
+// header_bytes + slot_shift: where the packed data starts inside payload[j].
+template <bool APPLY, bool SHARED>
+__device__ __forceinline__ void unpack_concat_body(const float* nib, const UnpackSources& src, int64_t data_offset,
+                                                   float* __restrict__ out, int64_t n, int add,
+                                                   float post_scale, const SgdApply& apply) {
+  const int64_t S = src.shard_elems;
+  const int64_t full_chunks = n / 512;
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = int64_t(gridDim.x) * (blockDim.x >> 5);
+  for (int64_t chunk = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); chunk < full_chunks;
+       chunk += warps) {
+    const int64_t e_chunk = chunk * 512;
+    const int j = int(e_chunk / S);
+    const uint8_t* p = select_payload(src, j) + data_offset + ((e_chunk - int64_t(j) * S) >> 2);
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(p + lane * 4);
+    const char* table = reinterpret_cast<const char*>(nib) + (SHARED ? 0 : j * 128);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t wq = __shfl_sync(0xffffffffu, word, q * 8 + (lane >> 2));
+      const uint32_t byte = (wq >> (8 * (lane & 3))) & 255u;
+      const float2 lo = *reinterpret_cast<const float2*>(table + ((byte & 15u) << 3));
+      const float2 hi = *reinterpret_cast<const float2*>(table + ((byte >> 4) << 3));
+      float acc[4] = {lo.x, lo.y, hi.x, hi.y};
+      unpack_finish4<APPLY>(acc, out, e_chunk + int64_t(q * 32 + lane) * 4, add, post_scale, apply);
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (int64_t e = full_chunks * 512 + threadIdx.x; e < n; e += blockDim.x) {
+      const int j = int(e / S);
+      const int64_t le = e - int64_t(j) * S;
+      const uint32_t byte = select_payload(src, j)[data_offset + (le >> 2)];
+      const uint32_t nb = (byte >> (4 * ((le & 3) >> 1))) & 15u;
+      unpack_finish1<APPLY>(nib[((SHARED ? 0 : j) * 16 + nb) * 2 + (le & 1)], out, e, add, post_scale, apply);
+    }
+  }
+}
+
+// True when the dense arrays allow the 16-byte accesses of the pair and concat bodies.
+__device__ __forceinline__ bool unpack_coalesced_ok(const float* out, bool apply_on, const SgdApply& apply) {
   uintptr_t bits = reinterpret_cast<uintptr_t>(out);
   if (apply_on) bits |= reinterpret_cast<uintptr_t>(apply.param) | reinterpret_cast<uintptr_t>(apply.momentum);
-  return src.world <= 2 && (bits & 15) == 0;
+  return (bits & 15) == 0;
 }
 
 }  // namespace cuda

@@ -56,6 +56,27 @@ cuda::UnpackSources sources_of(const std::vector<torch::Tensor>& payloads, const
   return s;
 }
 
+// CPU form of the one-pass unpack + accumulate: the decoded payloads are summed per element in
+// the canonical order (tree_sum in codec_math.h), `decoded + out` is applied to the finished
+// sum when accumulating, and the result is scaled.  decode(r, dst, add_to) decodes payload r.
+template <typename Decode>
+void cpu_accumulate(size_t world, int64_t n, float* out, bool add, double post_scale, Decode decode) {
+  if (world == 1) {
+    decode(0, out, add);
+  } else {
+    std::vector<std::vector<float>> tmp(world, std::vector<float>(size_t(n)));
+    for (size_t r = 0; r < world; ++r) decode(r, tmp[r].data(), false);
+    for (int64_t i = 0; i < n; ++i) {
+      float v[cuda::kMaxWorld];
+      for (size_t r = 0; r < world; ++r) v[r] = tmp[r][size_t(i)];
+      const float s = tree_sum(v, int(world));
+      out[i] = add ? hp_add(s, out[i]) : s;
+    }
+  }
+  if (post_scale != 1.0)
+    for (int64_t i = 0; i < n; ++i) out[i] = hp_mul(out[i], float(post_scale));
+}
+
 struct DeviceState {
   std::map<std::pair<int, cudaStream_t>, torch::Tensor> scratch;
   std::map<int, torch::Tensor> status;
@@ -157,14 +178,13 @@ void tbq_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor ou
                                          out.data_ptr<float>(), n, add ? 1 : 0, float(post_scale),
                                          cuda::SgdApply{}, at::cuda::getCurrentCUDAStream()));
   } else {
-    TORCH_CHECK(!payloads.empty(), "at least one payload expected");
-    for (size_t r = 0; r < payloads.size(); ++r)
-      cpu::tbq_decompress(payloads[r].data_ptr<uint8_t>(), n, float(threshold),
-                          out.data_ptr<float>(), (add || r > 0) ? 1 : 0);
-    if (post_scale != 1.0) {
-      float* o = out.data_ptr<float>();
-      for (int64_t i = 0; i < n; ++i) o[i] = hp_mul(o[i], float(post_scale));
-    }
+    TORCH_CHECK(!payloads.empty() && payloads.size() <= size_t(cuda::kMaxWorld),
+                "between 1 and ", cuda::kMaxWorld, " payloads expected");
+    cpu_accumulate(payloads.size(), n, out.data_ptr<float>(), add, post_scale,
+                   [&](size_t r, float* dst, bool add_to) {
+                     cpu::tbq_decompress(payloads[r].data_ptr<uint8_t>(), n, float(threshold), dst,
+                                         add_to ? 1 : 0);
+                   });
   }
 }
 
@@ -212,18 +232,15 @@ void terngrad_decompress(const std::vector<torch::Tensor>& payloads, torch::Tens
                                               status_word_for(out),
                                               at::cuda::getCurrentCUDAStream(), int(bitwidth)));
   } else {
-    TORCH_CHECK(!payloads.empty(), "at least one payload expected");
-    for (size_t r = 0; r < payloads.size(); ++r) {
-      check_u8(payloads[r], "payload");
-      const int64_t cnt = cpu::terngrad_decompress(payloads[r].data_ptr<uint8_t>(),
-                                                   payloads[r].numel(), out.data_ptr<float>(), n,
-                                                   (add || r > 0) ? 1 : 0);
-      TORCH_CHECK(cnt == n, "payload ", r, " decodes to ", cnt, " elements, expected ", n);
-    }
-    if (post_scale != 1.0) {
-      float* o = out.data_ptr<float>();
-      for (int64_t i = 0; i < n; ++i) o[i] = hp_mul(o[i], float(post_scale));
-    }
+    TORCH_CHECK(!payloads.empty() && payloads.size() <= size_t(cuda::kMaxWorld),
+                "between 1 and ", cuda::kMaxWorld, " payloads expected");
+    for (auto& p : payloads) check_u8(p, "payload");
+    cpu_accumulate(payloads.size(), n, out.data_ptr<float>(), add, post_scale,
+                   [&](size_t r, float* dst, bool add_to) {
+                     const int64_t cnt = cpu::terngrad_decompress(payloads[r].data_ptr<uint8_t>(),
+                                                                  payloads[r].numel(), dst, n, add_to ? 1 : 0);
+                     TORCH_CHECK(cnt == n, "payload ", r, " decodes to ", cnt, " elements, expected ", n);
+                   });
   }
 }
 

@@ -49,7 +49,6 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   if (cfg.sharded) {
     if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad)
       throw std::invalid_argument("the sharded exchange is implemented for the tbq and terngrad codecs");
-    if (cfg.device_epoch) throw std::invalid_argument("sharded and device_epoch cannot be combined yet");
   }
   // symmetric layout: [flags of all buckets][slots parity 0][slots parity 1] per bucket
   int64_t off = 0;
@@ -71,9 +70,9 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
     // region after the 10-byte header is 16-byte aligned for vector stores
     L.shift = (cfg.codec == Codec::kTernGrad || cfg.codec == Codec::kEcq) ? 6 : 0;
     if (cfg.sharded) {
-      // shards of a multiple of 64 elements: every shard starts 16-byte aligned in the dense
-      // buffers and its packed bytes fill whole 16-byte groups
-      L.shard_elems = round_up((buckets[b].numel + cfg.world - 1) / cfg.world, 64);
+      // shards of a multiple of 4,096 elements: every shard starts 16-byte aligned in the dense
+      // buffers and no 512-byte payload chunk of any bitwidth straddles two shards
+      L.shard_elems = round_up((buckets[b].numel + cfg.world - 1) / cfg.world, 4096);
       const int64_t cap = cfg.codec == Codec::kTbq ? tbq_payload_bytes(L.shard_elems)
                                                    : tern_payload_bytes(L.shard_elems, cfg.bitwidth);
       L.slot_bytes = round_up(cap + L.shift, 256);
@@ -103,10 +102,18 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
   if (cfg.sharded && res2 > 0) {
     check(cudaMalloc(reinterpret_cast<void**>(&residual2_), size_t(res2) * sizeof(float)), "cudaMalloc residual2");
     check(cudaMemset(residual2_, 0, size_t(res2) * sizeof(float)), "memset residual2");
+    residual2_elems_ = res2;
+  }
+  check(cudaMalloc(reinterpret_cast<void**>(&wait_ns_), 64), "cudaMalloc wait stats");
+  check(cudaMemset(wait_ns_, 0, 64), "memset wait stats");
+  if (cfg.trace) {
+    const size_t bytes = (buckets.size() * kStampCount + 2) * sizeof(unsigned long long);
+    check(cudaMalloc(reinterpret_cast<void**>(&stamps_), bytes), "cudaMalloc stamps");
+    check(cudaMemset(stamps_, 0, bytes), "memset stamps");
   }
   if (cfg.device_epoch) {
-    if (cfg.codec != Codec::kTbq && cfg.codec != Codec::kTernGrad && cfg.codec != Codec::kSparse)
-      throw std::invalid_argument("device_epoch is implemented for the tbq, terngrad, graddrop and dgc codecs");
+    if (cfg.codec == Codec::kDense)
+      throw std::invalid_argument("device_epoch is not implemented for the dense codec (its copy takes the slot parity from the host)");
     if (cfg.num_workers >= 1)
       throw std::invalid_argument("device_epoch needs inline issue (num_workers = 0): a captured step is issued by the capturing thread");
     check(cudaMalloc(reinterpret_cast<void**>(&epoch_dev_), 64), "cudaMalloc epoch");
@@ -156,6 +163,8 @@ DdpEngine::~DdpEngine() {
   if (status_) cudaFree(status_);
   if (epoch_dev_) cudaFree(epoch_dev_);
   if (residual2_) cudaFree(residual2_);
+  if (wait_ns_) cudaFree(wait_ns_);
+  if (stamps_) cudaFree(stamps_);
 }
 
 void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* momentum, float* aux,
@@ -169,7 +178,6 @@ void DdpEngine::set_buffers(float* grad, float* residual, float* param, float* m
 }
 
 void DdpEngine::set_adamw(float lr, float beta1, float beta2, float eps, float weight_decay) {
-  if (cfg_.sharded) throw std::invalid_argument("the sharded exchange applies the fused SGD only (no AdamW yet)");
   lr_ = lr;
   beta1_ = beta1;
   beta2_ = beta2;
@@ -205,6 +213,10 @@ void DdpEngine::begin_step(cudaStream_t consumer) {
     // ordered after the previous step (finish_step made `consumer` wait for its last kernels)
     // and before this step's gradients, whose ready events are recorded on `consumer`
     check(cuda::bump_epoch(epoch_dev_, consumer), "bump_epoch");
+    launches_ += 1;
+  }
+  if (stamps_) {
+    check(cuda::stamp_time(stamps_ + buckets_.size() * kStampCount, consumer), "stamp");
     launches_ += 1;
   }
   for (size_t b = 0; b < buckets_.size(); ++b) {
@@ -273,6 +285,7 @@ cuda::PushTargets DdpEngine::targets_for(int b, WorkerCtx& w) const {
   t.done = w.done;
   t.epoch_dev = epoch_dev_;
   t.parity_stride = L.slots[1] - L.slots[0];
+  t.guard = status_;
   for (int p = 0; p < cfg_.world; ++p) {
     uint8_t* base = bases_[static_cast<size_t>(p)];
     t.payload[p] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
@@ -288,6 +301,7 @@ cuda::UnpackSources DdpEngine::sources_for(int b) const {
   s.world = cfg_.world;
   s.epoch_dev = epoch_dev_;
   s.parity_stride = L.slots[1] - L.slots[0];
+  s.guard = status_;
   uint8_t* base = bases_[static_cast<size_t>(cfg_.rank)];
   for (int r = 0; r < cfg_.world; ++r) {
     s.payload[r] = base + L.slots[parity] + int64_t(r) * L.slot_bytes + L.shift;
@@ -316,53 +330,91 @@ int64_t DdpEngine::shard_len(int b, int j) const {
   return left <= 0 ? 0 : (left < S ? left : S);
 }
 
+cuda::SgdApply DdpEngine::sgd_apply_for(int b) const {
+  cuda::SgdApply apply;
+  if (fused_sgd_) {
+    const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+    apply.param = param_ + B.offset;
+    apply.momentum = momentum_ + B.offset;
+    apply.lr = lr_;
+    apply.mu = sgd_mu_;
+    apply.weight_decay = wd_;
+    // buf = g on the first step equals mu * buf + g with the zero-initialised momentum the
+    // wrappers allocate; a captured step must not bake the first-step flag in
+    apply.first_step = (steps_ == 0 && !epoch_dev_) ? 1 : 0;
+    apply.clear_grad = cfg_.clear_grad;
+    apply.guard = status_;
+  }
+  return apply;
+}
+
+void DdpEngine::issue_adamw(int b, cudaStream_t stream) {
+  if (!param_ || !momentum_ || !second_) throw std::runtime_error("AdamW needs param and both moment buffers");
+  const BucketDesc& B = buckets_[static_cast<size_t>(b)];
+  cuda::AdamWApply aw;
+  aw.param = param_ + B.offset;
+  aw.exp_avg = momentum_ + B.offset;
+  aw.exp_avg_sq = second_ + B.offset;
+  aw.lr = lr_;
+  aw.beta1 = beta1_;
+  aw.beta2 = beta2_;
+  aw.eps = eps_;
+  aw.weight_decay = wd_;
+  aw.step = int(steps_) + 1;
+  aw.step_dev = epoch_dev_;   // one epoch per step: the device counter is the 1-based step count
+  aw.clear_grad = cfg_.clear_grad;
+  aw.guard = status_;
+  check(cuda::adamw_apply_dense(grad_ + B.offset, 1.0f, aw, B.numel, stream), "adamw_apply_dense");
+}
+
+// Phase 1: every shard of the bucket is compressed as a payload of its own and stored into the
+// slot [rank] of the shard's owner -- one launch (two for TernGrad) over the whole bucket, the
+// kernels switching destination from shard to shard (PushTargets::shard_elems).
 void DdpEngine::issue_shard_push(int b, int worker) {
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
-  const int parity = int(epoch_ & 1u);
+  const int parity = epoch_dev_ ? 0 : int(epoch_ & 1u);
   check(cudaStreamWaitEvent(w.push, ready_events_[static_cast<size_t>(b)], 0), "wait ready");
-  int launched = 0;
+  stamp(b, kStampReady, w.push);
+  cuda::PushTargets dst;
+  dst.world = cfg_.world;
+  dst.epoch = epoch_;
+  dst.done = w.done;
+  dst.epoch_dev = epoch_dev_;
+  dst.parity_stride = L.slots[1] - L.slots[0];
+  dst.shard_elems = L.shard_elems;
+  dst.guard = status_;
   for (int j = 0; j < cfg_.world; ++j) {
-    const int64_t nj = shard_len(b, j);
-    const int64_t off = B.offset + int64_t(j) * L.shard_elems;
-    // one destination: my slot in the receive area of the shard's owner
-    cuda::PushTargets dst;
-    dst.world = 1;
-    dst.epoch = epoch_;
-    dst.done = w.done;
-    dst.remote = j != cfg_.rank ? 1 : 0;
     uint8_t* base = bases_[static_cast<size_t>(j)];
-    dst.payload[0] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
-    dst.flag[0] = reinterpret_cast<uint32_t*>(base + L.flags) + cfg_.rank;
-    if (nj == 0) {  // nothing of this bucket falls into shard j: only tell the owner
-      check(cuda::signal_flags(dst, w.push), "signal_flags");
-      launched += 1;
-      continue;
-    }
-    const uint64_t seed = cfg_.seed + uint64_t(epoch_) * cuda::kEpochSeedStride +
-                          uint64_t(b) * 0x632BE59BD9B4E019ull + uint64_t(j) * 0xD6E8FEB86659FD93ull;
-    float* res = residual_ ? residual_ + off : nullptr;
-    if (cfg_.codec == Codec::kTbq) {
-      if (!res) throw std::runtime_error("tbq needs a residual buffer");
-      check(cuda::tbq_compress(grad_ + off, res, nj, cfg_.threshold, dst, w.push), "tbq_compress");
-      launched += 1;
-    } else {
-      check(cuda::terngrad_compress(grad_ + off, cfg_.error_feedback ? res : nullptr, nj, cfg_.bitwidth,
-                                    cfg_.enable_random, seed, dst, w.scratch, w.push),
-            "terngrad_compress");
-      launched += 2;
-    }
+    dst.payload[j] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
+    dst.flag[j] = reinterpret_cast<uint32_t*>(base + L.flags) + cfg_.rank;
   }
+  // the kernels add the shard term (and, with the epoch on the device, the epoch term)
+  const uint64_t seed = cfg_.seed + (epoch_dev_ ? 0 : uint64_t(epoch_) * cuda::kEpochSeedStride) +
+                        uint64_t(b) * 0x632BE59BD9B4E019ull;
+  float* res = residual_ ? residual_ + B.offset : nullptr;
+  if (cfg_.codec == Codec::kTbq) {
+    if (!res) throw std::runtime_error("tbq needs a residual buffer");
+    check(cuda::tbq_compress(grad_ + B.offset, res, B.numel, cfg_.threshold, dst, w.push), "tbq_compress");
+    launches_ += 1;
+  } else {
+    check(cuda::terngrad_compress(grad_ + B.offset, cfg_.error_feedback ? res : nullptr, B.numel, cfg_.bitwidth,
+                                  cfg_.enable_random, seed, dst, w.scratch, w.push),
+          "terngrad_compress");
+    launches_ += 2;
+  }
+  stamp(b, kStampPushed, w.push);
   check(cudaEventRecord(w.pushed, w.push), "record pushed");
-  launches_ += launched;
 }
 
+// Phase 2: the owner decodes the `world` payloads of its shard in one pass, averages, and
+// re-compresses the average with its own residual into slot [rank] of every rank's phase-2 area.
 void DdpEngine::issue_shard_reduce(int b, int worker) {
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
-  const int parity = int(epoch_ & 1u);
+  const int parity = epoch_dev_ ? 0 : int(epoch_ & 1u);
   const int me = cfg_.rank;
   const int64_t n_me = shard_len(b, me);
   const int64_t off = B.offset + int64_t(me) * L.shard_elems;
@@ -371,13 +423,17 @@ void DdpEngine::issue_shard_reduce(int b, int worker) {
   check(cudaStreamWaitEvent(w.recv, w.pushed, 0), "wait pushed");
   // every rank's payload of my shard has arrived
   check(cuda::wait_flags(reinterpret_cast<const uint32_t*>(mine + L.flags), cfg_.world, epoch_,
-                         cfg_.flag_timeout_ns, status_, w.recv),
+                         cfg_.flag_timeout_ns, status_, w.recv, epoch_dev_, wait_ns_),
         "wait_flags");
   launched += 1;
+  stamp(b, kStampArrived, w.recv);
   // where the averaged, re-compressed shard goes: slot [me] of every rank's phase-2 area
   cuda::PushTargets dst;
   dst.world = cfg_.world;
   dst.epoch = epoch_;
+  dst.epoch_dev = epoch_dev_;
+  dst.parity_stride = L.slots2[1] - L.slots2[0];
+  dst.guard = status_;
   dst.done = w.done + 4;  // its own last-CTA counter: the push stream may be compressing the next bucket
   for (int p = 0; p < cfg_.world; ++p) {
     uint8_t* base = bases_[static_cast<size_t>(p)];
@@ -391,6 +447,9 @@ void DdpEngine::issue_shard_reduce(int b, int worker) {
   }
   cuda::UnpackSources src;
   src.world = cfg_.world;
+  src.epoch_dev = epoch_dev_;
+  src.parity_stride = L.slots[1] - L.slots[0];
+  src.guard = status_;
   for (int r = 0; r < cfg_.world; ++r) {
     src.payload[r] = mine + L.slots[parity] + int64_t(r) * L.slot_bytes + L.shift;
     src.payload_bytes[r] = L.slot_bytes - L.shift;
@@ -398,7 +457,7 @@ void DdpEngine::issue_shard_reduce(int b, int worker) {
   const float post = cfg_.average ? 1.0f / float(cfg_.world) : 1.0f;
   float* g = grad_ + off;
   float* res2 = residual2_ + residual2_off_[static_cast<size_t>(b)];
-  const uint64_t seed = cfg_.seed + uint64_t(epoch_) * cuda::kEpochSeedStride +
+  const uint64_t seed = cfg_.seed + (epoch_dev_ ? 0 : uint64_t(epoch_) * cuda::kEpochSeedStride) +
                         uint64_t(b) * 0x632BE59BD9B4E019ull + 0xA24BAED4963EE407ull;
   if (cfg_.codec == Codec::kTbq) {
     check(cuda::tbq_unpack_accum(src, cfg_.threshold, g, n_me, 0, post, cuda::SgdApply{}, w.recv), "tbq_unpack");
@@ -417,42 +476,62 @@ void DdpEngine::issue_shard_reduce(int b, int worker) {
   launches_ += launched;
 }
 
+// Phase 3: one pass over the whole bucket that decodes every shard from its owner's payload
+// (UnpackSources::shard_elems) and applies the update.
 void DdpEngine::issue_shard_final(int b, int worker) {
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
-  const int parity = int(epoch_ & 1u);
+  const int parity = epoch_dev_ ? 0 : int(epoch_ & 1u);
   uint8_t* mine = bases_[static_cast<size_t>(cfg_.rank)];
   int launched = 0;
   check(cuda::wait_flags(reinterpret_cast<const uint32_t*>(mine + L.flags2), cfg_.world, epoch_,
-                         cfg_.flag_timeout_ns, status_, w.recv),
+                         cfg_.flag_timeout_ns, status_, w.recv, epoch_dev_, wait_ns_),
         "wait_flags");
   launched += 1;
+  cuda::UnpackSources src;
+  src.world = cfg_.world;
+  src.epoch_dev = epoch_dev_;
+  src.parity_stride = L.slots2[1] - L.slots2[0];
+  src.shard_elems = L.shard_elems;
+  src.guard = status_;
   for (int j = 0; j < cfg_.world; ++j) {
-    const int64_t nj = shard_len(b, j);
-    if (nj == 0) continue;
-    const int64_t off = B.offset + int64_t(j) * L.shard_elems;
-    cuda::UnpackSources src;
-    src.world = 1;
-    src.payload[0] = mine + L.slots2[parity] + int64_t(j) * L.slot_bytes + L.shift;
-    src.payload_bytes[0] = L.slot_bytes - L.shift;
-    cuda::SgdApply apply;
-    if (fused_sgd_) {
-      apply.param = param_ + off;
-      apply.momentum = momentum_ + off;
-      apply.lr = lr_;
-      apply.mu = sgd_mu_;
-      apply.weight_decay = wd_;
-      apply.first_step = steps_ == 0 ? 1 : 0;
-      apply.clear_grad = cfg_.clear_grad;
-    }
-    if (cfg_.codec == Codec::kTbq)
-      check(cuda::tbq_unpack_accum(src, cfg_.threshold, grad_ + off, nj, 0, 1.0f, apply, w.recv), "tbq_unpack");
-    else
-      check(cuda::terngrad_unpack_accum(src, grad_ + off, nj, 0, 1.0f, apply, status_, w.recv, cfg_.bitwidth),
+    src.payload[j] = mine + L.slots2[parity] + int64_t(j) * L.slot_bytes + L.shift;
+    src.payload_bytes[j] = L.slot_bytes - L.shift;
+  }
+  const cuda::SgdApply apply = sgd_apply_for(b);
+  if (cfg_.codec == Codec::kTbq) {
+    check(cuda::tbq_unpack_accum(src, cfg_.threshold, grad_ + B.offset, B.numel, 0, 1.0f, apply, w.recv), "tbq_unpack");
+    launched += 1;
+  } else if (cfg_.bitwidth == 2) {
+    check(cuda::terngrad_unpack_accum(src, grad_ + B.offset, B.numel, 0, 1.0f, apply, status_, w.recv, cfg_.bitwidth),
+          "tern_unpack");
+    launched += 1;
+  } else {
+    // the one-pass form over concatenated shards exists for 2-bit payloads: one launch per shard
+    for (int j = 0; j < cfg_.world; ++j) {
+      const int64_t nj = shard_len(b, j);
+      if (nj == 0) continue;
+      const int64_t off = int64_t(j) * L.shard_elems;
+      cuda::UnpackSources one = src;
+      one.world = 1;
+      one.shard_elems = 0;
+      one.payload[0] = src.payload[j];
+      cuda::SgdApply ap = apply;
+      if (ap.param) {
+        ap.param += off;
+        ap.momentum += off;
+      }
+      check(cuda::terngrad_unpack_accum(one, grad_ + B.offset + off, nj, 0, 1.0f, ap, status_, w.recv, cfg_.bitwidth),
             "tern_unpack");
+      launched += 1;
+    }
+  }
+  if (adamw_) {
+    issue_adamw(b, w.recv);
     launched += 1;
   }
+  stamp(b, kStampDone, w.recv);
   check(cudaEventRecord(w.tail, w.recv), "record tail");
   w.used = true;
   launches_ += launched;
@@ -480,6 +559,7 @@ void DdpEngine::issue_push(int b, int worker) {
                         uint64_t(b) * 0x632BE59BD9B4E019ull;
   // ---- push stream: compress and deliver
   check(cudaStreamWaitEvent(w.push, ready_events_[static_cast<size_t>(b)], 0), "wait ready");
+  stamp(b, kStampReady, w.push);
   cuda::PushTargets dst = targets_for(b, w);
   int launched = 0;
   switch (cfg_.codec) {
@@ -537,6 +617,7 @@ void DdpEngine::issue_push(int b, int worker) {
     }
   }
 
+  stamp(b, kStampPushed, w.push);
   check(cudaEventRecord(w.pushed, w.push), "record pushed");
   launches_ += launched;
 }
@@ -548,18 +629,7 @@ void DdpEngine::issue_recv(int b, int worker) {
   const int64_t n = B.numel;
   float* g = grad_ + B.offset;
   const float post = cfg_.average ? 1.0f / float(cfg_.world) : 1.0f;
-  cuda::SgdApply apply;
-  if (fused_sgd_) {
-    apply.param = param_ + B.offset;
-    apply.momentum = momentum_ + B.offset;
-    apply.lr = lr_;
-    apply.mu = sgd_mu_;
-    apply.weight_decay = wd_;
-    // buf = g on the first step equals mu * buf + g with the zero-initialised momentum the
-    // wrappers allocate; a captured step must not bake the first-step flag in
-    apply.first_step = (steps_ == 0 && !epoch_dev_) ? 1 : 0;
-    apply.clear_grad = cfg_.clear_grad;
-  }
+  const cuda::SgdApply apply = sgd_apply_for(b);
   int launched = 0;
   // The receive half starts once this rank's own payload and flag are out: the flag wait below
   // then only ever waits for other GPUs, never for a kernel of this GPU that might not have
@@ -568,8 +638,10 @@ void DdpEngine::issue_recv(int b, int worker) {
   check(cudaStreamWaitEvent(w.recv, w.pushed, 0), "wait pushed");
   // ---- recv stream: wait for all ranks, decode everything in one pass
   const uint32_t* flags = reinterpret_cast<const uint32_t*>(bases_[static_cast<size_t>(cfg_.rank)] + L.flags);
-  check(cuda::wait_flags(flags, cfg_.world, epoch_, cfg_.flag_timeout_ns, status_, w.recv, epoch_dev_), "wait_flags");
+  check(cuda::wait_flags(flags, cfg_.world, epoch_, cfg_.flag_timeout_ns, status_, w.recv, epoch_dev_, wait_ns_),
+        "wait_flags");
   launched += 1;
+  stamp(b, kStampArrived, w.recv);
   cuda::UnpackSources src = sources_for(b);
   bool applied = false;
   switch (cfg_.codec) {
@@ -606,22 +678,10 @@ void DdpEngine::issue_recv(int b, int worker) {
     launched += 1;
   }
   if (adamw_) {
-    if (!param_ || !momentum_ || !second_) throw std::runtime_error("AdamW needs param and both moment buffers");
-    cuda::AdamWApply aw;
-    aw.param = param_ + B.offset;
-    aw.exp_avg = momentum_ + B.offset;
-    aw.exp_avg_sq = second_ + B.offset;
-    aw.lr = lr_;
-    aw.beta1 = beta1_;
-    aw.beta2 = beta2_;
-    aw.eps = eps_;
-    aw.weight_decay = wd_;
-    aw.step = int(steps_) + 1;
-    aw.step_dev = epoch_dev_;   // one epoch per step: the device counter is the 1-based step count
-    aw.clear_grad = cfg_.clear_grad;
-    check(cuda::adamw_apply_dense(g, 1.0f, aw, n, w.recv), "adamw_apply_dense");
+    issue_adamw(b, w.recv);
     launched += 1;
   }
+  stamp(b, kStampDone, w.recv);
   check(cudaEventRecord(w.tail, w.recv), "record tail");
   w.used = true;
   launches_ += launched;
@@ -655,7 +715,49 @@ void DdpEngine::finish_step(cudaStream_t consumer) {
   }
   for (auto& w : workers_)
     if (w.used) check(cudaStreamWaitEvent(consumer, w.tail, 0), "wait tail");
+  if (stamps_) {
+    check(cuda::stamp_time(stamps_ + buckets_.size() * kStampCount + 1, consumer), "stamp");
+    launches_ += 1;
+  }
   ++steps_;
+}
+
+void DdpEngine::stamp(int b, int which, cudaStream_t stream) {
+  if (!stamps_) return;
+  check(cuda::stamp_time(stamps_ + size_t(b) * kStampCount + which, stream), "stamp");
+  launches_ += 1;
+}
+
+void DdpEngine::set_progress(int64_t steps, uint32_t epoch) {
+  steps_ = steps;
+  epoch_ = epoch;
+  if (epoch_dev_) {
+    check(cudaDeviceSynchronize(), "sync");
+    check(cudaMemcpy(epoch_dev_, &epoch, sizeof(epoch), cudaMemcpyHostToDevice), "restore epoch");
+  }
+}
+
+std::vector<unsigned long long> DdpEngine::wait_stats() {
+  std::vector<unsigned long long> host(3, 0ull);
+  check(cudaDeviceSynchronize(), "sync");
+  check(cudaMemcpy(host.data(), wait_ns_, 3 * sizeof(unsigned long long), cudaMemcpyDeviceToHost), "read wait stats");
+  check(cudaMemset(wait_ns_, 0, 64), "reset wait stats");
+  return host;
+}
+
+std::vector<int64_t> DdpEngine::stage_times() {
+  std::vector<int64_t> out;
+  if (!stamps_) return out;
+  const size_t count = buckets_.size() * kStampCount + 2;
+  std::vector<unsigned long long> host(count, 0ull);
+  check(cudaDeviceSynchronize(), "sync");
+  check(cudaMemcpy(host.data(), stamps_, count * sizeof(unsigned long long), cudaMemcpyDeviceToHost), "read stamps");
+  const unsigned long long t0 = host[buckets_.size() * kStampCount];
+  for (size_t i = 0; i < count; ++i) {
+    if (i == buckets_.size() * kStampCount) continue;  // the begin stamp itself
+    out.push_back(host[i] == 0 ? 0 : int64_t(host[i]) - int64_t(t0));
+  }
+  return out;
 }
 
 int DdpEngine::check_status() {

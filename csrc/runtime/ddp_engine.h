@@ -79,6 +79,12 @@ struct EngineConfig {
   // (the reference's root does the same: decompress-accumulate, then re-compress,
   // ref hp_cuda.cpp:241-271).
   int sharded = 0;
+  // Per-stage device timing: one-thread kernels write the device wall clock into a small table
+  // at the stage boundaries of every bucket (gradients ready, payload pushed, peers' payloads
+  // arrived, update applied) and at the beginning and end of the step; stage_times() reads the
+  // last step's table.  Adds four tiny launches per bucket, so it is off unless asked for.  (The
+  // time spent inside flag waits is counted always: wait_stats().)
+  int trace = 0;
 };
 
 struct BucketDesc {
@@ -147,6 +153,20 @@ class DdpEngine {
 
   // Synchronises and returns the device status word (cuda::Status); resets it.
   int check_status();
+  // Continue from a checkpoint: `steps` optimizer steps have been taken and the exchange is at
+  // `epoch` (flag value, slot parity, rounding seed and AdamW's bias-correction step all derive
+  // from these).  Every rank must restore the same values before its next step.
+  void set_progress(int64_t steps, uint32_t epoch);
+  // Residual of the owner's re-compression in the sharded exchange (device pointer, elements).
+  float* residual2() const { return residual2_; }
+  int64_t residual2_elems() const { return residual2_elems_; }
+  // {total ns inside flag waits, longest single wait in ns, number of waits} since the last
+  // call (synchronises the device; the counters are reset).
+  std::vector<unsigned long long> wait_stats();
+  // With EngineConfig::trace: device wall-clock stamps (ns) of the last step, relative to the
+  // step's begin: per bucket {ready, pushed, arrived, done}, then {step end}.  Zero where a stage
+  // did not run.  Synchronises the device.
+  std::vector<int64_t> stage_times();
   uint32_t epoch() const { return epoch_; }
   int64_t steps() const { return steps_; }
   // kernels launched by the engine since construction
@@ -165,6 +185,10 @@ class DdpEngine {
     cudaEvent_t pushed = nullptr;  // this rank's payload and flag of the latest bucket are out
     bool used = false;
   };
+  enum Stamp : int { kStampReady = 0, kStampPushed = 1, kStampArrived = 2, kStampDone = 3, kStampCount = 4 };
+  void stamp(int b, int which, cudaStream_t stream);
+  cuda::SgdApply sgd_apply_for(int b) const;
+  void issue_adamw(int b, cudaStream_t stream);
   void issue_bucket(int b, int worker);
   void issue_push(int b, int worker);
   void issue_recv(int b, int worker);
@@ -195,6 +219,9 @@ class DdpEngine {
   int64_t steps_ = 0;
   uint32_t* epoch_dev_ = nullptr;   // device copy of epoch_ (device_epoch mode)
   float* residual2_ = nullptr;      // sharded: residual of the owner's re-compression, per bucket shard
+  int64_t residual2_elems_ = 0;
+  unsigned long long* wait_ns_ = nullptr;  // device: {total, max, count} of the flag waits
+  unsigned long long* stamps_ = nullptr;   // device: [buckets][kStampCount] + {begin, end}; trace only
   std::vector<int64_t> residual2_off_;
   int64_t launches_at_begin_ = 0;
   std::vector<std::atomic<int>> pending_params_;

@@ -266,9 +266,10 @@ void TaskRuntime::run_decompress(Task& t) {
 
 void TaskRuntime::run_root(Task& t) {
   // C holds `size` payload slices of equal length, slice r from rank r.  All
-  // slices but this rank's own are decoded into the dense tensor in ascending
-  // rank order in one pass, then the dense tensor is compressed into B and
-  // copied to C[0:len]  (ref hp_cuda.cpp:241-271, 421-449, 571-601).
+  // slices but this rank's own are decoded into the dense tensor one after
+  // another in ascending rank order -- the reference's order of accumulation,
+  // own tensor first -- then the dense tensor is compressed into B and copied
+  // to C[0:len]  (ref hp_cuda.cpp:241-271, 421-449, 571-601).
   const auto& a = alg_;
   const int64_t len = (a.name == "terngrad") ? t.B.numel() : staged_bytes(*this, t);
   TORCH_CHECK(t.C.numel() >= len * size_, "gathered buffer C holds fewer than size x payload bytes");
@@ -288,10 +289,12 @@ void TaskRuntime::run_root(Task& t) {
     if (r != rank_) peers.push_back(gathered.slice(0, int64_t(r) * len, int64_t(r + 1) * len));
   auto out = t.tensor.view(-1);
   const bool add = t.is_root != 0;
-  if (!peers.empty()) {
-    if (a.name == "terngrad") ops::terngrad_decompress(peers, out, add, 1.0, alg_.bitwidth);
-    else if (a.name == "tbq") ops::tbq_decompress(peers, out, a.threshold, add, 1.0);
-    else if (a.name == "graddrop") ops::sparse_decompress(peers, out, add, 1.0);
+  for (size_t i = 0; i < peers.size(); ++i) {
+    // the first peer overwrites unless the task accumulates; every later one adds
+    const bool add_to = add || i > 0;
+    if (a.name == "terngrad") ops::terngrad_decompress({peers[i]}, out, add_to, 1.0, alg_.bitwidth);
+    else if (a.name == "tbq") ops::tbq_decompress({peers[i]}, out, a.threshold, add_to, 1.0);
+    else if (a.name == "graddrop") ops::sparse_decompress({peers[i]}, out, add_to, 1.0);
     else TORCH_CHECK(false, "task 30 is not valid for algorithm ", a.name);
   }
   run_compress(t);

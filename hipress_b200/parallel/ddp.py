@@ -64,6 +64,8 @@ class CompressionConfig:
     momentum_correction: bool = False
     dgc_momentum: float = 0.9
     clip_norm: float = 0.0
+    # per-stage device timing (metrics()["stages"]): four one-thread launches per bucket
+    trace: bool = False
 
     def engine_dict(self, rank: int, world: int, device: int) -> Dict:
         return dict(rank=rank, world=world, device=device, codec=self.algorithm, bitwidth=self.bitwidth,
@@ -73,7 +75,8 @@ class CompressionConfig:
                     seed=int(self.seed), average=int(self.average), flag_timeout_s=float(self.flag_timeout_s),
                     num_workers=int(self.num_workers), momentum_correction=int(self.momentum_correction),
                     dgc_momentum=float(self.dgc_momentum),
-                    dgc_clip=float(self.clip_norm) / max(1.0, float(world)) ** 0.5)
+                    dgc_clip=float(self.clip_norm) / max(1.0, float(world)) ** 0.5,
+                    trace=int(self.trace))
 
     @property
     def needs_residual(self) -> bool:
@@ -190,8 +193,8 @@ class CompressedDataParallel(nn.Module):
         cfg_dict["sharded"] = 1 if self.config.sharded else 0
         self.graph_capturable = bool(self.config.graph_capturable)
         if self.graph_capturable:
-            if self.config.algorithm not in ("tbq", "terngrad", "graddrop", "dgc") or not fused:
-                raise ValueError("graph_capturable needs tbq, terngrad, graddrop or dgc with a fused optimizer")
+            if self.config.algorithm not in ("tbq", "terngrad", "graddrop", "dgc", "ecq") or not fused:
+                raise ValueError("graph_capturable needs tbq, terngrad, graddrop, dgc or ecq with a fused optimizer")
             cfg_dict["device_epoch"] = 1
             cfg_dict["num_workers"] = 0
         elif self.config.num_workers < 0:
@@ -281,8 +284,12 @@ class CompressedDataParallel(nn.Module):
 
     # ------------------------------------------------------------------ state
     def compression_state(self) -> Dict[str, torch.Tensor]:
-        """Residual / momentum state of the synchroniser, for checkpoints."""
-        out = {"steps": torch.tensor(self.engine.steps)}
+        """Everything the synchroniser and its fused optimizer carry from step to step, for
+        checkpoints: residual / momentum / moment / velocity buffers, the sharded exchange's
+        owner-side residual, and the step and epoch counters from which the rounding seeds,
+        the slot parity, DGC's position in its warm-up and AdamW's bias correction derive."""
+        torch.cuda.synchronize(self.device)
+        out = {"steps": torch.tensor(self.engine.steps), "epoch": torch.tensor(self.engine.epoch)}
         if self.flat_residual is not None:
             out["residual"] = self.flat_residual.clone()
         if self.flat_momentum is not None:
@@ -291,22 +298,69 @@ class CompressedDataParallel(nn.Module):
             out["second_moment"] = self.flat_second.clone()
         if self.flat_velocity is not None:
             out["velocity"] = self.flat_velocity.clone()
+        res2 = self.engine.residual2(self._dev_index)
+        if res2 is not None:
+            out["residual2"] = res2.clone()
         return out
 
     def load_compression_state(self, state: Dict[str, torch.Tensor]) -> None:
-        if "residual" in state and self.flat_residual is not None:
-            self.flat_residual.copy_(state["residual"])
-        if "momentum" in state and self.flat_momentum is not None:
-            self.flat_momentum.copy_(state["momentum"])
-        if "second_moment" in state and self.flat_second is not None:
-            self.flat_second.copy_(state["second_moment"])
-        if "velocity" in state and self.flat_velocity is not None:
-            self.flat_velocity.copy_(state["velocity"])
+        """Continue from ``compression_state()``: call it on every rank, with the model's
+        parameters restored, before the next step."""
+        if self._in_step:
+            raise RuntimeError("load_compression_state() in the middle of a step")
+        torch.cuda.synchronize(self.device)
+        for key, buf in (("residual", self.flat_residual), ("momentum", self.flat_momentum),
+                         ("second_moment", self.flat_second), ("velocity", self.flat_velocity),
+                         ("residual2", self.engine.residual2(self._dev_index))):
+            if key in state and buf is not None:
+                buf.copy_(state[key])
+        if "steps" in state:
+            steps = int(state["steps"])
+            self.engine.set_progress(steps, int(state.get("epoch", steps)))
+        torch.cuda.synchronize(self.device)
+
+    def close(self) -> None:
+        """Release the engine and the symmetric memory once no peer can still be reading it.
+
+        Peers read this rank's memory (the dense codec pulls every rank's slot) and write into
+        it; freeing it while a slower rank still runs its last step is undefined behaviour with
+        CUDA IPC mappings.  ``close`` synchronises this device, waits for every rank at a
+        barrier and only then drops the native objects.  Call it on every rank."""
+        if getattr(self, "engine", None) is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1 and dist.is_available() and dist.is_initialized():
+            dist.barrier(group=self.group)
+        for h in self._hooks:
+            h.remove()
+        self._hooks = []
+        self.engine = None
+        self.symmetric = None
 
     def metrics(self) -> Dict[str, float]:
+        """Counters of the synchroniser.  ``wait_*`` is the time this rank's flag waits spent
+        waiting for peers since the previous call (device-timed; it is what rank skew and the
+        transfer itself cost, as opposed to this rank's own kernels).  With
+        ``CompressionConfig(trace=True)``, ``stages`` holds, for the last step, the device time in
+        microseconds from the step's begin to each bucket's {gradients ready, payload pushed, all
+        payloads arrived, update applied}, ``step_us`` the step's length and ``exposed_tail_us``
+        the time between the last bucket's gradients being ready (the end of backward) and the
+        last update being applied.  Synchronises the device."""
         dense = self.engine.dense_bytes_per_step
         wire = self.engine.wire_bytes_per_step
-        return {"buckets": len(self.plan.buckets), "dense_bytes_per_step": dense,
-                "wire_bytes_per_step": wire,
-                "compression_ratio": dense * max(1, self.world - 1) / wire if wire else float("inf"),
-                "kernel_launches": self.engine.launches, "steps": self.engine.steps}
+        total_ns, max_ns, waits = self.engine.wait_stats()
+        out = {"buckets": len(self.plan.buckets), "dense_bytes_per_step": dense,
+               "wire_bytes_per_step": wire,
+               "compression_ratio": dense * max(1, self.world - 1) / wire if wire else float("inf"),
+               "kernel_launches": self.engine.launches, "steps": self.engine.steps,
+               "wait_us_total": total_ns / 1e3, "wait_us_max": max_ns / 1e3, "waits": waits}
+        times = self.engine.stage_times()
+        if times:
+            nb = len(self.plan.buckets)
+            names = ("ready", "pushed", "arrived", "done")
+            stages = [{k: times[4 * b + i] / 1e3 for i, k in enumerate(names)} for b in range(nb)]
+            out["stages"] = stages
+            out["step_us"] = times[4 * nb] / 1e3
+            last_ready = max(s["ready"] for s in stages)
+            out["exposed_tail_us"] = max(s["done"] for s in stages) - last_ready
+        return out

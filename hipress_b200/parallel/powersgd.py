@@ -225,14 +225,44 @@ class PowerSGDDataParallel(nn.Module):
             raise RuntimeError(f"hipress PowerSGD: device status {status}")
 
     def compression_state(self) -> Dict[str, torch.Tensor]:
-        return {"residual": self.flat_M.clone(), "momentum": self.flat_momentum.clone(),
-                "Q": [q.clone() for q in self.Q], "steps": torch.tensor(self.steps)}
+        """Error-feedback memory, warm-start factors, momentum and the step / epoch counters (flag
+        values and accumulator parity derive from the epoch), for checkpoints."""
+        torch.cuda.synchronize(self.device)
+        out = {"residual": self.flat_M.clone(), "momentum": self.flat_momentum.clone(),
+               "Q": [q.clone() for q in self.Q], "steps": torch.tensor(self.steps),
+               "epoch": torch.tensor(self.epoch)}
+        if self.vecs:
+            out["vec_momentum"] = self.vec_momentum.clone()
+        return out
 
     def load_compression_state(self, state: Dict) -> None:
+        """Continue from ``compression_state()``; call it on every rank, parameters restored,
+        before the next step."""
+        torch.cuda.synchronize(self.device)
         self.flat_M.copy_(state["residual"])
         self.flat_momentum.copy_(state["momentum"])
         for q, s in zip(self.Q, state["Q"]):
             q.copy_(s)
+        self.steps = int(state.get("steps", 0))
+        self.epoch = int(state.get("epoch", self.steps))
+        if self.vecs:
+            if "vec_momentum" in state:
+                self.vec_momentum.copy_(state["vec_momentum"])
+            self.vec_engine.set_progress(self.steps, self.epoch)
+        torch.cuda.synchronize(self.device)
+
+    def close(self) -> None:
+        """Synchronise, wait for every rank, then release the engines and the symmetric memory
+        (peers read this rank's accumulators; see ``CompressedDataParallel.close``)."""
+        if getattr(self, "engine", None) is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1 and dist.is_initialized() and not self.emulated:
+            dist.barrier(group=self.group)
+        self.engine = None
+        self.vec_engine = None
+        self.symmetric = None
+        self.vec_symmetric = None
 
     def metrics(self) -> Dict[str, float]:
         dense = sum(n * m for n, m in self.shapes) * 4

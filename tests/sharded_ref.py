@@ -18,7 +18,7 @@ def _signed(seed: int) -> int:
 
 def shard_elems(n: int, world: int) -> int:
     per = (n + world - 1) // world
-    return (per + 63) // 64 * 64
+    return (per + 4095) // 4096 * 4096
 
 
 def expected(codec, kw, base_seed, epoch, grads, resid, resid2, world):

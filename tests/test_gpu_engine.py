@@ -39,11 +39,15 @@ def make_engines(codec, world, n, **kw):
     ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05, device_epoch=1, num_workers=0)),
     ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05)),
     ("ecq", dict(bitwidth=4, alpha=1.0, beta=0.9)),
+    ("ecq", dict(bitwidth=2, alpha=1.0, beta=0.9, device_epoch=1, num_workers=0)),
     ("dense", dict()),
 ])
-@pytest.mark.parametrize("world", [1, 2, 4])
-def test_engine_matches_cpu_codec(codec, kw, world):
-    n = 100000 + 3 * 4
+@pytest.mark.parametrize("world,n", [(1, 100000 + 12), (2, 100000 + 12), (4, 100000 + 12), (3, 4099), (8, 50000 + 7),
+                                     # large enough for the chunked compress path (16-byte peer stores)
+                                     (2, 700000 + 12), (8, 620000 + 5)])
+def test_engine_matches_cpu_codec(codec, kw, world, n):
+    if n > 200000 and codec not in ("terngrad", "tbq"):
+        pytest.skip("the chunked path exists for tbq and terngrad")
     engines, mems = make_engines(codec, world, n, **kw)
     grads = [gauss(n, seed=10 + r).cuda() for r in range(world)]
     resid = [torch.zeros(n, device="cuda") for _ in range(world)]
@@ -108,21 +112,38 @@ def test_engine_matches_cpu_codec(codec, kw, world):
             cpu_grads[r] = fresh.clone()
 
 
-def test_flag_wait_times_out_with_status():
-    """A flag that nobody publishes: the bounded wait gives up, records it, the context lives on."""
-    n = 4096
-    cfg = dict(rank=0, world=2, device=0, codec="tbq", threshold=0.01, flag_timeout_s=0.2)
+@pytest.mark.parametrize("codec,kw,opt", [
+    ("tbq", dict(threshold=0.01), "sgd"),
+    ("terngrad", dict(bitwidth=2), "sgd"),
+    ("terngrad", dict(bitwidth=2, sharded=1, num_workers=0), "sgd"),
+    ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05), "adamw"),
+    ("ecq", dict(bitwidth=4), "sgd"),
+])
+def test_flag_wait_times_out_with_status(codec, kw, opt):
+    """A flag that nobody publishes: the bounded wait gives up and records it, the kernels queued
+    behind it leave parameters and optimizer state untouched, and the context lives on."""
+    n = 8192 + 4
+    cfg = dict(rank=0, world=2, device=0, codec=codec, flag_timeout_s=0.2, **kw)
     e = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
     mems = SymmetricMemory.emulate(e.symmetric_bytes, 2)
     g, r = gauss(n).cuda(), torch.zeros(n, device="cuda")
-    e.set_buffers(g, r, None, None)
+    param, mom, second = gauss(n, 1.0, seed=5).cuda(), gauss(n, 1.0, seed=6).cuda(), gauss(n, 1.0, seed=7).cuda().abs()
+    e.set_buffers(g, r, param, mom, None, second)
     e.set_symmetric(mems[0].buf)
-    e.set_sgd(0.0, 0.0, 0.0, False)
+    if opt == "adamw":
+        e.set_adamw(0.1, 0.9, 0.999, 1e-8, 0.01)
+    else:
+        e.set_sgd(0.1, 0.9, 0.0, True)
+    before = [t.clone() for t in (param, mom, second)]
     e.begin_step()
     e.bucket_ready(0, 0)   # rank 1 never pushes
     e.finish_step(0)
     assert e.check_status() == 1
+    for t, b in zip((param, mom, second), before):
+        assert torch.equal(t, b)
     assert e.check_status() == 0
+    total_ns, max_ns, waits = e.wait_stats()
+    assert waits >= 1 and max_ns >= 0.15e9
     # the device is still usable
     assert torch.equal(torch.ones(4, device="cuda") * 2, torch.full((4,), 2.0, device="cuda"))
 
@@ -188,12 +209,14 @@ def test_ddp_dense_world1_equals_torch_sgd():
     ("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)),
     ("terngrad", dict(bitwidth=4, enable_random=0, error_feedback=0)),
 ])
-@pytest.mark.parametrize("world,n", [(1, 100000 + 12), (2, 100000 + 12), (4, 100000 + 12), (4, 100), (8, 70001)])
-def test_sharded_exchange_matches_cpu_restatement(codec, kw, world, n):
+@pytest.mark.parametrize("device_epoch", [0, 1])
+@pytest.mark.parametrize("world,n", [(1, 100000 + 12), (2, 100000 + 12), (4, 100000 + 12), (4, 100), (8, 70001),
+                                     (3, 5 * 4096), (8, 300000 + 3)])
+def test_sharded_exchange_matches_cpu_restatement(codec, kw, world, n, device_epoch):
     """Compressed reduce-scatter + compressed all-gather, ranks emulated on one device phase by
     phase (a device synchronise between phases, so no wait ever spins on an unlaunched kernel)."""
     from sharded_ref import expected, shard_elems
-    engines, mems = make_engines(codec, world, n, sharded=1, num_workers=0, **kw)
+    engines, mems = make_engines(codec, world, n, sharded=1, num_workers=0, device_epoch=device_epoch, **kw)
     grads = [gauss(n, seed=10 + r).cuda() for r in range(world)]
     resid = [torch.zeros(n, device="cuda") for _ in range(world)]
     for e, m, g, r in zip(engines, mems, grads, resid):

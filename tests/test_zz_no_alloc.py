@@ -49,6 +49,39 @@ def test_noalloc_terngrad_matches_regular_entry_point_twice():
         assert torch.equal(r_new, r_ref), f"residual differs on call {call}"
 
 
+def test_noalloc_without_residual_and_with_4_byte_aligned_buffers():
+    """No residual, and gradient / residual that are 4-byte but not 16-byte aligned (a view one
+    element into a tensor): the scalar-load forms of the kernels, through the same entry."""
+    from hipress_b200 import ops
+    lib, fn = _lib()
+    stream = torch.cuda.current_stream().cuda_stream
+    n, bw, seed = 300_001, 2, 21
+    base = (torch.randn(n + 1, generator=torch.Generator().manual_seed(5)) * 0.01).cuda()
+    rbase = (torch.randn(n + 1, generator=torch.Generator().manual_seed(6)) * 0.002).cuda()
+    for g, r0 in ((base[:n], None), (base[1:], None), (base[1:], rbase[1:])):
+        r_ref = None if r0 is None else r0.clone()
+        ref = ops.terngrad_compress(g.clone(), bw, True, seed, residual=r_ref)
+        # a clone is freshly aligned: rebuild the one-element offset for the new entry point
+        holder = torch.empty(n + 1, device="cuda")
+        off = 1 if g.data_ptr() % 16 else 0
+        g_new = holder[off:off + n]
+        g_new.copy_(g)
+        assert g_new.data_ptr() % 16 == g.data_ptr() % 16
+        r_new = None
+        if r0 is not None:
+            rholder = torch.empty(n + 1, device="cuda")
+            r_new = rholder[1:1 + n]
+            r_new.copy_(r0)
+        out = torch.empty(ops.terngrad_payload_bytes(n, bw), dtype=torch.uint8, device="cuda")
+        rc = fn(g_new.data_ptr(), None if r_new is None else r_new.data_ptr(), n, bw, 1, seed, out.data_ptr(),
+                out.numel(), stream)
+        assert rc == 0, lib.hipress_noalloc_last_error()
+        torch.cuda.synchronize()
+        assert torch.equal(out, ref)
+        if r0 is not None:
+            assert torch.equal(r_new, r_ref)
+
+
 def test_noalloc_rejects_bad_sizes():
     lib, fn = _lib()
     g = torch.zeros(16, device="cuda")
