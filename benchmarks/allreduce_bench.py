@@ -13,6 +13,8 @@ rank are synchronised (sum / W on every rank) by
 * ``dgc``       top-k 0.1 % with 1 % sample threshold estimation,
 * ``tbq_sharded`` / ``terngrad_sharded``  the same codecs as a compressed reduce-scatter to shard
   owners followed by a compressed all-gather of the re-quantised averages (``--codecs ... tbq_sharded``),
+* ``tbq_auto`` / ``terngrad_auto``  whichever of the two forms the library's size rule picks
+  (``hipress_b200.parallel.prefer_sharded``),
 
 each as ONE fused pipeline per step: compress kernels that store the packed payload straight
 into every peer's receive slot over NVLink, a bounded flag wait, and a one-pass unpack +
@@ -21,6 +23,12 @@ iteration, L2 flushed before each, ranks aligned by a barrier) and reported as t
 ranks of the median.  Effective GB/s = dense bytes (4 N) / time.  The roofline is the slower
 of the kernels' HBM traffic at the measured copy bandwidth and the bytes a rank must send
 over NVLink at 770 GB/s.
+
+``--graph 1`` replays every arm from a CUDA graph (NCCL's all-reduce included; this framework's
+engine then keeps the step's epoch on the device, as a captured training step does), which takes
+the host's launch calls out of the measurement: small buffers are otherwise bound by them.
+The reference extension's composition (its compress task, NCCL all-gather, its decompress tasks)
+is measured by ``benchmarks/reference_codec_bench.py`` under the same launcher.
 """
 from __future__ import annotations
 
@@ -37,7 +45,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
 import hipress_b200 as hp  # noqa: E402
-from hipress_b200.parallel import SymmetricMemory  # noqa: E402
+from hipress_b200.parallel import SymmetricMemory, prefer_sharded  # noqa: E402
 from hipress_b200.utils.timing import flush_l2, max_over_ranks  # noqa: E402
 
 NVLINK_GBS = 770.0
@@ -78,6 +86,22 @@ def wire_bytes(codec: str, n: int, world: int) -> float:
     return per * (world - 1)
 
 
+def maybe_graphed(step, graph: int):
+    """(callable, keep-alive): `step` itself, or a replay of `step` captured in a CUDA graph."""
+    if not graph:
+        return step, None
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()                                   # NCCL sets its communicator up on first use
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    return g.replay, g
+
+
 def time_iters(fn, iters: int, warmup: int):
     times = []
     for i in range(warmup + iters):
@@ -101,6 +125,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--codecs", nargs="+", default=["nccl", "dense", "tbq", "terngrad", "dgc"])
+    ap.add_argument("--graph", type=int, default=0, help="1 = replay each arm from a CUDA graph")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -122,40 +147,63 @@ def main():
                 if world == 1:
                     continue
 
-                def fn():
+                def step():
                     dist.all_reduce(grad)
                     grad.mul_(1.0 / world)
+                fn, keep = maybe_graphed(step, args.graph)
                 ms = time_iters(fn, args.iters, args.warmup)
                 nccl_ms = ms
                 launches = None
             else:
-                sharded = codec.endswith("_sharded")
-                cfg = dict(rank=rank, world=world, device=local, codec=codec[:-8] if sharded else codec,
+                base = codec.rsplit("_", 1)[0] if codec.endswith(("_sharded", "_auto")) else codec
+                sharded = codec.endswith("_sharded") or (codec.endswith("_auto") and prefer_sharded(n * 4, world))
+                graphable = bool(args.graph) and base != "dense"
+                cfg = dict(rank=rank, world=world, device=local, codec=base,
                            threshold=2e-3, bitwidth=2, enable_random=1, error_feedback=1, keep_fraction=0.001,
-                           sample_rate=0.01, seed=1, sharded=1 if sharded else 0)
+                           sample_rate=0.01, seed=1, sharded=1 if sharded else 0,
+                           device_epoch=1 if graphable else 0, num_workers=0 if (graphable or sharded) else 1)
                 eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
                 sym = SymmetricMemory(eng.symmetric_bytes, dev)
                 resid = torch.zeros(n, device=dev)
                 eng.set_buffers(grad, resid, None, None)
                 eng.set_symmetric(sym.buf)
                 eng.set_sgd(0.0, 0.0, 0.0, False)
-                l0 = eng.launches
 
-                def fn():
-                    eng.begin_step()
+                def step():
+                    eng.begin_step(local)
                     eng.bucket_ready(0, local)
                     eng.finish_step(local)
+                if graphable:
+                    step()                       # first-use set-up outside the capture
+                    torch.cuda.synchronize()
+                    if dist.is_initialized():
+                        dist.barrier()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        step()
+                    per_step = eng.end_capture()
+
+                    def fn():
+                        g.replay()
+                        eng.note_replay(1, per_step)
+                else:
+                    fn = step
+                l0 = eng.launches
                 ms = time_iters(fn, args.iters, args.warmup)
                 status = eng.check_status()
                 assert status == 0, f"engine status {status}"
                 launches = (eng.launches - l0) // (args.iters + args.warmup)
+                if dist.is_initialized():
+                    dist.barrier()           # nobody frees its buffer while a peer may still read it
                 del eng, sym
             dense_bytes = 4.0 * n
-            row = {"codec": codec, "world": world, "buffer_mb": mb, "n": n, "ms": round(ms, 4),
+            row = {"codec": codec, "world": world, "buffer_mb": mb, "n": n, "graph": int(args.graph), "ms": round(ms, 4),
                    "effective_gbs": round(dense_bytes / (ms * 1e-3) / 1e9, 2), "launches_per_step": launches}
             if codec != "nccl":
-                t_hbm = hbm_bytes_per_elem(codec, world) * n / (hbm * 1e9)
-                t_link = wire_bytes(codec, n, world) / (NVLINK_GBS * 1e9)
+                model = (base + "_sharded") if sharded else base
+                row["form"] = "sharded" if sharded else "all-gather"
+                t_hbm = hbm_bytes_per_elem(model, world) * n / (hbm * 1e9)
+                t_link = wire_bytes(model, n, world) / (NVLINK_GBS * 1e9)
                 roof = max(t_hbm, t_link)
                 row.update({"roofline_ms": round(roof * 1e3, 4), "roofline_bound": "hbm" if t_hbm >= t_link else "nvlink",
                             "fraction_of_roofline": round(roof * 1e3 / ms, 3),

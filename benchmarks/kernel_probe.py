@@ -71,7 +71,14 @@ def main():
         fn = lambda: ops.terngrad_compress(g, 2, True, 1, residual=r, out=out)
         traffic = n * (8 + 8 + 4 + 0.25)
     elif k == "terngrad_unpack":
-        pl = [ops.terngrad_compress(torch.randn(n, device=dev) * 1e-3, 2, True, s) for s in range(args.world)]
+        # payloads sit 6 bytes into their buffers, as in the engine's receive slots: the packed
+        # data behind the 10-byte header is then 16-byte aligned and is read with 32-bit loads
+        nbytes = ops.terngrad_payload_bytes(n, 2)
+        pl = []
+        for s in range(args.world):
+            buf = torch.empty(nbytes + 16, dtype=torch.uint8, device=dev)[6:6 + nbytes]
+            ops.terngrad_compress(torch.randn(n, device=dev) * 1e-3, 2, True, s, out=buf)
+            pl.append(buf)
         fn = lambda: ops.terngrad_decompress(pl, g, post_scale=1.0 / args.world, bitwidth=2)
         traffic = n * (0.25 * args.world + 4)
     elif k == "tbq":

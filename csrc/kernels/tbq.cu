@@ -151,7 +151,7 @@ tbq_compress_kernel(const float* __restrict__ grad, float* __restrict__ residual
 // (aligned dense arrays), kConcat = concatenated shards, kGeneric = nibble table.
 enum UnpackMode : int { kGeneric = 0, kPair = 1, kConcat = 2 };
 
-template <bool APPLY, int MODE>
+template <bool APPLY, int MODE, int WORLD>
 __global__ void __launch_bounds__(kUnpackThreads, MODE == kGeneric ? 1 : 3)
 tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
                       float post_scale, SgdApply apply) {
@@ -168,7 +168,7 @@ tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int
     });
     __syncthreads();
     // a rank without a partner pairs with four "zero" fields, which decode to +0.0
-    unpack_pair_body<APPLY, true>(tab, 0x55555555u, first, src, src.parity_off, out, n, add, post_scale, apply);
+    unpack_pair_body<APPLY, true, (WORLD > 0 ? WORLD : 1)>(tab, 0x55555555u, first, src, src.parity_off, out, n, add, post_scale, apply);
   } else {
     if (threadIdx.x < 32) tab[threadIdx.x] = tbq_dequant((uint32_t(threadIdx.x) >> 1 >> (2 * (threadIdx.x & 1))) & 3u, thr);
     __syncthreads();
@@ -228,17 +228,25 @@ cudaError_t tbq_unpack_accum(const UnpackSources& src, float threshold, float* o
   bool aligned = aligned16(out);
   if (apply.param != nullptr) aligned = aligned && aligned16(apply.param) && aligned16(apply.momentum);
   const int mode = src.shard_elems > 0 ? kConcat : (aligned ? kPair : kGeneric);
-#define HP_LAUNCH(AP, MODE) \
-  tbq_unpack_lut_kernel<AP, MODE><<<grid, kUnpackThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply)
-  if (apply.param != nullptr) {
-    if (mode == kConcat) HP_LAUNCH(true, kConcat);
-    else if (mode == kPair) HP_LAUNCH(true, kPair);
-    else HP_LAUNCH(true, kGeneric);
-  } else {
-    if (mode == kConcat) HP_LAUNCH(false, kConcat);
-    else if (mode == kPair) HP_LAUNCH(false, kPair);
-    else HP_LAUNCH(false, kGeneric);
+#define HP_LAUNCH(AP, MODE, W) \
+  tbq_unpack_lut_kernel<AP, MODE, W><<<grid, kUnpackThreads, 0, stream>>>(src, threshold, out, n, add, post_scale, apply)
+#define HP_PAIR(AP)                                                                                     \
+  switch (src.world) {                                                                                  \
+    case 1: HP_LAUNCH(AP, kPair, 1); break;  case 2: HP_LAUNCH(AP, kPair, 2); break;                    \
+    case 3: HP_LAUNCH(AP, kPair, 3); break;  case 4: HP_LAUNCH(AP, kPair, 4); break;                    \
+    case 5: HP_LAUNCH(AP, kPair, 5); break;  case 6: HP_LAUNCH(AP, kPair, 6); break;                    \
+    case 7: HP_LAUNCH(AP, kPair, 7); break;  default: HP_LAUNCH(AP, kPair, 8); break;                   \
   }
+  if (apply.param != nullptr) {
+    if (mode == kConcat) HP_LAUNCH(true, kConcat, 0);
+    else if (mode == kPair) { HP_PAIR(true) }
+    else HP_LAUNCH(true, kGeneric, 0);
+  } else {
+    if (mode == kConcat) HP_LAUNCH(false, kConcat, 0);
+    else if (mode == kPair) { HP_PAIR(false) }
+    else HP_LAUNCH(false, kGeneric, 0);
+  }
+#undef HP_PAIR
 #undef HP_LAUNCH
   return cudaGetLastError();
 }

@@ -352,7 +352,7 @@ __device__ __forceinline__ TernHeader read_header(const uint8_t* p, int64_t cap,
 // aligned), kGeneric = nibble or byte tables.
 enum UnpackMode : int { kGeneric = 0, kPair = 1, kConcat = 2 };
 
-template <int BW, bool APPLY, int MODE>
+template <int BW, bool APPLY, int MODE, int WORLD>
 __global__ void __launch_bounds__(kUnpackThreads, MODE == kGeneric ? 1 : 3)
 tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
                        float post_scale, SgdApply apply, int* status) {
@@ -404,7 +404,7 @@ tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, in
       return tern_dequant((uint32_t(nibble) >> (2 * which)) & 3u, hdr[r].gap, hdr[r].mn);
     });
     __syncthreads();
-    unpack_pair_body<APPLY, false>(tab, 0u, first, src, data_offset, out, n, add, post_scale, apply);
+    unpack_pair_body<APPLY, false, (WORLD > 0 ? WORLD : 1)>(tab, 0u, first, src, data_offset, out, n, add, post_scale, apply);
     return;
   } else if constexpr (BW == 1 || BW == 2 || BW == 4) {
     // nibble tables (see unpack_lut.cuh): entry (rank, nibble, slot)
@@ -451,7 +451,7 @@ cudaError_t launch_tern_unpack(const UnpackSources& src, float* out, int64_t n, 
   const size_t smem = nibble ? 0 : size_t(src.world) * 256 * dpb * sizeof(float);
   if (!nibble) {
     // per device, and cheap: set on every launch rather than remembered per process
-    cudaError_t e = cudaFuncSetAttribute(tern_unpack_lut_kernel<BW, APPLY, kGeneric>,
+    cudaError_t e = cudaFuncSetAttribute(tern_unpack_lut_kernel<BW, APPLY, kGeneric, 0>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 256 * 8 * 4);
     if (e != cudaSuccess) return e;
   }
@@ -462,15 +462,21 @@ cudaError_t launch_tern_unpack(const UnpackSources& src, float* out, int64_t n, 
   if (APPLY) aligned = aligned && aligned16(apply.param) && aligned16(apply.momentum);
   if constexpr (BW == 2) {
     if (src.shard_elems > 0) {
-      tern_unpack_lut_kernel<2, APPLY, kConcat><<<grid, kUnpackThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
+      tern_unpack_lut_kernel<2, APPLY, kConcat, 0><<<grid, kUnpackThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
       return cudaGetLastError();
     }
     if (aligned) {
-      tern_unpack_lut_kernel<2, APPLY, kPair><<<grid, kUnpackThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status);
+#define HP_PAIR(W) \
+  case W: tern_unpack_lut_kernel<2, APPLY, kPair, W><<<grid, kUnpackThreads, 0, stream>>>(src, out, n, add, post_scale, apply, status); break
+      switch (src.world) {
+        HP_PAIR(1); HP_PAIR(2); HP_PAIR(3); HP_PAIR(4); HP_PAIR(5); HP_PAIR(6); HP_PAIR(7); HP_PAIR(8);
+        default: return cudaErrorInvalidValue;
+      }
+#undef HP_PAIR
       return cudaGetLastError();
     }
   }
-  tern_unpack_lut_kernel<BW, APPLY, kGeneric><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status);
+  tern_unpack_lut_kernel<BW, APPLY, kGeneric, 0><<<grid, kUnpackThreads, smem, stream>>>(src, out, n, add, post_scale, apply, status);
   return cudaGetLastError();
 }
 

@@ -74,22 +74,28 @@ __device__ __forceinline__ int64_t shard_count(int64_t n, int64_t S, int j) {
 }
 
 // Finish one group of 4 consecutive elements: accumulate mode, scale, store, fused update.
+// The group lives at o[off .. off+3]; e is its index in the tensor (for the fused update).
 template <bool APPLY>
-__device__ __forceinline__ void unpack_finish4(float (&acc)[4], float* __restrict__ out, int64_t e, int add,
-                                               float post_scale, const SgdApply& apply) {
+__device__ __forceinline__ void unpack_finish4(float (&acc)[4], float* __restrict__ o, int off, int add,
+                                               float post_scale, const SgdApply& apply, int64_t e) {
   if (add) {
-    const float4 o = *reinterpret_cast<const float4*>(out + e);
-    acc[0] = hp_add(acc[0], o.x); acc[1] = hp_add(acc[1], o.y);
-    acc[2] = hp_add(acc[2], o.z); acc[3] = hp_add(acc[3], o.w);
+    const float4 x = *reinterpret_cast<const float4*>(o + off);
+    acc[0] = hp_add(acc[0], x.x); acc[1] = hp_add(acc[1], x.y);
+    acc[2] = hp_add(acc[2], x.z); acc[3] = hp_add(acc[3], x.w);
   }
   if (post_scale != 1.0f) {
 #pragma unroll
     for (int k = 0; k < 4; ++k) acc[k] = hp_mul(acc[k], post_scale);
   }
   const bool clear = APPLY && apply.clear_grad;
-  *reinterpret_cast<float4*>(out + e) =
+  *reinterpret_cast<float4*>(o + off) =
       clear ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(acc[0], acc[1], acc[2], acc[3]);
   if (APPLY) sgd_update4(apply, e, acc);
+}
+template <bool APPLY>
+__device__ __forceinline__ void unpack_finish4(float (&acc)[4], float* __restrict__ out, int64_t e, int add,
+                                               float post_scale, const SgdApply& apply) {
+  unpack_finish4<APPLY>(acc, out + e, 0, add, post_scale, apply, e);
 }
 template <bool APPLY>
 __device__ __forceinline__ void unpack_finish1(float acc, float* __restrict__ out, int64_t e, int add,
@@ -159,7 +165,7 @@ __device__ __forceinline__ void unpack_lut_body(const float* lut, const UnpackSo
         for (int k = 0; k < VW; ++k) acc[k] = tree_sum(v[k], src.world);
         const int64_t e = e0 + b * DPB + q * VW;
         if (VW == 4 && vec) {
-          unpack_finish4<APPLY>(*reinterpret_cast<float(*)[4]>(acc), out, e, add, post_scale, apply);
+          if constexpr (VW == 4) unpack_finish4<APPLY>(acc, out, e, add, post_scale, apply);
         } else {
 #pragma unroll
           for (int k = 0; k < VW; ++k) unpack_finish1<APPLY>(acc[k], out, e + k, add, post_scale, apply);
@@ -327,13 +333,15 @@ __device__ __forceinline__ void build_pair_tables(float* tables, int world, Valu
   }
 }
 
-template <bool APPLY, bool SHARED>
+// WORLD is a template parameter: with the rank count known at compile time the loops below are
+// straight-line code (a first version that tested `r < src.world` everywhere spent 60 % of its
+// instructions on those tests and their branches).
+template <bool APPLY, bool SHARED, int WORLD>
 __device__ __forceinline__ void unpack_pair_body(const float* tables, uint32_t lone_word, uint32_t (&w)[kMaxWorld],
                                                  const UnpackSources& src, int64_t data_offset,
                                                  float* __restrict__ out, int64_t n, int add,
                                                  float post_scale, const SgdApply& apply) {
-  constexpr int kSlots = kMaxWorld / 2;
-  const int slots = (src.world + 1) / 2;
+  constexpr int kSlots = (WORLD + 1) / 2;
   const int64_t full_chunks = n / 512;  // complete 128-byte warp chunks
   const int lane = threadIdx.x & 31;
   const uint32_t sel = 0x4440u | uint32_t(lane & 3);  // byte (lane & 3) of a register, zero-extended
@@ -341,42 +349,40 @@ __device__ __forceinline__ void unpack_pair_body(const float* tables, uint32_t l
   int64_t chunk = int64_t(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   for (; chunk < full_chunks; chunk += warps) {
     const int64_t nxt = (chunk + warps) * 32 + lane;
-    uint32_t wn[kMaxWorld];
+    const bool more = chunk + warps < full_chunks;
+    uint32_t wn[WORLD];
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r)
-      wn[r] = (r < src.world && chunk + warps < full_chunks) ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
+    for (int r = 0; r < WORLD; ++r)
+      wn[r] = more ? load_u32_any(src.payload[r] + data_offset + nxt * 4) : 0u;
     uint32_t lo[kSlots], hi[kSlots];
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
-      if (s < slots) {
-        const uint32_t wa = w[2 * s];
-        const uint32_t wb = (2 * s + 1 < src.world) ? w[2 * s + 1] : lone_word;
-        lo[s] = pair_swizzle((wa & 0x0f0f0f0fu) | ((wb << 4) & 0xf0f0f0f0u));
-        hi[s] = pair_swizzle(((wa >> 4) & 0x0f0f0f0fu) | (wb & 0xf0f0f0f0u));
-      }
+      const uint32_t wa = w[2 * s];
+      const uint32_t wb = (2 * s + 1 < WORLD) ? w[2 * s + 1] : lone_word;
+      lo[s] = pair_swizzle((wa & 0x0f0f0f0fu) | ((wb << 4) & 0xf0f0f0f0u));
+      hi[s] = pair_swizzle(((wa >> 4) & 0x0f0f0f0fu) | (wb & 0xf0f0f0f0u));
     }
+    float* const o = out + chunk * 512 + lane * 4;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int from = j * 8 + (lane >> 2);
       float v[4][kSlots];
 #pragma unroll
       for (int s = 0; s < kSlots; ++s) {
-        if (s < slots) {
-          const uint32_t l = __shfl_sync(0xffffffffu, lo[s], from);
-          const uint32_t h = __shfl_sync(0xffffffffu, hi[s], from);
-          const char* table = reinterpret_cast<const char*>(tables) + (SHARED ? 0 : s * kPairRows * 8);
-          const float2 a = *reinterpret_cast<const float2*>(table + (__byte_perm(l, 0u, sel) << 3));
-          const float2 b = *reinterpret_cast<const float2*>(table + (__byte_perm(h, 0u, sel) << 3));
-          v[0][s] = a.x; v[1][s] = a.y; v[2][s] = b.x; v[3][s] = b.y;
-        }
+        const uint32_t l = __shfl_sync(0xffffffffu, lo[s], from);
+        const uint32_t h = __shfl_sync(0xffffffffu, hi[s], from);
+        const char* table = reinterpret_cast<const char*>(tables) + (SHARED ? 0 : s * kPairRows * 8);
+        const float2 a = *reinterpret_cast<const float2*>(table + (__byte_perm(l, 0u, sel) << 3));
+        const float2 b = *reinterpret_cast<const float2*>(table + (__byte_perm(h, 0u, sel) << 3));
+        v[0][s] = a.x; v[1][s] = a.y; v[2][s] = b.x; v[3][s] = b.y;
       }
       float acc[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) acc[k] = tree_sum(v[k], slots);
-      unpack_finish4<APPLY>(acc, out, chunk * 512 + int64_t(j * 32 + lane) * 4, add, post_scale, apply);
+      for (int k = 0; k < 4; ++k) acc[k] = tree_sum(v[k], kSlots);
+      unpack_finish4<APPLY>(acc, o, j * 128, add, post_scale, apply, chunk * 512 + lane * 4 + j * 128);
     }
 #pragma unroll
-    for (int r = 0; r < kMaxWorld; ++r) w[r] = wn[r];
+    for (int r = 0; r < WORLD; ++r) w[r] = wn[r];
   }
   // elements past the last complete chunk (fewer than 512): block 0, element by element,
   // through the same tables (rank pairs, then the canonical order over the slots)
@@ -386,16 +392,14 @@ __device__ __forceinline__ void unpack_pair_body(const float* tables, uint32_t l
       float v[kSlots];
 #pragma unroll
       for (int s = 0; s < kSlots; ++s) {
-        if (s < slots) {
-          const int sh = 4 * int((e & 3) >> 1);
-          const uint32_t a = (uint32_t(src.payload[2 * s][data_offset + (e >> 2)]) >> sh) & 15u;
-          uint32_t b = lone_nib;
-          if (2 * s + 1 < src.world) b = (uint32_t(src.payload[2 * s + 1][data_offset + (e >> 2)]) >> sh) & 15u;
-          const uint32_t row = (b << 4) | a;
-          v[s] = tables[((SHARED ? 0 : s) * kPairRows + (row ^ ((row >> 4) & 5u))) * 2 + (e & 1)];
-        }
+        const int sh = 4 * int((e & 3) >> 1);
+        const uint32_t a = (uint32_t(src.payload[2 * s][data_offset + (e >> 2)]) >> sh) & 15u;
+        uint32_t b = lone_nib;
+        if (2 * s + 1 < WORLD) b = (uint32_t(src.payload[(2 * s + 1) % kMaxWorld][data_offset + (e >> 2)]) >> sh) & 15u;
+        const uint32_t row = (b << 4) | a;
+        v[s] = tables[((SHARED ? 0 : s) * kPairRows + (row ^ ((row >> 4) & 5u))) * 2 + (e & 1)];
       }
-      unpack_finish1<APPLY>(tree_sum(v, slots), out, e, add, post_scale, apply);
+      unpack_finish1<APPLY>(tree_sum(v, kSlots), out, e, add, post_scale, apply);
     }
   }
 }

@@ -13,17 +13,6 @@
 namespace hipress {
 namespace runtime {
 
-void FinishQueue::push(const std::string& key) {
-  std::lock_guard<std::mutex> lk(mu_);
-  keys_.push_back(key);
-}
-std::vector<std::string> FinishQueue::drain() {
-  std::lock_guard<std::mutex> lk(mu_);
-  std::vector<std::string> out;
-  out.swap(keys_);
-  return out;
-}
-
 TaskRuntime& TaskRuntime::instance() {
   static TaskRuntime* rt = new TaskRuntime();  // leaked: must outlive worker threads at exit
   return *rt;
@@ -64,6 +53,11 @@ bool TaskRuntime::init(const std::string& alg_name, std::unordered_map<std::stri
     errors_.clear();
   }
   pool_ = std::make_unique<WorkerPool>(threads, [](int) {});
+  const double age_limit = params.count("task_age_limit") ? params["task_age_limit"] : 120.0;
+  watchdog_ = std::make_unique<AgeWatchdog>(age_limit, [this](const std::string& label, double age) {
+    std::lock_guard<std::mutex> lk(err_mu_);
+    errors_.push_back(label + ": still running after " + std::to_string(age) + " s (task age limit)");
+  });
   return true;
 }
 
@@ -73,6 +67,7 @@ bool TaskRuntime::end() {
     pool_->shutdown();
     pool_.reset();
   }
+  watchdog_.reset();
   std::lock_guard<std::mutex> lk(map_mu_);
   gathered_.clear();
   return true;
@@ -185,13 +180,19 @@ bool TaskRuntime::submit(Task t) {
     ready = std::make_shared<at::cuda::CUDAEvent>();
     ready->record(at::cuda::getCurrentCUDAStream(t.tensor.get_device()));
   }
-  pool_->submit([this, t, ready](int) mutable {
+  const uint64_t serial = t.serial;
+  watchdog_->track(serial, t.tensor_name + " (task " + std::to_string(t.task_id) + ")");
+  pool_->submit([this, t, ready, serial](int) mutable {
     try {
       if (t.tensor.is_cuda()) {
         c10::cuda::CUDAGuard dev(t.tensor.device());
-        // one high-priority stream per worker thread, taken from torch's pool
-        thread_local c10::cuda::CUDAStream stream =
-            c10::cuda::getStreamFromPool(/*isHighPriority=*/true, t.tensor.get_device());
+        // one high-priority stream per worker thread and device, taken from torch's pool
+        thread_local std::unordered_map<int, c10::cuda::CUDAStream> streams;
+        const int device = t.tensor.get_device();
+        auto it = streams.find(device);
+        if (it == streams.end())
+          it = streams.emplace(device, c10::cuda::getStreamFromPool(/*isHighPriority=*/true, device)).first;
+        c10::cuda::CUDAStream stream = it->second;
         c10::cuda::CUDAStreamGuard sg(stream);
         ready->block(stream);
         run(t);
@@ -204,6 +205,7 @@ bool TaskRuntime::submit(Task t) {
       std::lock_guard<std::mutex> lk(err_mu_);
       errors_.push_back(t.tensor_name + ": " + e.what());
     }
+    watchdog_->done(serial);
   });
   return true;
 }

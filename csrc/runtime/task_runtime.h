@@ -7,7 +7,9 @@
 //   * the submitter's stream is ordered before the worker's stream by an event
 //     (the reference synchronises an unrelated stream and hopes),
 //   * one pass decodes all peers' payloads for a root task,
-//   * a failed task reports through getErrors() and the worker keeps serving,
+//   * a failed task reports through getErrors() and the worker keeps serving; a task still
+//     unfinished after `task_age_limit` seconds (an init parameter, default 120, 0 = off) is
+//     reported there too, so that pollers do not wait for ever,
 //   * end() followed by init() starts a fresh runtime (the reference never
 //     restarts its threads: hp_cuda.cpp:814),
 //   * tensors may live on the CPU, in which case the CPU codec runs (tests).
@@ -20,6 +22,8 @@
 #include <unordered_map>
 #include <vector>
 
+#include "finish_queue.h"
+#include "watchdog.h"
 #include "worker_pool.h"
 
 namespace hipress {
@@ -50,16 +54,6 @@ struct Task {
   int is_root = 0;
   int task_id = 0;
   uint64_t serial = 0;
-};
-
-class FinishQueue {
- public:
-  void push(const std::string& key);
-  std::vector<std::string> drain();
-
- private:
-  std::mutex mu_;
-  std::vector<std::string> keys_;
 };
 
 class TaskRuntime {
@@ -97,6 +91,7 @@ class TaskRuntime {
   CompAlg alg_;
   int device_id_ = 0, rank_ = 0, size_ = 1;
   std::unique_ptr<WorkerPool> pool_;
+  std::unique_ptr<AgeWatchdog> watchdog_;
   FinishQueue comp_, decomp_, root_;
   std::mutex err_mu_;
   std::vector<std::string> errors_;

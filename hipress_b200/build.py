@@ -13,6 +13,9 @@ when a source or any header is newer.  The reference builds one extension with
 ``CUDAExtension(..., nvcc: ['-O3'])`` and no architecture flag
 (ref setup.py:5-18); there is no install step here: the built object is
 imported from the source tree.
+
+``python -m hipress_b200.build --sanitize thread|address`` builds the host runtime's stress
+test under ThreadSanitizer or AddressSanitizer instead (see ``build_sanitized``).
 """
 from __future__ import annotations
 
@@ -166,6 +169,29 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
     return ext
 
 
+SANITIZERS = {"thread": ["-fsanitize=thread"], "address": ["-fsanitize=address,undefined", "-fno-omit-frame-pointer"]}
+
+
+def build_sanitized(kind: str) -> Path:
+    """Build the host runtime's stress test (tests/cpp/runtime_stress.cpp: WorkerPool,
+    FinishQueue, AgeWatchdog -- the plain-C++ parts, which need neither torch nor a GPU) with
+    ThreadSanitizer (``thread``) or AddressSanitizer + UBSan (``address``) and return the
+    executable.  Run it directly; a sanitizer report makes it exit non-zero.  The reference
+    has no such check and carries unsynchronised shared state in exactly these parts
+    (ref hp_cuda.cpp:789, 930)."""
+    if kind not in SANITIZERS:
+        raise ValueError(f"sanitizer must be one of {sorted(SANITIZERS)}")
+    out_dir = ROOT / "build" / "sanitize"
+    out_dir.mkdir(parents=True, exist_ok=True)
+    exe = out_dir / f"runtime_stress_{kind}"
+    src = ROOT / "tests" / "cpp" / "runtime_stress.cpp"
+    newest = max([src.stat().st_mtime] + [p.stat().st_mtime for p in (CSRC / "runtime").glob("*.h")])
+    if not exe.exists() or exe.stat().st_mtime < newest:
+        _run(["g++", "-std=c++17", "-O1", "-g", *SANITIZERS[kind], "-I", str(CSRC), str(src), "-o", str(exe),
+              "-lpthread"])
+    return exe
+
+
 def ptxas_report() -> str:
     """Registers / spills / shared memory per kernel, from the cached nvcc logs."""
     out = []
@@ -176,5 +202,7 @@ def ptxas_report() -> str:
 
 
 if __name__ == "__main__":
-    path = build(verbose=True)
-    print(path)
+    if len(sys.argv) >= 3 and sys.argv[1] == "--sanitize":
+        print(build_sanitized(sys.argv[2]))
+    else:
+        print(build(verbose=True))

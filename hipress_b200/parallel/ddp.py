@@ -58,8 +58,9 @@ class CompressionConfig:
     # inline issue)
     graph_capturable: bool = False
     # sharded exchange (tbq / terngrad): rank j owns 1/world of every bucket; compressed
-    # reduce-scatter to the owners, then compressed all-gather of the re-quantised averages
-    sharded: bool = False
+    # reduce-scatter to the owners, then compressed all-gather of the re-quantised averages.
+    # None = decide from the bucket size and the world size (prefer_sharded)
+    sharded: Optional[bool] = False
     # DGC extras (algorithm "dgc"): momentum correction with factor masking, local clipping
     momentum_correction: bool = False
     dgc_momentum: float = 0.9
@@ -82,6 +83,22 @@ class CompressionConfig:
     def needs_residual(self) -> bool:
         return self.algorithm in ("tbq", "graddrop", "dgc", "ecq") or (
             self.algorithm == "terngrad" and self.error_feedback)
+
+
+def prefer_sharded(bucket_bytes: float, world: int) -> bool:
+    """Size rule for the form of the tbq / terngrad exchange.
+
+    All-gather form: every rank stores its payload into all ``world`` slots and decodes
+    ``world`` payloads per element -- two phases, the fewest launches.  Sharded form: compressed
+    reduce-scatter to shard owners, then compressed all-gather of the re-quantised averages --
+    2 (world-1)/world of one payload on the wire and two table look-ups per element instead of
+    ``world``, for a third phase, a second flag wait and a second quantisation.  The sharded form
+    pays once a rank's outgoing payloads and its ``world``-fold decode dominate: large buckets on
+    many GPUs."""
+    return world >= 4 and bucket_bytes >= SHARDED_MIN_BYTES
+
+
+SHARDED_MIN_BYTES = 48 * (1 << 20)
 
 
 @dataclass
@@ -190,7 +207,12 @@ class CompressedDataParallel(nn.Module):
         # with a fused optimizer nobody reads the averaged gradient: the kernel that applies the
         # update leaves zeros behind, ready for the next backward pass
         cfg_dict["clear_grad"] = 1 if fused else 0
-        cfg_dict["sharded"] = 1 if self.config.sharded else 0
+        sharded = self.config.sharded
+        if sharded is None:
+            sharded = self.config.algorithm in ("tbq", "terngrad") and \
+                prefer_sharded(self.config.bucket_mb * (1 << 20), world)
+        self.sharded = bool(sharded)
+        cfg_dict["sharded"] = 1 if self.sharded else 0
         self.graph_capturable = bool(self.config.graph_capturable)
         if self.graph_capturable:
             if self.config.algorithm not in ("tbq", "terngrad", "graddrop", "dgc", "ecq") or not fused:

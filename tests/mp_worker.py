@@ -36,8 +36,7 @@ def same_on_all_ranks(t: torch.Tensor) -> bool:
     return all(int(v) == int(allv[0]) for v in allv)
 
 
-def check_codec(codec, kw, rank, world, local):
-    n = 300000 + 8
+def check_codec(codec, kw, rank, world, local, n=300000 + 8):
     cfg = dict(rank=rank, world=world, device=local, codec=codec, seed=5, flag_timeout_s=10.0, **kw)
     eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
     sym = SymmetricMemory(eng.symmetric_bytes, torch.device("cuda", local))
@@ -89,12 +88,12 @@ def check_codec(codec, kw, rank, world, local):
     del eng, sym
 
 
-def check_sharded(codec, kw, rank, world, local):
+def check_sharded(codec, kw, rank, world, local, device_epoch=0):
     """Compressed reduce-scatter + compressed all-gather across real GPUs against the CPU restatement."""
     from sharded_ref import expected, shard_elems
     n = 300000 + 8
     cfg = dict(rank=rank, world=world, device=local, codec=codec, seed=5, flag_timeout_s=10.0, sharded=1,
-               num_workers=0, **kw)
+               num_workers=0, device_epoch=device_epoch, **kw)
     eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
     sym = SymmetricMemory(eng.symmetric_bytes, torch.device("cuda", local))
     grad = torch.zeros(n, device="cuda")
@@ -137,10 +136,22 @@ def main():
         if rank == 0:
             print(f"MP_OK codec_{codec}_device_epoch", flush=True)
 
+    # large enough for the chunked compress path: 16-byte stores into the peers' slots
+    for codec, kw in [("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)), ("tbq", dict(threshold=0.01))]:
+        check_codec(codec, kw, rank, world, local, n=1400000 + 8)
+        if rank == 0:
+            print(f"MP_OK codec_{codec}_wide", flush=True)
+    check_codec("ecq", dict(bitwidth=2, alpha=1.0, beta=0.9, device_epoch=1, num_workers=0), rank, world, local)
+    if rank == 0:
+        print("MP_OK codec_ecq_device_epoch", flush=True)
+
     for codec, kw in [("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)), ("tbq", dict(threshold=0.01))]:
         check_sharded(codec, kw, rank, world, local)
         if rank == 0:
             print(f"MP_OK sharded_{codec}", flush=True)
+        check_sharded(codec, kw, rank, world, local, device_epoch=1)
+        if rank == 0:
+            print(f"MP_OK sharded_{codec}_device_epoch", flush=True)
 
     # DDP wrapper: replicas stay bit-identical, loss goes down
     torch.manual_seed(0)
@@ -182,6 +193,20 @@ def main():
     assert min(losses[-3:]) < losses[0]
     if rank == 0:
         print("MP_OK ddp_graphed", flush=True)
+
+    # the sharded exchange inside the captured step
+    torch.manual_seed(0)
+    net = resnet_tiny(10).cuda().to(memory_format=torch.channels_last)
+    sm = CompressedDataParallel(net, CompressionConfig("terngrad", bucket_mb=0.05, graph_capturable=True, sharded=True),
+                                lr=0.05, momentum=0.9)
+    sstep = GraphedTrainStep(sm, loss_fn, (xc, y))
+    assert sstep.whole_step
+    slosses = [float(sstep(xc, y).detach()) for _ in range(10)]
+    sm.check()
+    assert same_on_all_ranks(sm.flat_param), "graphed sharded replicas diverged"
+    assert min(slosses[-3:]) < slosses[0]
+    if rank == 0:
+        print("MP_OK ddp_graphed_sharded", flush=True)
 
     # DGC (momentum correction, clipping, fused AdamW) with the exchange captured in the graph
     from hipress_b200.parallel.dgc import DGCDataParallel

@@ -23,6 +23,8 @@ def test_engine_and_wrappers_across_gpus(nproc):
     res = _run_workers(nproc, 29540 + nproc)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     for name in ("codec_terngrad", "codec_tbq", "codec_graddrop", "codec_ecq", "codec_dense",
-                 "codec_terngrad_device_epoch", "codec_tbq_device_epoch", "sharded_terngrad", "sharded_tbq", "ddp_terngrad", "ddp_graphed",
-                 "ddp_graphed_dgc", "ddp_powersgd"):
+                 "codec_terngrad_device_epoch", "codec_tbq_device_epoch", "codec_terngrad_wide", "codec_tbq_wide",
+                 "codec_ecq_device_epoch", "sharded_terngrad", "sharded_tbq", "sharded_terngrad_device_epoch",
+                 "sharded_tbq_device_epoch", "ddp_terngrad", "ddp_graphed", "ddp_graphed_sharded", "ddp_graphed_dgc",
+                 "ddp_powersgd"):
         assert f"MP_OK {name}" in res.stdout, res.stdout[-2000:]
