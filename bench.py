@@ -181,14 +181,13 @@ class OurTrainer:
         self.model.step()
         return loss
 
-    def launches(self):
-        return int(self.model.metrics().get("kernel_launches", 0))
-
-    def exchange_metrics(self):
+    def snapshot(self):
+        """(kernel launches so far, exchange counters since the previous call).  One call to the
+        wrapper's ``metrics()``: it reads and resets the device-side wait counters."""
         m = self.model.metrics()
         keep = ("wait_us_total", "wait_us_max", "waits", "step_us", "exposed_tail_us", "stages", "selected_k",
-                "wire_bytes_last_step", "threshold")
-        return {k: m[k] for k in keep if k in m}
+                "candidates", "wire_bytes_last_step", "thresholds", "dropped_candidates")
+        return int(m.get("kernel_launches", 0)), {k: m[k] for k in keep if k in m}
 
     def finish(self):
         self.model.check()
@@ -431,11 +430,8 @@ class ReferenceTrainer:
             dist.all_reduce(self.vec_flat)
             self.vec_flat.div_(self.world)
 
-    def launches(self):
-        return None
-
-    def exchange_metrics(self):
-        return {}
+    def snapshot(self):
+        return None, {}
 
     def finish(self):
         if self.hp is not None:
@@ -471,10 +467,9 @@ def run(args):
     for i in range(max(args.warmup, 3)):
         trainer.step(resident[i % len(resident)])
     barrier()
-    trainer.exchange_metrics()   # reset the wait counters: warm-up waits include first-use set-up
 
     # ---- device-timed regions: exactly K steps each, inputs resident (per-step working set >> L2)
-    launches0 = trainer.launches()
+    launches0, _ = trainer.snapshot()   # also resets the wait counters: warm-up waits include first-use set-up
     region_ms = []
     try:
         clocks.mark_start()
@@ -490,8 +485,9 @@ def run(args):
         clocks.mark_end()
     finally:
         clocks.__exit__(None, None, None)
-    launches1 = trainer.launches()
-    exchange = trainer.exchange_metrics()
+    launches1, exchange = trainer.snapshot()
+    if "wait_us_total" in exchange:
+        exchange["wait_us_per_step"] = round(exchange["wait_us_total"] / (repeats * args.steps), 2)
     clock_summary = clocks.summary()
     ms = statistics.median(region_ms)
 

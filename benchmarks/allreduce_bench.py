@@ -213,9 +213,18 @@ def main():
             results.append(row)
             if rank == 0:
                 print(json.dumps(row), flush=True)
+    # captured graphs hold on to the communicator: drop them before it is torn down
+    fn = keep = step = None  # noqa: F841
+    import gc
+    gc.collect()
+    torch.cuda.synchronize()
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps({"done": True, "rows": len(results)}), flush=True)
+    sys.stdout.flush()
+    os._exit(0)   # leave without waiting on library teardown (an NCCL graph capture can stall it)
 
 
 if __name__ == "__main__":

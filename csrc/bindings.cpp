@@ -145,6 +145,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("residual") = py::none());
   m.def("terngrad_decompress", &ops::terngrad_decompress, py::arg("payloads"), py::arg("out"),
         py::arg("add") = false, py::arg("post_scale") = 1.0, py::arg("bitwidth") = 0);
+  m.def("dgc_momentum_compress", &ops::dgc_momentum_compress, py::arg("grad"), py::arg("u"), py::arg("v"),
+        py::arg("out"), py::arg("sample_rate"), py::arg("keep_fraction"), py::arg("seed"), py::arg("momentum"),
+        py::arg("clip") = 0.0, py::arg("zero_grad") = false);
   m.def("sparse_compress", &ops::sparse_compress, py::arg("grad"), py::arg("R"), py::arg("out"),
         py::arg("sample_rate"), py::arg("keep_fraction"), py::arg("seed"), py::arg("accumulate"));
   m.def("sparse_decompress", &ops::sparse_decompress, py::arg("payloads"), py::arg("out"),
@@ -479,6 +482,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            py::arg("device"))
       .def("wait_stats", &runtime::DdpEngine::wait_stats)
       .def("stage_times", &runtime::DdpEngine::stage_times)
+      .def("sparse_stats", &runtime::DdpEngine::sparse_stats)
       .def_property_readonly("epoch", &runtime::DdpEngine::epoch)
       .def_property_readonly("steps", &runtime::DdpEngine::steps)
       .def_property_readonly("launches", &runtime::DdpEngine::launches)

@@ -147,6 +147,12 @@ adamw_kernel(float* __restrict__ grad, float scale, AdamWApply a, int64_t n) {
 
 }  // namespace
 
+cudaError_t dgc_sumsq(const float* g, int64_t n, float* out, cudaStream_t stream) {
+  if (n <= 0 || g == nullptr || out == nullptr) return cudaErrorInvalidValue;
+  sumsq_kernel<<<grid_for(n, 148 * 4), kThreads, 0, stream>>>(g, n, out);
+  return cudaGetLastError();
+}
+
 cudaError_t dgc_accumulate(const float* grad, float* u, float* v, int64_t n, float momentum,
                            float clip, float* sumsq_scratch, cudaStream_t stream) {
   if (n <= 0) return cudaErrorInvalidValue;

@@ -134,6 +134,32 @@ size_t sparse_scratch_bytes(int64_t n);
 cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sample_rate,
                             double keep_fraction, uint64_t seed, int accumulate,
                             const PushTargets& dst, void* scratch, cudaStream_t stream);
+// The same compressor with the codec's state update fused into its one pass over the tensor.
+//   mode 0  plain: select from R as it is (DGC without momentum correction)
+//   mode 1  GradDrop: R += grad, then select from R
+//   mode 2  DGC with momentum correction: u = momentum*u + s*grad; R (the velocity v) += u; select
+//           from v; u and v are cleared at the sent positions (momentum factor masking).  s clips
+//           the bucket's gradient to norm `clip` (> 0; sumsq: one float of scratch, zero on entry,
+//           left zero).  zero_grad leaves zeros in grad: the dense gradient is rebuilt from the
+//           payloads afterwards, which saves the separate clearing pass.
+// For keep fractions up to 1 % the tensor is read once ("list form", see sparse.cu); otherwise,
+// or when the scratch cannot hold the expected candidates, the multi-pass scan form runs.
+// scratch: sparse_scratch_bytes(n) bytes, zero before its first use.
+struct SparseFuse {
+  int mode = 0;
+  const float* grad = nullptr;
+  float* u = nullptr;
+  float momentum = 0.f, clip = 0.f;
+  const float* sumsq = nullptr;
+  int zero_grad = 0;
+};
+cudaError_t sparse_compress_fused(const SparseFuse& fuse, float* R, int64_t n, double sample_rate,
+                                  double keep_fraction, uint64_t seed, const PushTargets& dst, void* scratch,
+                                  cudaStream_t stream);
+// {elements emitted, candidates over the sampled threshold (list form), threshold as float bits,
+// candidates dropped so far for lack of pool space} of the last call on `scratch`; asynchronous
+// copies to host4 on `stream`.
+cudaError_t sparse_read_stats(const void* scratch, unsigned int* host4, cudaStream_t stream);
 // add == 0 zero-fills out first.  Payloads are applied one after another in
 // rank order so that the fp32 sum is reproducible on every replica.
 cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
@@ -173,6 +199,8 @@ cudaError_t dense_gather_sum(const float* const* srcs, int world, float* out, in
 // sumsq_scratch: one float, zero on entry when clip > 0; cleared by dgc_mask.
 cudaError_t dgc_accumulate(const float* grad, float* u, float* v, int64_t n, float momentum,
                            float clip, float* sumsq_scratch, cudaStream_t stream);
+// out += sum of g[i]^2 (out: one float, not cleared here).
+cudaError_t dgc_sumsq(const float* g, int64_t n, float* out, cudaStream_t stream);
 // Momentum factor masking: u[idx] = 0 for every index in the sparse payload.
 cudaError_t dgc_mask(const uint8_t* payload, int64_t payload_capacity, float* u, int64_t n,
                      float* sumsq_scratch, cudaStream_t stream, const uint32_t* epoch_dev = nullptr,

@@ -24,9 +24,32 @@
 // Content rule (identical to the CPU codec): keep |R[i]| > threshold in
 // ascending index order; when over-selected keep the largest magnitudes, ties
 // toward the lower index.
+//
+// Two forms of everything after the sampling.  The passes above ("scan form") read the whole
+// tensor up to five times.  For keep fractions up to 1 % the "list form" reads it ONCE:
+//
+//   count+collect  the one pass over the tensor.  It applies the codec's state update (R += G
+//               for GradDrop; u = m*u + s*g, v += u and g = 0 for DGC with momentum correction;
+//               nothing for plain DGC) and appends every candidate |value| > threshold, as
+//               (index, value), to a per-warp list in index order.  A warp owns a contiguous
+//               part of its CTA's chunk, so the lists, taken in order, are sorted by index.
+//               Lists grow in blocks of 16 entries taken from a pool with one atomic.
+//   select      One CTA: exact cut among the candidates (radix select over the pool, 35 K
+//               entries for a 128 MB bucket at 0.1 %), kept counts per list, exclusive offsets,
+//               k, the header.
+//   emit        One warp per list: indices and values to every destination, residual (and
+//               DGC's momentum u) cleared at the emitted positions, then the completion flag.
+//
+// The sample keys are stored by the first sampling round and re-read by the other two (the
+// scan form recomputes them, three random gathers per sample and round with momentum
+// correction).  The pool is sized for many times the expected number of candidates (see
+// list_plan); should it still run out, the candidates that did not fit stay in the residual
+// and are sent in a later step (counted in SparseScratch::dropped).
 #include "../common/codec_math.h"
 #include "kernels.h"
 #include "p2p.cuh"
+
+#include <cmath>
 
 namespace hipress {
 namespace cuda {
@@ -37,6 +60,10 @@ constexpr int kThreads = 256;
 constexpr int kBins = 2048;
 constexpr int kMaxBlocks = 148 * 4;
 constexpr int kTile = kThreads * 4;  // elements per CTA iteration
+constexpr int kMaxLists = kMaxBlocks * (kThreads / 32);
+constexpr int kBlockEntries = 16;
+constexpr unsigned int kNoBlock = 0xffffffffu;
+constexpr double kListMaxKeep = 0.01;   // the list form serves keep fractions up to this
 
 struct SparseScratch {
   unsigned int shist[3][kBins];  // sample radix-select rounds
@@ -53,7 +80,18 @@ struct SparseScratch {
   unsigned int cand;                    // candidates over the threshold
   unsigned int cut_key, ties_kept;      // final rule
   unsigned int k;                       // elements emitted
-  unsigned int pad[3];
+  // list form
+  unsigned int pool_used;               // blocks handed out (reset by select)
+  unsigned int dropped;                 // candidates that found no block (cumulative)
+  unsigned int last_cand;               // candidates seen by the last call (metrics)
+  unsigned int list_head[kMaxLists];    // first block of each warp's list, kNoBlock when empty
+  unsigned int list_gt[kMaxLists], list_eq[kMaxLists];   // exclusive offsets per list
+};
+
+// One block of a candidate list: 16 (index, value bits) pairs.
+struct ListBlock {
+  unsigned int count, next, pad0, pad1;
+  uint2 entry[kBlockEntries];
 };
 
 __device__ __forceinline__ int digit_of(uint32_t key, int round) {
@@ -149,12 +187,39 @@ __device__ __forceinline__ void for_each_value(const float* __restrict__ R, int6
   }
 }
 
+// ---- the value the selection looks at, for one element, by mode
+// mode 0: R as it is (plain DGC); mode 1: G + R (GradDrop's accumulation); mode 2: DGC with
+// momentum correction, v + (m*u + s*g), rounded exactly as the collect pass rounds it.
+struct SparseFuseDev {
+  const float* grad;   // modes 1, 2
+  float* u;            // mode 2: momentum
+  float momentum;      // mode 2
+  float clip;          // mode 2: > 0 = scale g by min(1, clip / |g|)
+  const float* sumsq;  // mode 2 with clipping: |g|^2 of the bucket
+  int zero_grad;       // mode 2: leave zeros in grad (the dense gradient is rebuilt from the payloads)
+  int mode;
+};
+__device__ __forceinline__ float dgc_clip_scale(const SparseFuseDev& f) {
+  if (f.mode != 2 || f.clip <= 0.f) return 1.0f;
+  return fminf(1.0f, f.clip / (sqrtf(*f.sumsq) + 1e-6f));
+}
+__device__ __forceinline__ float dgc_new_u(float u, float g, float momentum, float scale) {
+  return __fmaf_rn(momentum, u, __fmul_rn(scale, g));
+}
+__device__ __forceinline__ float fused_value(const SparseFuseDev& f, const float* R, uint32_t i, float scale) {
+  if (f.mode == 0) return R[i];
+  if (f.mode == 1) return hp_add(f.grad[i], R[i]);
+  return __fadd_rn(R[i], dgc_new_u(f.u[i], f.grad[i], f.momentum, scale));
+}
+
 // ---- sample rounds
+// keys: when non-null, round 0 stores every sample's key there and rounds 1 and 2 read them
+// back instead of drawing and gathering again.
 template <int ROUND>
 __global__ void __launch_bounds__(kThreads)
-sample_round_kernel(const float* __restrict__ grad, const float* __restrict__ R, int64_t n,
-                    int64_t sample_cnt, unsigned int rank0, uint64_t seed, int accumulate,
-                    SparseScratch* s, const uint32_t* epoch_dev) {
+sample_round_kernel(SparseFuseDev fuse, const float* __restrict__ R, int64_t n,
+                    int64_t sample_cnt, unsigned int rank0, uint64_t seed,
+                    SparseScratch* s, uint32_t* __restrict__ keys, const uint32_t* epoch_dev) {
   if (epoch_dev != nullptr) seed += uint64_t(*epoch_dev) * kEpochSeedStride;  // see PushTargets
   __shared__ unsigned int sh[kBins];
   for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
@@ -171,11 +236,17 @@ sample_round_kernel(const float* __restrict__ grad, const float* __restrict__ R,
     }
   }
   __syncthreads();
+  const float scale = dgc_clip_scale(fuse);
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < sample_cnt; x += stride) {
-    const uint32_t idx = sparse_sample_index(seed, x, uint32_t(n));
-    const float v = accumulate ? hp_add(grad[idx], R[idx]) : R[idx];
-    const uint32_t key = abs_key(v);
+    uint32_t key;
+    if (ROUND > 0 && keys != nullptr) {
+      key = keys[x];
+    } else {
+      const uint32_t idx = sparse_sample_index(seed, x, uint32_t(n));
+      key = abs_key(fused_value(fuse, R, idx, scale));
+      if (keys != nullptr) keys[x] = key;
+    }
     if (prefix_matches(key, ROUND, prefix)) atomicAdd(&sh[digit_of(key, ROUND)], 1u);
   }
   hist_flush(sh, s->shist[ROUND]);
@@ -184,7 +255,7 @@ sample_round_kernel(const float* __restrict__ grad, const float* __restrict__ R,
 // ---- count pass (also performs R += G)
 __global__ void __launch_bounds__(kThreads)
 count_kernel(const float* __restrict__ grad, float* __restrict__ R, int64_t n, int64_t chunk,
-             int64_t sample_cnt, unsigned int rank0, int accumulate, SparseScratch* s) {
+             int64_t sample_cnt, unsigned int rank0, int accumulate, int zero_grad, SparseScratch* s) {
   __shared__ unsigned int sh[kBins];
   __shared__ unsigned int blk_cnt;
   for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
@@ -213,6 +284,7 @@ count_kernel(const float* __restrict__ grad, float* __restrict__ R, int64_t n, i
     for (int64_t i = begin + threadIdx.x; i < end; i += kThreads) {
       const float r = hp_add(grad[i], R[i]);
       R[i] = r;
+      if (zero_grad) const_cast<float*>(grad)[i] = 0.f;
       const uint32_t key = abs_key(r);
       if (key > thr_key) {
         ++mine;
@@ -354,6 +426,7 @@ scan_kernel(int blocks, PushTargets dst, SparseScratch* s) {
     uint8_t header[4];
     for (int i = 0; i < 4; ++i) header[i] = uint8_t(total >> (8 * i));
     push_bytes(dst, 0, header, 4);
+    s->last_cand = s->cand;
     s->cand = 0;
   }
   unsigned int* h = &s->shist[0][0];
@@ -370,8 +443,8 @@ scan_kernel(int blocks, PushTargets dst, SparseScratch* s) {
 // across the whole CTA per 1,024-element tile -- five barriers per tile that held a hit -- and
 // took 64 us for 64 MB where the reads cost 12.)
 __global__ void __launch_bounds__(kThreads)
-write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
-             const SparseScratch* s) {
+write_kernel(float* __restrict__ R, float* __restrict__ u_mask, float* sumsq_to_clear, int64_t n,
+             int64_t chunk, PushTargets dst, const SparseScratch* s) {
   resolve_epoch(dst);
   constexpr int kWarps = kThreads / 32;
   __shared__ unsigned int warp_gt[kWarps], warp_eq[kWarps];
@@ -485,6 +558,7 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
             push_u32(dst, 4 + 4 * int64_t(pos), uint32_t(e0 + j));
             push_u32(dst, 4 + 4 * int64_t(k_total) + 4 * int64_t(pos), __float_as_uint(v[j]));
             R[e0 + j] = 0.0f;
+            if (u_mask != nullptr) u_mask[e0 + j] = 0.0f;   // DGC's momentum factor masking
           }
         }
         gt_before += above;
@@ -494,6 +568,7 @@ write_kernel(float* __restrict__ R, int64_t n, int64_t chunk, PushTargets dst,
       run_eq += __shfl_sync(0xffffffffu, inc_eq, 31);
     }
   }
+  if (sumsq_to_clear != nullptr && blockIdx.x == 0 && threadIdx.x == 0) *sumsq_to_clear = 0.f;
   publish_when_grid_done(dst);
 }
 
@@ -526,6 +601,339 @@ scatter_kernel(const uint8_t* __restrict__ payload, int64_t cap, float* __restri
   }
 }
 
+// Scan form, DGC with momentum correction: the state update as a pass of its own
+// (u = m*u + s*g, v += u, g = 0), with the same rounding as the list form's collect pass.
+__global__ void __launch_bounds__(kThreads)
+dgc_update_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n) {
+  const float scale = dgc_clip_scale(fuse);
+  float* gw = const_cast<float*>(fuse.grad);
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const float u = dgc_new_u(fuse.u[i], fuse.grad[i], fuse.momentum, scale);
+    fuse.u[i] = u;
+    R[i] = __fadd_rn(R[i], u);
+    if (fuse.zero_grad) gw[i] = 0.f;
+  }
+}
+
+// ================================================================ list form
+// Pool of list blocks, behind the sample keys in the scratch.
+struct ListPool {
+  ListBlock* blocks;
+  unsigned int capacity;  // blocks
+};
+
+// Cursor of a warp's list; only lane 0's copy is used.
+struct ListCursor {
+  unsigned int block = kNoBlock, fill = 0, lost = 0;
+  bool exhausted = false;
+};
+
+// Appends this step's candidates of the calling warp to the warp's list, in lane order and,
+// within a lane, element order.  count: candidates of this lane (0..4); idx / val: their
+// indices and values.  Candidates are rare (0.1 % of the elements), so the entries are handed
+// to lane 0 by shuffle and appended one at a time; a list grows by one block of the pool when
+// its last block is full.
+__device__ __forceinline__ void list_append(SparseScratch* s, const ListPool& pool, int list, int lane,
+                                            unsigned int count, const uint32_t (&idx)[4], const float (&val)[4],
+                                            ListCursor& cur) {
+  unsigned int mask = __ballot_sync(0xffffffffu, count != 0);
+  while (mask != 0) {
+    const int src = __ffs(mask) - 1;
+    mask &= mask - 1;
+    const unsigned int c = __shfl_sync(0xffffffffu, count, src);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t i = __shfl_sync(0xffffffffu, idx[j], src);
+      const float v = __shfl_sync(0xffffffffu, val[j], src);
+      if (lane != 0 || j >= int(c)) continue;
+      if (cur.exhausted) {
+        ++cur.lost;
+        continue;
+      }
+      if (cur.block == kNoBlock || cur.fill == kBlockEntries) {
+        const unsigned int id = atomicAdd(&s->pool_used, 1u);
+        if (id >= pool.capacity) {
+          cur.exhausted = true;
+          ++cur.lost;
+          continue;
+        }
+        pool.blocks[id].count = 0;
+        pool.blocks[id].next = kNoBlock;
+        if (cur.block == kNoBlock) s->list_head[list] = id;
+        else pool.blocks[cur.block].next = id;
+        cur.block = id;
+        cur.fill = 0;
+      }
+      pool.blocks[cur.block].entry[cur.fill] = make_uint2(i, __float_as_uint(v));
+      pool.blocks[cur.block].count = ++cur.fill;
+    }
+  }
+}
+
+// ---- the one pass over the tensor
+__global__ void __launch_bounds__(kThreads)
+collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chunk, int64_t sample_cnt,
+               SparseScratch* s, ListPool pool) {
+  constexpr int kWarps = kThreads / 32;
+  uint32_t thr_key = 0;
+  if (sample_cnt > 0) {
+    unsigned int bin, rin;
+    pick_from_top(s->shist[2], s->s_rank[2], bin, rin);
+    thr_key = extend_prefix(s->s_prefix[2], 2, bin);
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) s->thr_key = thr_key;
+  const float scale = dgc_clip_scale(fuse);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int list = blockIdx.x * kWarps + warp;
+  const int64_t begin = int64_t(blockIdx.x) * chunk;
+  const int64_t end = begin + chunk < n ? begin + chunk : n;
+  // warp ranges: multiples of 128 elements so that every step is 32 lanes x 4 elements
+  int64_t wlen = (end - begin + kWarps - 1) / kWarps;
+  wlen = (wlen + 127) / 128 * 128;
+  const int64_t wbegin = begin + warp * wlen < end ? begin + warp * wlen : end;
+  const int64_t wend = wbegin + wlen < end ? wbegin + wlen : end;
+  uintptr_t bits = reinterpret_cast<uintptr_t>(R);
+  if (fuse.mode >= 1) bits |= reinterpret_cast<uintptr_t>(fuse.grad);
+  if (fuse.mode == 2) bits |= reinterpret_cast<uintptr_t>(fuse.u);
+  const bool vec_ok = (bits & 15) == 0 && (begin & 3) == 0;
+  float* gw = const_cast<float*>(fuse.grad);   // mode 2 leaves zeros behind
+
+  ListCursor cur;
+  if (lane == 0) s->list_head[list] = kNoBlock;
+
+  // state update + candidate test of the 4 elements at e0 (e0 + 3 < wend, 16-byte aligned)
+  auto step4 = [&](int64_t e0, float4 r4, float4 g4, float4 u4, uint32_t (&idx)[4], float (&val)[4]) -> unsigned int {
+    float r[4] = {r4.x, r4.y, r4.z, r4.w};
+    if (fuse.mode == 1) {
+      const float g[4] = {g4.x, g4.y, g4.z, g4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = hp_add(g[j], r[j]);
+      *reinterpret_cast<float4*>(R + e0) = make_float4(r[0], r[1], r[2], r[3]);
+      if (fuse.zero_grad) *reinterpret_cast<float4*>(gw + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else if (fuse.mode == 2) {
+      const float g[4] = {g4.x, g4.y, g4.z, g4.w};
+      float u[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        u[j] = dgc_new_u(u[j], g[j], fuse.momentum, scale);
+        r[j] = __fadd_rn(r[j], u[j]);
+      }
+      *reinterpret_cast<float4*>(fuse.u + e0) = make_float4(u[0], u[1], u[2], u[3]);
+      *reinterpret_cast<float4*>(R + e0) = make_float4(r[0], r[1], r[2], r[3]);
+      if (fuse.zero_grad) *reinterpret_cast<float4*>(gw + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    unsigned int count = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (abs_key(r[j]) > thr_key) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {   // compile-time indices keep idx / val in registers
+          if (c == int(count)) {
+            idx[c] = uint32_t(e0 + j);
+            val[c] = r[j];
+          }
+        }
+        ++count;
+      }
+    }
+    return count;
+  };
+
+  int64_t base = wbegin;
+  if (vec_ok) {
+    // four steps per iteration with their loads issued together
+    for (; base + 512 <= wend; base += 512) {
+      float4 r4[4], g4[4] = {}, u4[4] = {};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int64_t e0 = base + q * 128 + lane * 4;
+        r4[q] = *reinterpret_cast<const float4*>(R + e0);
+        if (fuse.mode >= 1) g4[q] = *reinterpret_cast<const float4*>(fuse.grad + e0);
+        if (fuse.mode == 2) u4[q] = *reinterpret_cast<const float4*>(fuse.u + e0);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t idx[4] = {0u, 0u, 0u, 0u};
+        float val[4] = {0.f, 0.f, 0.f, 0.f};
+        const unsigned int count = step4(base + q * 128 + lane * 4, r4[q], g4[q], u4[q], idx, val);
+        if (__ballot_sync(0xffffffffu, count != 0) != 0) list_append(s, pool, list, lane, count, idx, val, cur);
+      }
+    }
+  }
+  // the rest of the warp's range, element by element within steps of 128
+  for (; base < wend; base += 128) {
+    uint32_t idx[4] = {0u, 0u, 0u, 0u};
+    float val[4] = {0.f, 0.f, 0.f, 0.f};
+    unsigned int count = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t e = base + lane * 4 + j;
+      if (e < wend) {
+        float r = R[e];
+        if (fuse.mode == 1) {
+          r = hp_add(fuse.grad[e], r);
+          R[e] = r;
+          if (fuse.zero_grad) gw[e] = 0.f;
+        } else if (fuse.mode == 2) {
+          const float u = dgc_new_u(fuse.u[e], fuse.grad[e], fuse.momentum, scale);
+          r = __fadd_rn(r, u);
+          fuse.u[e] = u;
+          R[e] = r;
+          if (fuse.zero_grad) gw[e] = 0.f;
+        }
+        if (abs_key(r) > thr_key) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (c == int(count)) {
+              idx[c] = uint32_t(e);
+              val[c] = r;
+            }
+          }
+          ++count;
+        }
+      }
+    }
+    if (__ballot_sync(0xffffffffu, count != 0) != 0) list_append(s, pool, list, lane, count, idx, val, cur);
+  }
+  if (lane == 0 && cur.lost != 0) atomicAdd(&s->dropped, cur.lost);
+}
+
+// ---- one CTA: exact cut among the candidates, offsets, k, header, housekeeping
+__global__ void __launch_bounds__(kThreads)
+select_kernel(int lists, unsigned int expected, PushTargets dst, SparseScratch* s, ListPool pool,
+              const float* sumsq_to_clear) {
+  resolve_epoch(dst);
+  __shared__ unsigned int sh[kBins];
+  __shared__ unsigned int part_gt[kThreads], part_eq[kThreads];
+  __shared__ unsigned int total_sh;
+  const unsigned int used = s->pool_used < pool.capacity ? s->pool_used : pool.capacity;
+  const uint32_t thr_key = s->thr_key;
+  // how many candidates are there (block counts are final: the collect pass has completed)
+  unsigned int mine = 0;
+  for (unsigned int b = threadIdx.x; b < used; b += kThreads) mine += pool.blocks[b].count;
+  if (threadIdx.x == 0) total_sh = 0;
+  __syncthreads();
+  atomicAdd(&total_sh, mine);
+  __syncthreads();
+  const unsigned int cand = total_sh;
+  uint32_t cut = thr_key;
+  unsigned int ties = 0;
+  if (cand > expected) {
+    // radix select of the element of rank expected-1 (0-based, from the top) over the pool
+    uint32_t prefix = 0;
+    unsigned int rank = expected - 1;
+    for (int round = 0; round < 3; ++round) {
+      for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
+      __syncthreads();
+      for (unsigned int b = threadIdx.x; b < used; b += kThreads) {
+        const unsigned int c = pool.blocks[b].count;
+        for (unsigned int e = 0; e < c; ++e) {
+          const uint32_t key = pool.blocks[b].entry[e].y & 0x7fffffffu;
+          const bool match = round == 0 ? true : round == 1 ? (key >> 21) == prefix : (key >> 10) == prefix;
+          if (match) atomicAdd(&sh[round == 0 ? int(key >> 21) : round == 1 ? int((key >> 10) & 0x7ffu) : int(key & 0x3ffu)], 1u);
+        }
+      }
+      __syncthreads();
+      unsigned int bin, rin;
+      pick_from_top(sh, rank, bin, rin);
+      prefix = round == 0 ? bin : round == 1 ? (prefix << 11) | bin : (prefix << 10) | bin;
+      rank = rin;
+      __syncthreads();
+    }
+    cut = prefix;
+    ties = rank + 1;
+  }
+  // kept counts per list, in list (= index) order
+  const int per = (lists + kThreads - 1) / kThreads;
+  const int l0 = threadIdx.x * per, l1 = (l0 + per < lists) ? l0 + per : lists;
+  unsigned int g = 0, e = 0;
+  for (int l = l0; l < l1; ++l) {
+    unsigned int lg = 0, le = 0;
+    for (unsigned int b = s->list_head[l]; b != kNoBlock && b < pool.capacity; b = pool.blocks[b].next) {
+      const unsigned int c = pool.blocks[b].count;
+      for (unsigned int i = 0; i < c; ++i) {
+        const uint32_t key = pool.blocks[b].entry[i].y & 0x7fffffffu;
+        lg += key > cut;
+        le += key == cut;
+      }
+    }
+    s->list_gt[l] = g;   // exclusive within this thread's run; the run's base is added below
+    s->list_eq[l] = e;
+    g += lg;
+    e += le;
+  }
+  part_gt[threadIdx.x] = g;
+  part_eq[threadIdx.x] = e;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int rg = 0, re = 0;
+    for (int i = 0; i < kThreads; ++i) {
+      const unsigned int a = part_gt[i], b = part_eq[i];
+      part_gt[i] = rg;
+      part_eq[i] = re;
+      rg += a;
+      re += b;
+    }
+    const unsigned int k = rg + (re < ties ? re : ties);
+    s->k = k;
+    s->cut_key = cut;
+    s->ties_kept = ties;
+    s->last_cand = cand;
+    const uint32_t total = 4u + 8u * k;
+    uint8_t header[4];
+    for (int i = 0; i < 4; ++i) header[i] = uint8_t(total >> (8 * i));
+    push_bytes(dst, 0, header, 4);
+    s->pool_used = 0;
+    s->cand = 0;
+    if (sumsq_to_clear != nullptr) *const_cast<float*>(sumsq_to_clear) = 0.f;
+  }
+  __syncthreads();
+  for (int l = l0; l < l1; ++l) {
+    s->list_gt[l] += part_gt[threadIdx.x];
+    s->list_eq[l] += part_eq[threadIdx.x];
+  }
+  unsigned int* h = &s->shist[0][0];
+  for (int i = threadIdx.x; i < 3 * kBins; i += kThreads) h[i] = 0;
+}
+
+// ---- one warp per list: deliver, clear the emitted positions, publish
+__global__ void __launch_bounds__(kThreads)
+emit_kernel(float* __restrict__ R, float* __restrict__ u_mask, int lists, PushTargets dst,
+            const SparseScratch* s, ListPool pool) {
+  resolve_epoch(dst);
+  const int lane = threadIdx.x & 31;
+  const int list = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const uint32_t cut = s->cut_key;
+  const unsigned int ties = s->ties_kept, k_total = s->k;
+  if (list < lists) {
+    unsigned int run_gt = s->list_gt[list], run_eq = s->list_eq[list];
+    for (unsigned int b = s->list_head[list]; b != kNoBlock && b < pool.capacity; b = pool.blocks[b].next) {
+      const unsigned int c = pool.blocks[b].count;
+      uint2 en = make_uint2(0u, 0u);
+      if (lane < int(c)) en = pool.blocks[b].entry[lane];
+      const uint32_t key = en.y & 0x7fffffffu;
+      const bool above = lane < int(c) && key > cut, at = lane < int(c) && key == cut;
+      const unsigned int ma = __ballot_sync(0xffffffffu, above), me = __ballot_sync(0xffffffffu, at);
+      const unsigned int lt = (1u << lane) - 1u;
+      const unsigned int gt_before = run_gt + __popc(ma & lt), eq_before = run_eq + __popc(me & lt);
+      if (above || (at && eq_before < ties)) {
+        const unsigned int pos = gt_before + (eq_before < ties ? eq_before : ties);
+        if (pos < k_total) {
+          push_u32(dst, 4 + 4 * int64_t(pos), en.x);
+          push_u32(dst, 4 + 4 * int64_t(k_total) + 4 * int64_t(pos), en.y);
+          R[en.x] = 0.0f;
+          if (u_mask != nullptr) u_mask[en.x] = 0.0f;
+        }
+      }
+      run_gt += __popc(ma);
+      run_eq += __popc(me);
+    }
+  }
+  publish_when_grid_done(dst);
+}
+
 struct Plan {
   int blocks;
   int64_t chunk;
@@ -542,12 +950,40 @@ inline Plan plan_for(int64_t n) {
 
 }  // namespace
 
-size_t sparse_scratch_bytes(int64_t) { return sizeof(SparseScratch); }
+namespace {
 
-cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sample_rate,
-                            double keep_fraction, uint64_t seed, int accumulate,
-                            const PushTargets& dst, void* scratch, cudaStream_t stream) {
-  if (n <= 0 || n > 0x7fffffff || scratch == nullptr) return cudaErrorInvalidValue;
+// Layout of the scratch behind SparseScratch: sample keys, then the pool of list blocks.  Both
+// are sized from n alone, so that one allocation serves every keep fraction and sample rate a
+// caller may pick later; a call whose sample or expected candidate count does not fit takes the
+// scan form, which needs neither.
+struct ListPlan {
+  int64_t key_capacity;    // sample keys
+  int64_t pool_blocks;
+  size_t keys_offset, pool_offset, total_bytes;
+};
+inline ListPlan list_plan(int64_t n) {
+  ListPlan p;
+  p.key_capacity = n / 100 + 1024;
+  // candidates: 6 % of n (six times the largest expectation the list form serves) plus a floor
+  // that covers thresholds drawn from a handful of samples, plus one partly filled block per list
+  const int64_t entries = n / 100 * 6 + 65536;
+  p.pool_blocks = entries / kBlockEntries + kMaxLists;
+  p.keys_offset = (sizeof(SparseScratch) + 255) / 256 * 256;
+  p.pool_offset = (p.keys_offset + size_t(p.key_capacity) * 4 + 255) / 256 * 256;
+  p.total_bytes = p.pool_offset + size_t(p.pool_blocks) * sizeof(ListBlock);
+  return p;
+}
+
+}  // namespace
+
+size_t sparse_scratch_bytes(int64_t n) { return list_plan(n < 1 ? 1 : n).total_bytes; }
+
+cudaError_t sparse_compress_fused(const SparseFuse& fuse, float* R, int64_t n, double sample_rate,
+                                  double keep_fraction, uint64_t seed, const PushTargets& dst, void* scratch,
+                                  cudaStream_t stream) {
+  if (n <= 0 || n > 0x7fffffff || scratch == nullptr || R == nullptr) return cudaErrorInvalidValue;
+  if (fuse.mode < 0 || fuse.mode > 2 || (fuse.mode >= 1 && fuse.grad == nullptr) || (fuse.mode == 2 && fuse.u == nullptr))
+    return cudaErrorInvalidValue;
   for (int p = 0; p < dst.world; ++p)
     if (reinterpret_cast<uintptr_t>(dst.payload[p]) & 3) return cudaErrorInvalidValue;
   auto* s = static_cast<SparseScratch*>(scratch);
@@ -557,22 +993,78 @@ cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sampl
   const int64_t sample_cnt = sparse_sample_count(n, sample_rate);
   int64_t rank0 = sparse_threshold_rank(sample_cnt, keep_fraction);
   if (sample_cnt > 0 && rank0 > sample_cnt - 1) rank0 = sample_cnt - 1;
+  const ListPlan lp = list_plan(n);
+  SparseFuseDev f{fuse.grad, fuse.u, fuse.momentum, fuse.clip, fuse.sumsq, fuse.zero_grad, fuse.mode};
+  uint32_t* keys = sample_cnt <= lp.key_capacity
+                       ? reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(scratch) + lp.keys_offset) : nullptr;
+  // the list form: keep fractions up to 1 %, and a pool that holds the candidates with a wide
+  // margin: their number is about n (rank0+1) / (samples+1) with a relative spread of
+  // 1 / sqrt(rank0+1); without sampling every non-zero element is a candidate
+  bool lists = keep_fraction <= kListMaxKeep && sample_cnt > 0;
+  if (lists) {
+    const double mean = double(n) * double(rank0 + 1) / double(sample_cnt + 1);
+    const double need = mean * (1.0 + 40.0 / std::sqrt(double(rank0 + 1)));
+    lists = need <= double(lp.pool_blocks - kMaxLists) * kBlockEntries;
+  }
+  if (fuse.mode == 2 && fuse.clip > 0.f) {
+    if (fuse.sumsq == nullptr) return cudaErrorInvalidValue;
+    cudaError_t e = dgc_sumsq(fuse.grad, n, const_cast<float*>(fuse.sumsq), stream);
+    if (e != cudaSuccess) return e;
+  }
   if (sample_cnt > 0) {
     int64_t sb = (sample_cnt + kThreads - 1) / kThreads;
     if (sb > kMaxBlocks) sb = kMaxBlocks;
-    sample_round_kernel<0><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s, dst.epoch_dev);
-    sample_round_kernel<1><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s, dst.epoch_dev);
-    sample_round_kernel<2><<<int(sb), kThreads, 0, stream>>>(grad, R, n, sample_cnt, unsigned(rank0), seed, accumulate, s, dst.epoch_dev);
+    sample_round_kernel<0><<<int(sb), kThreads, 0, stream>>>(f, R, n, sample_cnt, unsigned(rank0), seed, s, keys, dst.epoch_dev);
+    sample_round_kernel<1><<<int(sb), kThreads, 0, stream>>>(f, R, n, sample_cnt, unsigned(rank0), seed, s, keys, dst.epoch_dev);
+    sample_round_kernel<2><<<int(sb), kThreads, 0, stream>>>(f, R, n, sample_cnt, unsigned(rank0), seed, s, keys, dst.epoch_dev);
   }
-  count_kernel<<<pl.blocks, kThreads, 0, stream>>>(grad, R, n, pl.chunk, sample_cnt, unsigned(rank0), accumulate, s);
+  PushTargets hdr = dst;
+  hdr.done = nullptr;
+  if (lists) {
+    ListPool pool{reinterpret_cast<ListBlock*>(static_cast<uint8_t*>(scratch) + lp.pool_offset),
+                  static_cast<unsigned int>(lp.pool_blocks)};
+    const int nlists = pl.blocks * (kThreads / 32);
+    collect_kernel<<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);
+    select_kernel<<<1, kThreads, 0, stream>>>(nlists, unsigned(expected), hdr, s, pool,
+                                              fuse.mode == 2 && fuse.clip > 0.f ? fuse.sumsq : nullptr);
+    emit_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, fuse.mode == 2 ? fuse.u : nullptr, nlists, dst, s, pool);
+    return cudaGetLastError();
+  }
+  // scan form
+  if (fuse.mode == 2) {
+    dgc_update_kernel<<<pl.blocks, kThreads, 0, stream>>>(f, R, n);
+  }
+  count_kernel<<<pl.blocks, kThreads, 0, stream>>>(fuse.grad, R, n, pl.chunk, sample_cnt, unsigned(rank0),
+                                                   fuse.mode == 1 ? 1 : 0, fuse.zero_grad, s);
   trim_round_kernel<1><<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
   trim_round_kernel<2><<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
   recount_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, unsigned(expected), s);
-  PushTargets hdr = dst;
-  hdr.done = nullptr;
   scan_kernel<<<1, 1024, 0, stream>>>(pl.blocks, hdr, s);
-  write_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, n, pl.chunk, dst, s);
+  write_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, fuse.mode == 2 ? fuse.u : nullptr,
+                                                   fuse.mode == 2 && fuse.clip > 0.f ? const_cast<float*>(fuse.sumsq) : nullptr,
+                                                   n, pl.chunk, dst, s);
   return cudaGetLastError();
+}
+
+cudaError_t sparse_compress(const float* grad, float* R, int64_t n, double sample_rate,
+                            double keep_fraction, uint64_t seed, int accumulate,
+                            const PushTargets& dst, void* scratch, cudaStream_t stream) {
+  SparseFuse fuse;
+  fuse.mode = accumulate ? 1 : 0;
+  fuse.grad = accumulate ? grad : nullptr;
+  return sparse_compress_fused(fuse, R, n, sample_rate, keep_fraction, seed, dst, scratch, stream);
+}
+
+// Counters of the last compress call that used `scratch`: {elements emitted, candidates over the
+// sampled threshold (list form; 0 otherwise), threshold as the bit pattern of a float, candidates
+// dropped so far because the pool was full}.  Copied to the host on `stream`.
+cudaError_t sparse_read_stats(const void* scratch, unsigned int* host4, cudaStream_t stream) {
+  const auto* s = static_cast<const SparseScratch*>(scratch);
+  cudaError_t e = cudaMemcpyAsync(host4 + 0, &s->k, 4, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(host4 + 1, &s->last_cand, 4, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(host4 + 2, &s->thr_key, 4, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(host4 + 3, &s->dropped, 4, cudaMemcpyDeviceToHost, stream);
+  return e;
 }
 
 cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,

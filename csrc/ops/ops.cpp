@@ -279,6 +279,36 @@ void sparse_compress(const c10::optional<torch::Tensor>& grad, torch::Tensor R, 
   }
 }
 
+void dgc_momentum_compress(torch::Tensor grad, torch::Tensor u, torch::Tensor v, torch::Tensor out,
+                           double sample_rate, double keep_fraction, int64_t seed, double momentum,
+                           double clip, bool zero_grad) {
+  check_f32(grad, "grad");
+  check_f32(u, "u");
+  check_f32(v, "v");
+  check_u8(out, "out");
+  check_same_device(v, out);
+  check_same_device(v, grad);
+  check_same_device(v, u);
+  const int64_t n = v.numel();
+  TORCH_CHECK(v.is_cuda(), "dgc_momentum_compress runs on CUDA tensors");
+  TORCH_CHECK(n > 0 && n <= 0x7fffffff && grad.numel() == n && u.numel() == n, "grad, u and v must have the same size");
+  TORCH_CHECK(keep_fraction > 0.0 && keep_fraction <= 1.0, "keep_fraction must be in (0, 1]");
+  TORCH_CHECK(out.numel() >= sparse_payload_bytes(n, keep_fraction), "out needs ",
+              sparse_payload_bytes(n, keep_fraction), " bytes");
+  c10::cuda::CUDAGuard guard(v.device());
+  uint8_t* base = static_cast<uint8_t*>(scratch_for(v, 16384 + cuda::sparse_scratch_bytes(n)));
+  cuda::SparseFuse fuse;
+  fuse.mode = 2;
+  fuse.grad = grad.data_ptr<float>();
+  fuse.u = u.data_ptr<float>();
+  fuse.momentum = float(momentum);
+  fuse.clip = float(clip);
+  fuse.sumsq = reinterpret_cast<float*>(base + 12288);
+  fuse.zero_grad = zero_grad ? 1 : 0;
+  HP_CHECK_CUDA(cuda::sparse_compress_fused(fuse, v.data_ptr<float>(), n, sample_rate, keep_fraction, uint64_t(seed),
+                                            local_target(out), base + 16384, at::cuda::getCurrentCUDAStream()));
+}
+
 void sparse_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
                        double post_scale) {
   check_f32(out, "out");

@@ -37,6 +37,12 @@ void terngrad_decompress(const std::vector<torch::Tensor>& payloads, torch::Tens
 // accumulate: R += grad first (GradDrop).  Otherwise grad may be undefined (DGC).
 void sparse_compress(const c10::optional<torch::Tensor>& grad, torch::Tensor R, torch::Tensor out,
                      double sample_rate, double keep_fraction, int64_t seed, bool accumulate);
+// DGC with momentum correction in one fused pipeline (CUDA): u = momentum*u + s*grad, v += u,
+// top-k of v into `out`, u and v cleared at the sent positions; s clips grad to norm `clip`
+// (<= 0: off); zero_grad leaves zeros in grad.
+void dgc_momentum_compress(torch::Tensor grad, torch::Tensor u, torch::Tensor v, torch::Tensor out,
+                           double sample_rate, double keep_fraction, int64_t seed, double momentum,
+                           double clip, bool zero_grad);
 void sparse_decompress(const std::vector<torch::Tensor>& payloads, torch::Tensor out, bool add,
                        double post_scale);
 

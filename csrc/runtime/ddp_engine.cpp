@@ -1,5 +1,6 @@
 #include "ddp_engine.h"
 
+#include <algorithm>
 #include <cstring>
 #include <stdexcept>
 
@@ -122,13 +123,27 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
 
   const int nw = cfg.num_workers < 1 ? 1 : cfg.num_workers;
   workers_.resize(static_cast<size_t>(nw));
+  // per worker: min/max reduction state (first 16 KB, second region at 128 KB for the sharded
+  // exchange's owner phase); the sparse codecs' state, sample keys and candidate pool behind it
+  size_t scratch_bytes = kScratchBytes;
+  if (cfg.codec == Codec::kSparse) {
+    size_t need = 0;
+    for (auto& b : buckets) need = std::max(need, cuda::sparse_scratch_bytes(b.numel));
+    scratch_bytes = std::max(scratch_bytes, size_t(16384) + need);
+    if (cfg.trace) {
+      check(cudaHostAlloc(reinterpret_cast<void**>(&sparse_stats_host_), buckets.size() * 4 * sizeof(unsigned int),
+                          cudaHostAllocDefault),
+            "cudaHostAlloc stats");
+      std::memset(sparse_stats_host_, 0, buckets.size() * 4 * sizeof(unsigned int));
+    }
+  }
   int lo = 0, hi = 0;
   check(cudaDeviceGetStreamPriorityRange(&lo, &hi), "priority range");
   for (auto& w : workers_) {
     check(cudaStreamCreateWithPriority(&w.push, cudaStreamNonBlocking, hi), "stream");
     check(cudaStreamCreateWithPriority(&w.recv, cudaStreamNonBlocking, hi), "stream");
-    check(cudaMalloc(&w.scratch, kScratchBytes), "cudaMalloc scratch");
-    check(cudaMemset(w.scratch, 0, kScratchBytes), "memset scratch");
+    check(cudaMalloc(&w.scratch, scratch_bytes), "cudaMalloc scratch");
+    check(cudaMemset(w.scratch, 0, scratch_bytes), "memset scratch");
     check(cudaMalloc(reinterpret_cast<void**>(&w.done), 64), "cudaMalloc counter");
     check(cudaMemset(w.done, 0, 64), "memset counter");
     check(cudaEventCreateWithFlags(&w.tail, cudaEventDisableTiming), "event");
@@ -164,6 +179,7 @@ DdpEngine::~DdpEngine() {
   if (epoch_dev_) cudaFree(epoch_dev_);
   if (residual2_) cudaFree(residual2_);
   if (wait_ns_) cudaFree(wait_ns_);
+  if (sparse_stats_host_) cudaFreeHost(sparse_stats_host_);
   if (stamps_) cudaFree(stamps_);
 }
 
@@ -576,27 +592,35 @@ void DdpEngine::issue_push(int b, int worker) {
       break;
     case Codec::kSparse: {
       if (!res) throw std::runtime_error("sparse codecs need a residual buffer");
-      int accumulate = cfg_.sparse_accumulate;
-      float* sumsq = reinterpret_cast<float*>(static_cast<uint8_t*>(w.scratch) + 12288);
+      // one fused pipeline: the codec's state update (GradDrop's R += G, or DGC's momentum
+      // correction with clipping and factor masking) happens inside the compressor's single pass
+      // over the bucket, which also leaves zeros in the gradient: the dense gradient is rebuilt
+      // from the payloads by the receive half
+      cuda::SparseFuse fuse;
+      fuse.zero_grad = 1;
       if (cfg_.momentum_correction) {
         if (!aux_) throw std::runtime_error("momentum correction needs the velocity buffer");
-        check(cuda::dgc_accumulate(g, aux_ + B.offset, res, n, cfg_.dgc_momentum, cfg_.dgc_clip, sumsq,
-                                   w.push),
-              "dgc_accumulate");
-        launched += cfg_.dgc_clip > 0.f ? 2 : 1;
-        accumulate = 0;  // v already holds the accumulated velocity
+        fuse.mode = 2;
+        fuse.grad = g;
+        fuse.u = aux_ + B.offset;
+        fuse.momentum = cfg_.dgc_momentum;
+        fuse.clip = cfg_.dgc_clip;
+        fuse.sumsq = reinterpret_cast<float*>(static_cast<uint8_t*>(w.scratch) + 12288);
+      } else if (cfg_.sparse_accumulate) {
+        fuse.mode = 1;
+        fuse.grad = g;
+      } else {
+        // plain DGC selects from the caller's accumulator; the gradient itself is not an input
+        fuse.mode = 0;
+        check(cudaMemsetAsync(g, 0, size_t(n) * 4, w.push), "clear grad");
       }
-      check(cuda::sparse_compress(accumulate ? g : nullptr, res, n, cfg_.sample_rate, keep_fraction_,
-                                  seed, accumulate, dst, static_cast<uint8_t*>(w.scratch) + 16384,
-                                  w.push),
+      void* sparse_scratch = static_cast<uint8_t*>(w.scratch) + 16384;
+      check(cuda::sparse_compress_fused(fuse, res, n, cfg_.sample_rate, keep_fraction_, seed, dst, sparse_scratch,
+                                        w.push),
             "sparse_compress");
-      launched += 9;
-      if (cfg_.momentum_correction) {
-        check(cuda::dgc_mask(dst.payload[cfg_.rank], L.slot_bytes - L.shift, aux_ + B.offset, n, sumsq,
-                             w.push, dst.epoch_dev, dst.parity_stride),
-              "dgc_mask");
-        launched += 1;
-      }
+      launched += 6 + (fuse.mode == 2 && fuse.clip > 0.f ? 1 : 0);
+      if (sparse_stats_host_)
+        check(cuda::sparse_read_stats(sparse_scratch, sparse_stats_host_ + 4 * b, w.push), "sparse stats");
       break;
     }
     case Codec::kEcq:
@@ -656,7 +680,8 @@ void DdpEngine::issue_recv(int b, int worker) {
       launched += 1;
       break;
     case Codec::kSparse:
-      check(cuda::sparse_unpack_accum(src, g, n, 0, post, status_, w.recv), "sparse_unpack");
+      // the compressor left zeros in the bucket: the payloads are added onto them
+      check(cuda::sparse_unpack_accum(src, g, n, 1, post, status_, w.recv), "sparse_unpack");
       launched += cfg_.world;
       break;
     case Codec::kEcq:
@@ -743,6 +768,14 @@ std::vector<unsigned long long> DdpEngine::wait_stats() {
   check(cudaMemcpy(host.data(), wait_ns_, 3 * sizeof(unsigned long long), cudaMemcpyDeviceToHost), "read wait stats");
   check(cudaMemset(wait_ns_, 0, 64), "reset wait stats");
   return host;
+}
+
+std::vector<unsigned int> DdpEngine::sparse_stats() {
+  std::vector<unsigned int> out;
+  if (!sparse_stats_host_) return out;
+  check(cudaDeviceSynchronize(), "sync");
+  out.assign(sparse_stats_host_, sparse_stats_host_ + buckets_.size() * 4);
+  return out;
 }
 
 std::vector<int64_t> DdpEngine::stage_times() {

@@ -167,6 +167,10 @@ class DdpEngine {
   // step's begin: per bucket {ready, pushed, arrived, done}, then {step end}.  Zero where a stage
   // did not run.  Synchronises the device.
   std::vector<int64_t> stage_times();
+  // With EngineConfig::trace and a sparse codec: per bucket {elements sent, candidates over the
+  // sampled threshold, threshold (bit pattern of a float), candidates dropped so far} of the
+  // last step.  Synchronises the device.
+  std::vector<unsigned int> sparse_stats();
   uint32_t epoch() const { return epoch_; }
   int64_t steps() const { return steps_; }
   // kernels launched by the engine since construction
@@ -222,6 +226,7 @@ class DdpEngine {
   int64_t residual2_elems_ = 0;
   unsigned long long* wait_ns_ = nullptr;  // device: {total, max, count} of the flag waits
   unsigned long long* stamps_ = nullptr;   // device: [buckets][kStampCount] + {begin, end}; trace only
+  unsigned int* sparse_stats_host_ = nullptr;  // pinned: [buckets][4]; trace + sparse codec only
   std::vector<int64_t> residual2_off_;
   int64_t launches_at_begin_ = 0;
   std::vector<std::atomic<int>> pending_params_;

@@ -131,6 +131,21 @@ def dgc_compress(values: torch.Tensor, sample_rate: float, keep_fraction: float,
     return out
 
 
+def dgc_momentum_compress(grad: torch.Tensor, u: torch.Tensor, v: torch.Tensor, sample_rate: float,
+                          keep_fraction: float, seed: int = 0, momentum: float = 0.9, clip: float = 0.0,
+                          zero_grad: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """DGC with momentum correction as one fused pipeline (CUDA tensors): ``u = momentum*u + s*grad``,
+    ``v += u``, sampled-threshold top-k of ``v`` into the payload, ``u`` and ``v`` cleared at the
+    sent positions (momentum factor masking).  ``s = min(1, clip / |grad|)`` when ``clip > 0``.
+    For keep fractions up to 1 % the three tensors are read once.  (Momentum correction, clipping
+    and masking are not in the reference, whose dgc_body.h is the selector alone.)"""
+    if out is None:
+        out = _u8(sparse_payload_bytes(v.numel(), keep_fraction), v)
+    _C.dgc_momentum_compress(grad.reshape(-1), u.reshape(-1), v.reshape(-1), out, float(sample_rate),
+                             float(keep_fraction), int(seed), float(momentum), float(clip), bool(zero_grad))
+    return out
+
+
 def sparse_decompress(payloads, out: torch.Tensor, add: bool = False,
                       post_scale: float = 1.0) -> torch.Tensor:
     """Scatter payload(s) into ``out`` (ref gd_body.h:283-353); ``add=False`` zero-fills first."""

@@ -367,7 +367,9 @@ class CompressedDataParallel(nn.Module):
         microseconds from the step's begin to each bucket's {gradients ready, payload pushed, all
         payloads arrived, update applied}, ``step_us`` the step's length and ``exposed_tail_us``
         the time between the last bucket's gradients being ready (the end of backward) and the
-        last update being applied.  Synchronises the device."""
+        last update being applied; with a sparse codec also what the last step selected:
+        ``selected_k`` elements out of ``candidates`` over the sampled ``thresholds`` (one per
+        bucket) and the bytes that put on the wire.  Synchronises the device."""
         dense = self.engine.dense_bytes_per_step
         wire = self.engine.wire_bytes_per_step
         total_ns, max_ns, waits = self.engine.wait_stats()
@@ -385,4 +387,15 @@ class CompressedDataParallel(nn.Module):
             out["step_us"] = times[4 * nb] / 1e3
             last_ready = max(s["ready"] for s in stages)
             out["exposed_tail_us"] = max(s["done"] for s in stages) - last_ready
+        sparse = self.engine.sparse_stats()
+        if sparse:
+            import struct
+            nb = len(self.plan.buckets)
+            ks = [int(sparse[4 * b]) for b in range(nb)]
+            out["selected_k"] = sum(ks)
+            out["candidates"] = sum(int(sparse[4 * b + 1]) for b in range(nb))
+            out["thresholds"] = [struct.unpack("<f", struct.pack("<I", int(sparse[4 * b + 2])))[0] for b in range(nb)]
+            out["dropped_candidates"] = max(int(sparse[4 * b + 3]) for b in range(nb))
+            # what this rank actually put on the wire in the last step (capacity is in wire_bytes_per_step)
+            out["wire_bytes_last_step"] = sum(4 + 8 * k for k in ks) * max(1, self.world - 1)
         return out

@@ -148,6 +148,47 @@ def test_sparse_compress_matches_cpu(n, keep, rate, accumulate):
         assert torch.equal(rg.cpu(), rc)
 
 
+@pytest.mark.parametrize("keep,rate", [(0.001, 0.01), (0.01, 0.02)])
+def test_sparse_clustered_values_match_cpu(keep, rate):
+    """All the large values sit in a few short index ranges (one layer with large gradients):
+    the lists of the warps that own those ranges grow over many pool blocks."""
+    n = (1 << 21) + 77
+    r = gauss(n, 1e-4, seed=3)
+    big = gauss(n, 1.0, seed=4)
+    for lo in (1000, 700000, n - 6000):
+        r[lo:lo + 5000] = big[lo:lo + 5000]
+    for seed in (1, 2):
+        rc, rg = r.clone(), dev(r)
+        ref = ops.dgc_compress(rc, rate, keep, seed)
+        out = ops.dgc_compress(rg, rate, keep, seed)
+        total, k = _parse(ref)
+        assert k > 0
+        assert torch.equal(out[:total].cpu(), ref[:total]), f"seed {seed} k {k}"
+        assert torch.equal(rg.cpu(), rc)
+
+
+@pytest.mark.parametrize("n,keep,rate", [(300000 + 3, 0.001, 0.01), (1 << 20, 0.01, 0.01), (70000, 0.05, 0.1)])
+def test_dgc_momentum_fused_matches_restatement(n, keep, rate):
+    """u = m*u + g, v += u, select from v, mask u and v: the fused pipeline against the same steps
+    spelled out with tensor ops and the CPU selector (momentum 0.5 keeps the products exact, so the
+    restatement rounds like the kernel's fused multiply-add)."""
+    g, u, v = gauss(n, seed=1), gauss(n, 0.02, seed=2), gauss(n, 0.03, seed=3)
+    for seed in (5, 6):
+        cu = 0.5 * u + g
+        cv = v + cu
+        ref = ops.dgc_compress(cv, rate, keep, seed)        # zeroes the selected entries of cv
+        total, k = _parse(ref)
+        idx = ref[4:4 + 4 * k].view(torch.int32).long()
+        cu[idx] = 0.0
+        dg, du, dv = dev(g), dev(u), dev(v)
+        out = ops.dgc_momentum_compress(dg, du, dv, rate, keep, seed, momentum=0.5, zero_grad=True)
+        assert torch.equal(out[:total].cpu(), ref[:total]), f"seed {seed} k {k}"
+        assert torch.equal(dv.cpu(), cv) and torch.equal(du.cpu(), cu)
+        assert float(dg.abs().max()) == 0.0
+        u, v = cu, cv
+        g = gauss(n, seed=10 + seed)
+
+
 def test_sparse_ties_and_trim_on_gpu():
     v = torch.tensor([1.0, -1.0, 1.0, 0.5, 1.0, -1.0, 0.25, 1.0] * 300)
     ref_v, dev_v = v.clone(), dev(v)
