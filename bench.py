@@ -121,7 +121,8 @@ class OurTrainer:
         self.error_feedback = True
         if self.algorithm == "powersgd":
             from hipress_b200.parallel.powersgd import PowerSGDDataParallel
-            self.model = PowerSGDDataParallel(net, rank_r=4, lr=self.lr, momentum=0.9)
+            self.model = PowerSGDDataParallel(net, rank_r=4, lr=self.lr, momentum=0.9,
+                                              graph_capturable=bool(args.cuda_graph))
         elif self.algorithm == "dgc":
             from hipress_b200.parallel.dgc import DGCDataParallel
             # measured in the steady state: the 400-step sparsity warm-up is skipped, not shortened
@@ -135,7 +136,7 @@ class OurTrainer:
                                           optimizer="adamw" if args.model == "bert_large" else "sgd",
                                           weight_decay=0.01 if args.model == "bert_large" else 0.0)
         else:
-            whole = bool(args.cuda_graph) and self.algorithm in ("tbq", "terngrad", "graddrop", "ecq")
+            whole = bool(args.cuda_graph)
             adamw = args.model == "bert_large"
             cfg = CompressionConfig(self.algorithm, bitwidth=2, enable_random=True, error_feedback=True,
                                     threshold=2e-3, keep_fraction=0.001, sample_rate=0.01, bucket_mb=self.bucket_mb,

@@ -15,6 +15,9 @@ rank are synchronised (sum / W on every rank) by
   owners followed by a compressed all-gather of the re-quantised averages (``--codecs ... tbq_sharded``),
 * ``tbq_auto`` / ``terngrad_auto``  whichever of the two forms the library's size rule picks
   (``hipress_b200.parallel.prefer_sharded``),
+* any of these with ``_nvls`` appended (``terngrad_nvls``, ``tbq_sharded_nvls``): payloads delivered
+  with one NVLS multicast store per packed word instead of one store per destination, where the
+  host exposes multicast (the row says so when it does not),
 
 each as ONE fused pipeline per step: compress kernels that store the packed payload straight
 into every peer's receive slot over NVLink, a bounded flag wait, and a one-pass unpack +
@@ -155,15 +158,24 @@ def main():
                 nccl_ms = ms
                 launches = None
             else:
-                base = codec.rsplit("_", 1)[0] if codec.endswith(("_sharded", "_auto")) else codec
-                sharded = codec.endswith("_sharded") or (codec.endswith("_auto") and prefer_sharded(n * 4, world))
-                graphable = bool(args.graph) and base != "dense"
+                base, *flags = codec.split("_")       # e.g. terngrad_sharded_nvls
+                sharded = "sharded" in flags or ("auto" in flags and prefer_sharded(n * 4, world))
+                nvls = "nvls" in flags
+                graphable = bool(args.graph)
                 cfg = dict(rank=rank, world=world, device=local, codec=base,
                            threshold=2e-3, bitwidth=2, enable_random=1, error_feedback=1, keep_fraction=0.001,
                            sample_rate=0.01, seed=1, sharded=1 if sharded else 0,
-                           device_epoch=1 if graphable else 0, num_workers=0 if (graphable or sharded) else 1)
+                           device_epoch=1 if graphable else 0, num_workers=0 if (graphable or sharded) else 1,
+                           nvls=1 if nvls else 0)
                 eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
-                sym = SymmetricMemory(eng.symmetric_bytes, dev)
+                sym = SymmetricMemory(eng.symmetric_bytes, dev, multicast=nvls)
+                if nvls and not sym.multicast:
+                    if rank == 0:
+                        print(json.dumps({"codec": codec, "world": world, "buffer_mb": mb,
+                                          "unavailable": "no NVLS multicast mapping: " + getattr(sym, "multicast_note", "")}),
+                              flush=True)
+                    del eng, sym
+                    continue
                 resid = torch.zeros(n, device=dev)
                 eng.set_buffers(grad, resid, None, None)
                 eng.set_symmetric(sym.buf)
@@ -202,6 +214,7 @@ def main():
             if codec != "nccl":
                 model = (base + "_sharded") if sharded else base
                 row["form"] = "sharded" if sharded else "all-gather"
+                row["transport"] = "nvls" if nvls else "p2p"
                 t_hbm = hbm_bytes_per_elem(model, world) * n / (hbm * 1e9)
                 t_link = wire_bytes(model, n, world) / (NVLINK_GBS * 1e9)
                 roof = max(t_hbm, t_link)

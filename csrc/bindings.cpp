@@ -80,6 +80,7 @@ runtime::EngineConfig config_from(const py::dict& d) {
   c.device_epoch = get("device_epoch", 0);
   c.sharded = get("sharded", 0);
   c.trace = get("trace", 0);
+  c.nvls = get("nvls", 0);
   c.momentum_correction = get("momentum_correction", 0);
   c.dgc_momentum = get("dgc_momentum", 0.9f);
   c.dgc_clip = get("dgc_clip", 0.0f);
@@ -291,6 +292,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
              return std::make_unique<comm::SymmetricBuffer>(size_t(bytes), rank, world);
            }),
            py::arg("bytes"), py::arg("rank"), py::arg("world"), py::arg("device"))
+      .def(py::init([](const std::vector<uint64_t>& bases, uint64_t multicast, int64_t bytes, int rank, int world) {
+             return std::make_unique<comm::SymmetricBuffer>(bases, multicast, size_t(bytes), rank, world);
+           }),
+           py::arg("bases"), py::arg("multicast"), py::arg("bytes"), py::arg("rank"), py::arg("world"))
+      .def_property_readonly("multicast",
+                             [](comm::SymmetricBuffer& b) { return uint64_t(reinterpret_cast<uintptr_t>(b.multicast())); })
       .def("export_handle", [](comm::SymmetricBuffer& b) { return py::bytes(b.export_handle()); })
       .def("open_peers",
            [](comm::SymmetricBuffer& b, const std::vector<py::bytes>& handles) {
@@ -308,24 +315,42 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def_property_readonly("connected", &comm::SymmetricBuffer::connected);
 
   // flag protocol for protocols orchestrated from Python (PowerSGD factors)
+  m.def("bump_epoch",
+        [](torch::Tensor epoch_dev) {
+          TORCH_CHECK(epoch_dev.is_cuda() && epoch_dev.element_size() == 4 && epoch_dev.numel() >= 1,
+                      "epoch_dev must be a 32-bit CUDA tensor");
+          c10::cuda::CUDAGuard guard(epoch_dev.device());
+          cudaError_t e = cuda::bump_epoch(static_cast<uint32_t*>(epoch_dev.data_ptr()), current_stream(epoch_dev.get_device()));
+          TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
+        },
+        "epoch_dev[0] += 1 on the current stream: first kernel of a step whose epoch lives on the device");
   m.def("signal_flags",
-        [](comm::SymmetricBuffer& buf, int64_t flag_offset, uint32_t epoch, int device) {
+        [](comm::SymmetricBuffer& buf, int64_t flag_offset, uint32_t epoch, int device,
+           c10::optional<torch::Tensor> epoch_dev) {
           cuda::PushTargets t;
           t.world = buf.world();
           t.epoch = epoch;
+          if (epoch_dev.has_value() && epoch_dev->defined())
+            t.epoch_dev = static_cast<const uint32_t*>(epoch_dev->data_ptr());
           for (int p = 0; p < buf.world(); ++p)
             t.flag[p] = reinterpret_cast<uint32_t*>(buf.base(p) + flag_offset) + buf.rank();
           cudaError_t e = cuda::signal_flags(t, current_stream(device));
           TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
-        });
+        },
+        py::arg("buffer"), py::arg("flag_offset"), py::arg("epoch"), py::arg("device"),
+        py::arg("epoch_dev") = py::none());
   m.def("wait_flags",
         [](comm::SymmetricBuffer& buf, int64_t flag_offset, uint32_t epoch, double timeout_s,
-           const torch::Tensor& like) {
+           const torch::Tensor& like, c10::optional<torch::Tensor> epoch_dev) {
+          const uint32_t* ed = (epoch_dev.has_value() && epoch_dev->defined())
+                                   ? static_cast<const uint32_t*>(epoch_dev->data_ptr()) : nullptr;
           cudaError_t e = cuda::wait_flags(reinterpret_cast<const uint32_t*>(buf.local() + flag_offset),
                                            buf.world(), epoch, uint64_t(timeout_s * 1e9),
-                                           ops::status_word_for(like), current_stream(like.get_device()));
+                                           ops::status_word_for(like), current_stream(like.get_device()), ed);
           TORCH_CHECK(e == cudaSuccess, cudaGetErrorString(e));
-        });
+        },
+        py::arg("buffer"), py::arg("flag_offset"), py::arg("epoch"), py::arg("timeout_s"), py::arg("like"),
+        py::arg("epoch_dev") = py::none());
 
   // ---------------------------------------------------------------- PowerSGD step driver
   py::class_<runtime::PsgdEngine>(m, "PsgdEngine")
@@ -437,7 +462,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
            [](runtime::DdpEngine& e, comm::SymmetricBuffer& buf) {
              std::vector<uint8_t*> bases;
              for (int r = 0; r < buf.world(); ++r) bases.push_back(buf.base(r));
-             e.set_symmetric(bases);
+             e.set_symmetric(bases, buf.multicast());
            })
       .def("set_sgd", &runtime::DdpEngine::set_sgd, py::arg("lr"), py::arg("momentum"),
            py::arg("weight_decay"), py::arg("fused"))

@@ -26,7 +26,21 @@ SymmetricBuffer::SymmetricBuffer(size_t bytes, int rank, int world)
   if (world == 1) connected_ = true;
 }
 
+SymmetricBuffer::SymmetricBuffer(const std::vector<uint64_t>& bases, uint64_t multicast, size_t bytes, int rank,
+                                 int world)
+    : bytes_(bytes), rank_(rank), world_(world), connected_(true), owned_(false),
+      multicast_(reinterpret_cast<uint8_t*>(multicast)), ptr_(static_cast<size_t>(world), nullptr),
+      opened_(static_cast<size_t>(world), false) {
+  if (world < 1 || rank < 0 || rank >= world || static_cast<int>(bases.size()) != world)
+    throw std::invalid_argument("bad rank/world or base pointer count");
+  for (int r = 0; r < world; ++r) {
+    if (bases[static_cast<size_t>(r)] == 0) throw std::invalid_argument("null base pointer");
+    ptr_[static_cast<size_t>(r)] = reinterpret_cast<uint8_t*>(bases[static_cast<size_t>(r)]);
+  }
+}
+
 SymmetricBuffer::~SymmetricBuffer() {
+  if (!owned_) return;
   for (int r = 0; r < world_; ++r)
     if (opened_[static_cast<size_t>(r)]) cudaIpcCloseMemHandle(ptr_[static_cast<size_t>(r)]);
   if (ptr_[static_cast<size_t>(rank_)]) cudaFree(ptr_[static_cast<size_t>(rank_)]);

@@ -20,6 +20,10 @@ class SymmetricBuffer {
  public:
   // Allocates and zero-fills `bytes` on the current device.
   SymmetricBuffer(size_t bytes, int rank, int world);
+  // Adopts memory that somebody else allocated, mapped and owns: bases[r] is rank r's buffer as
+  // mapped in this process, multicast an address whose stores reach the same offset of every
+  // rank's buffer through the NVLink switch (0 when there is none).  Nothing is freed here.
+  SymmetricBuffer(const std::vector<uint64_t>& bases, uint64_t multicast, size_t bytes, int rank, int world);
   ~SymmetricBuffer();
   SymmetricBuffer(const SymmetricBuffer&) = delete;
   SymmetricBuffer& operator=(const SymmetricBuffer&) = delete;
@@ -34,6 +38,8 @@ class SymmetricBuffer {
 
   uint8_t* base(int r) const { return ptr_.at(static_cast<size_t>(r)); }
   uint8_t* local() const { return ptr_.at(static_cast<size_t>(rank_)); }
+  // NVLS multicast mapping of the buffer, or null.
+  uint8_t* multicast() const { return multicast_; }
   size_t bytes() const { return bytes_; }
   int rank() const { return rank_; }
   int world() const { return world_; }
@@ -43,6 +49,8 @@ class SymmetricBuffer {
   size_t bytes_;
   int rank_, world_;
   bool connected_ = false;
+  bool owned_ = true;
+  uint8_t* multicast_ = nullptr;
   std::vector<uint8_t*> ptr_;
   std::vector<bool> opened_;
 };

@@ -49,6 +49,10 @@ struct PushTargets {
   // Device status word: when set and non-zero on entry (an earlier wait of this step timed out
   // or a payload was malformed) the kernel returns without storing or publishing anything.
   const int* guard = nullptr;
+  // NVLS: multicast address of the payload (the same offset of every destination's buffer).
+  // When set, aligned 4- and 16-byte payload stores are issued once with multimem.st instead of
+  // once per destination; smaller stores and the flags stay unicast.
+  uint8_t* mc = nullptr;
 };
 constexpr uint64_t kEpochSeedStride = 0x9E3779B97F4A7C15ull;
 constexpr uint64_t kShardSeedStride = 0xD6E8FEB86659FD93ull;
@@ -165,6 +169,11 @@ cudaError_t sparse_read_stats(const void* scratch, unsigned int* host4, cudaStre
 cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,
                                 float post_scale, int* status, cudaStream_t stream);
 
+// out[idx] = 0 for every index of every payload (one launch): after the optimizer has consumed a
+// dense gradient that only held scattered payload entries, this leaves it all zero again
+// without a pass over the whole buffer.
+cudaError_t sparse_clear(const UnpackSources& src, float* out, int64_t n, cudaStream_t stream);
+
 // ---------------------------------------------------------------- flags
 // Spins (one warp) until flag[r] >= epoch for all r < world, or timeout_ns
 // passes; on timeout writes kFlagTimeout to *status and returns normally.
@@ -190,8 +199,15 @@ cudaError_t sgd_apply_dense(float* grad, float scale, const SgdApply& apply, int
 cudaError_t add_into(const float* a, const float* b, float* out, int64_t n, cudaStream_t stream);
 // Sum of W dense fp32 buffers (peer pointers) into out: the P2P dense
 // all-reduce used for small PowerSGD factors and 1-D parameters.
+// With epoch_dev the sources are the slots of even epochs; odd epochs read parity_elems floats
+// further.  guard: see UnpackSources::guard.
 cudaError_t dense_gather_sum(const float* const* srcs, int world, float* out, int64_t n,
-                             float post_scale, cudaStream_t stream);
+                             float post_scale, cudaStream_t stream, const uint32_t* epoch_dev = nullptr,
+                             int64_t parity_elems = 0, const int* guard = nullptr);
+// slot_even + (epoch odd ? parity_elems : 0) = src: staging copy of the dense codec when the
+// step's epoch lives on the device (a captured step cannot change a copy's destination).
+cudaError_t dense_stage(const float* src, float* slot_even, int64_t parity_elems, const uint32_t* epoch_dev,
+                        int64_t n, cudaStream_t stream);
 
 // ---------------------------------------------------------------- DGC / AdamW
 // Momentum correction: u = momentum*u + s*grad; v += u, where s clips the

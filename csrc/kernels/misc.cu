@@ -105,14 +105,30 @@ struct SrcTable {
   const float* p[kMaxWorld];
 };
 
+// epoch_dev: when set, the sources given are the slots of even epochs and odd epochs read
+// parity_elems floats further (slots are double-buffered by epoch parity, see PushTargets).
 __global__ void __launch_bounds__(kThreads)
-gather_sum_kernel(SrcTable srcs, int world, float* __restrict__ out, int64_t n, float post_scale) {
+gather_sum_kernel(SrcTable srcs, int world, float* __restrict__ out, int64_t n, float post_scale,
+                  const uint32_t* epoch_dev, int64_t parity_elems, const int* guard) {
+  if (status_guarded(guard)) return;
+  const int64_t shift = (epoch_dev != nullptr && (*epoch_dev & 1u)) ? parity_elems : 0;
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
   for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
-    float acc = srcs.p[0][i];
-    for (int r = 1; r < world; ++r) acc += srcs.p[r][i];
+    float acc = srcs.p[0][shift + i];
+#pragma unroll
+    for (int r = 1; r < kMaxWorld; ++r)
+      if (r < world) acc += srcs.p[r][shift + i];
     out[i] = acc * post_scale;
   }
+}
+
+// slot(parity of *epoch_dev) = src: the dense codec's staging copy when the epoch lives on the device.
+__global__ void __launch_bounds__(kThreads)
+dense_stage_kernel(const float* __restrict__ src, float* __restrict__ slot_even, int64_t parity_elems,
+                   const uint32_t* epoch_dev, int64_t n) {
+  float* dst = slot_even + ((*epoch_dev & 1u) ? parity_elems : 0);
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) dst[i] = src[i];
 }
 
 inline int grid_for(int64_t items, int max_blocks) {
@@ -171,11 +187,20 @@ cudaError_t add_into(const float* a, const float* b, float* out, int64_t n, cuda
 }
 
 cudaError_t dense_gather_sum(const float* const* srcs, int world, float* out, int64_t n,
-                             float post_scale, cudaStream_t stream) {
+                             float post_scale, cudaStream_t stream, const uint32_t* epoch_dev,
+                             int64_t parity_elems, const int* guard) {
   if (n <= 0 || world < 1 || world > kMaxWorld) return cudaErrorInvalidValue;
   SrcTable t{};
   for (int r = 0; r < world; ++r) t.p[r] = srcs[r];
-  gather_sum_kernel<<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(t, world, out, n, post_scale);
+  gather_sum_kernel<<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(t, world, out, n, post_scale, epoch_dev,
+                                                                   parity_elems, guard);
+  return cudaGetLastError();
+}
+
+cudaError_t dense_stage(const float* src, float* slot_even, int64_t parity_elems, const uint32_t* epoch_dev,
+                        int64_t n, cudaStream_t stream) {
+  if (n <= 0 || epoch_dev == nullptr) return cudaErrorInvalidValue;
+  dense_stage_kernel<<<grid_for(n, 148 * 8), kThreads, 0, stream>>>(src, slot_even, parity_elems, epoch_dev, n);
   return cudaGetLastError();
 }
 

@@ -52,8 +52,23 @@ __device__ __forceinline__ void resolve_epoch(UnpackSources& s) {
   s.parity_off = (*s.epoch_dev & 1u) ? s.parity_stride : 0;
 }
 
+// NVLS multicast stores: one store, delivered by the NVLink switch to the same offset of every
+// GPU bound to the multicast object (this GPU included).  Natural alignment required.
+__device__ __forceinline__ void multimem_st_u32(uint8_t* p, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void multimem_st_u128(uint8_t* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
 // The same 4 payload bytes to every destination.
 __device__ __forceinline__ void push_u32(const PushTargets& t, int64_t byte_off, uint32_t v) {
+  if (t.mc != nullptr && ((reinterpret_cast<uintptr_t>(t.mc) + t.parity_off + byte_off) & 3) == 0) {
+    multimem_st_u32(t.mc + t.parity_off + byte_off, v);
+    return;
+  }
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p)
     if (p < t.world) store_u32_any(t.payload[p] + t.parity_off + byte_off, v);
@@ -67,13 +82,17 @@ __device__ __forceinline__ void push_u8(const PushTargets& t, int64_t byte_off, 
 // (push_aligned16).  Peer stores of this width cross NVLink as full 128-byte+ runs per warp
 // instead of one 32-byte sector per warp and destination.
 __device__ __forceinline__ void push_u128(const PushTargets& t, int64_t byte_off, uint4 v) {
+  if (t.mc != nullptr) {   // same alignment as the destinations (push_aligned16 covers it)
+    multimem_st_u128(t.mc + t.parity_off + byte_off, v);
+    return;
+  }
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p)
     if (p < t.world) *reinterpret_cast<uint4*>(t.payload[p] + t.parity_off + byte_off) = v;
 }
 // True when payload + data_off is 16-byte aligned in every destination.
 __device__ __forceinline__ bool push_aligned16(const PushTargets& t, int64_t data_off) {
-  uintptr_t bits = 0;
+  uintptr_t bits = t.mc != nullptr ? reinterpret_cast<uintptr_t>(t.mc + t.parity_off + data_off) : 0;
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p)
     if (p < t.world) bits |= reinterpret_cast<uintptr_t>(t.payload[p] + t.parity_off + data_off);

@@ -22,6 +22,8 @@
 // expand / residual kernel (ref powersgd_body.h:69-75).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "kernels.h"
 #include "p2p.cuh"
 #include "unpack_lut.cuh"
@@ -33,20 +35,23 @@ namespace {
 
 constexpr int kBM = 128;     // accumulator rows per CTA (UMMA M)
 constexpr int kBN = 16;      // padded rank (UMMA N)
-constexpr int kBK = 32;      // fp32 elements along K per stage = 128 bytes
-constexpr int kStages = 6;
-constexpr int kStageA = kBM * kBK * 4;  // 16384
-constexpr int kStageB = kBN * kBK * 4;  // 2048
+constexpr int kBoxK = 32;    // fp32 elements along K of one TMA box = 128 bytes, the swizzle width
+constexpr int kKPad = 64;    // the K extent of the operands is padded to a multiple of this
 constexpr int kGemmThreads = 192;       // warp0 TMA, warp1 MMA, warps 2-5 epilogue
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every barrier wait gives up after 2 s
 constexpr int kTmemCols = 32;
 
+// BK: fp32 elements along K per pipeline stage (32 or 64: one or two 128-byte boxes per matrix
+// row, i.e. 128- or 256-byte runs in DRAM); STAGES: depth of the ring.
+template <int BK, int STAGES>
 struct GemmSmem {
+  static constexpr int kStageA = kBM * BK * 4;
+  static constexpr int kStageB = kBN * BK * 4;
   // 1024-byte aligned tiles first
-  uint8_t a[kStages][kStageA];
-  uint8_t b[kStages][kStageB];
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint8_t a[STAGES][kStageA];
+  uint8_t b[STAGES][kStageB];
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
   uint64_t accum;
   uint32_t tmem_base;
   int abort;
@@ -133,13 +138,16 @@ struct OwnerTargets {
 // MODE 0: out[n x r] += Mat * X,   A tile K-major  (rows of Mat x K along m)
 // MODE 1: out[m x r] += Mat^T * X, A tile MN-major (columns of Mat x K along n)
 // Xt is X transposed and zero-padded to [16][k_pad] (K-major B operand).
-template <int MODE>
+template <int MODE, int BK, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  int64_t out_rows, int r, int total_kb, int kb_per_split, OwnerTargets out,
                  int* status) {
+  using Smem = GemmSmem<BK, STAGES>;
+  constexpr int kBK = BK, kStages = STAGES, kStageA = Smem::kStageA, kStageB = Smem::kStageB;
+  constexpr int kBoxes = BK / kBoxK;   // 128-byte boxes along K per stage
   extern __shared__ uint8_t smem_raw[];
-  GemmSmem& s = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x;
   // Split-K with a contiguous K range per CTA.  (Dealing the K blocks round-robin, so that the
@@ -182,13 +190,18 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         mbar_expect_tx(&s.full[st], kStageA + kStageB);
         const int k0 = (kb_begin + i) * kBK;
         if (MODE == 0) {
-          tma_load_2d(s.a[st], &map_a, k0, tile * kBM, &s.full[st]);
+          // K-major A: one box of 128 rows x 128 bytes per 32 K elements, side by side in K
+#pragma unroll
+          for (int j = 0; j < kBoxes; ++j)
+            tma_load_2d(s.a[st] + j * (kBM * 128), &map_a, k0 + j * kBoxK, tile * kBM, &s.full[st]);
         } else {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             tma_load_2d(s.a[st] + j * (kBK * 128), &map_a, tile * kBM + j * 32, k0, &s.full[st]);
         }
-        tma_load_2d(s.b[st], &map_b, k0, 0, &s.full[st]);
+#pragma unroll
+        for (int j = 0; j < kBoxes; ++j)
+          tma_load_2d(s.b[st] + j * (kBN * 128), &map_b, k0 + j * kBoxK, 0, &s.full[st]);
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------- MMA issuer
@@ -211,9 +224,10 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // MN-major: swizzle atoms are 4 K-rows x 128 bytes (512 bytes apart,
           // SBO); the four 32-column groups of the tile are one TMA box apart
           // (LBO); one MMA consumes 8 K-rows = 1024 bytes.
-          const uint64_t da = MODE == 0 ? make_desc(a0 + k * 32, 16, 1024, 2)
+          // with two boxes per stage the K-major operands continue in the next box after four MMAs
+          const uint64_t da = MODE == 0 ? make_desc(a0 + (k / 4) * (kBM * 128) + (k % 4) * 32, 16, 1024, 2)
                                         : make_desc(a0 + k * 1024, kBK * 128, 512, 1);
-          const uint64_t db = make_desc(b0 + k * 32, 16, 1024, 2);
+          const uint64_t db = make_desc(b0 + (k / 4) * (kBN * 128) + (k % 4) * 32, 16, 1024, 2);
           umma_tf32(tmem, da, db, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(&s.empty[st]);  // frees the stage once the MMAs have read it
@@ -239,9 +253,24 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           int owner = int(row / out.rows_per_owner);
           if (owner >= out.world) owner = out.world - 1;
           float* dst = out.dst[owner] + row * r;
+          if (r == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            // one 16-byte reduction per row: a remote owner sees a quarter of the NVLink
+            // transactions of four scalar atomics
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(v[0])),
+                         "f"(__uint_as_float(v[1])), "f"(__uint_as_float(v[2])), "f"(__uint_as_float(v[3]))
+                         : "memory");
+          } else if ((r & 1) == 0 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
 #pragma unroll
-          for (int c = 0; c < 16; ++c)
-            if (c < r) atomicAdd(dst + c, __uint_as_float(v[c]));
+            for (int c = 0; c < 16; c += 2)
+              if (c < r)
+                asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(dst + c), "f"(__uint_as_float(v[c])),
+                             "f"(__uint_as_float(v[c + 1]))
+                             : "memory");
+          } else {
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              if (c < r) atomicAdd(dst + c, __uint_as_float(v[c]));
+          }
         }
       }
     }
@@ -524,6 +553,27 @@ bool make_map(CUtensorMap* map, const float* base, int64_t inner, int64_t outer,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Pipeline shape of the tensor-core GEMM.  The default was chosen by measurement (see the
+// kernel's profile); HIPRESS_PSGD_BK (32 | 64) and HIPRESS_PSGD_STAGES select another compiled
+// shape for experiments.
+struct GemmVariant {
+  int bk, stages;
+  size_t smem_bytes;
+};
+GemmVariant gemm_variant() {
+  static const GemmVariant v = [] {
+    int bk = 32, stages = 6;
+    if (const char* e = std::getenv("HIPRESS_PSGD_BK")) bk = std::atoi(e);
+    if (const char* e = std::getenv("HIPRESS_PSGD_STAGES")) stages = std::atoi(e);
+    if (bk == 32 && stages == 6) return GemmVariant{32, 6, sizeof(GemmSmem<32, 6>)};
+    if (bk == 32 && stages == 4) return GemmVariant{32, 4, sizeof(GemmSmem<32, 4>)};
+    if (bk == 64 && stages == 3) return GemmVariant{64, 3, sizeof(GemmSmem<64, 3>)};
+    if (bk == 64 && stages == 4) return GemmVariant{64, 4, sizeof(GemmSmem<64, 4>)};
+    return GemmVariant{64, 6, sizeof(GemmSmem<64, 6>)};
+  }();
+  return v;
+}
+
 OwnerTargets owners_of(const ReduceTargets& red, int64_t rows) {
   OwnerTargets o{};
   o.world = red.world;
@@ -535,7 +585,7 @@ OwnerTargets owners_of(const ReduceTargets& red, int64_t rows) {
 
 }  // namespace
 
-int64_t psgd_kpad(int64_t k) { return (k + kBK - 1) / kBK * kBK; }
+int64_t psgd_kpad(int64_t k) { return (k + kKPad - 1) / kKPad * kKPad; }
 
 bool psgd_tensor_core_eligible(const float* Mat, int64_t n, int64_t m) {
   return (reinterpret_cast<uintptr_t>(Mat) & 15) == 0 && (m % 4) == 0 && n >= 1 && m >= 1 &&
@@ -574,36 +624,50 @@ cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const fl
     return cudaGetLastError();
   }
   const int64_t k_pad = psgd_kpad(K);
+  const GemmVariant var = gemm_variant();
+  const int bk = var.bk;
   CUtensorMap map_a, map_b;
   const bool ok_a = mode == 0
-                        ? make_map(&map_a, Mat, m, n, kBK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)
-                        : make_map(&map_a, Mat, m, n, 32, kBK, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
-  const bool ok_b = make_map(&map_b, Xt, k_pad, kBN, kBK, kBN, CU_TENSOR_MAP_SWIZZLE_128B);
+                        ? make_map(&map_a, Mat, m, n, kBoxK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)
+                        : make_map(&map_a, Mat, m, n, 32, bk, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+  const bool ok_b = make_map(&map_b, Xt, k_pad, kBN, kBoxK, kBN, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok_a || !ok_b) return cudaErrorInvalidValue;
   const int tiles = int((out_rows + kBM - 1) / kBM);
-  const int total_kb = int(k_pad / kBK);
-  // Two CTAs fit on an SM (110 KB of shared memory each): aim for one full wave of
-  // 148 x 2 CTAs, never more, so that no partial second wave runs at half occupancy.
-  constexpr int kResident = 148 * 2;
-  int splits = kResident / tiles;
+  const int total_kb = int(k_pad / bk);
+  const size_t smem = var.smem_bytes + 1024;
+  // As many CTAs as fit on the SMs at once (by shared memory): aim for one full wave, never
+  // more, so that no partial second wave runs at low occupancy.
+  int per_sm = int((227 * 1024) / smem);
+  if (per_sm < 1) per_sm = 1;
+  if (per_sm > 4) per_sm = 4;
+  const int resident = 148 * per_sm;
+  int splits = resident / tiles;
   const int max_splits = total_kb / 4 > 0 ? total_kb / 4 : 1;
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
   int kbps = (total_kb + splits - 1) / splits;
   splits = (total_kb + kbps - 1) / kbps;
-  const size_t smem = sizeof(GemmSmem) + 1024;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[mode]) {
-    cudaError_t e = mode == 0 ? cudaFuncSetAttribute(psgd_gemm_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem))
-                              : cudaFuncSetAttribute(psgd_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    if (e != cudaSuccess) return e;
-    attr_set[mode] = true;
-  }
   const dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(splits), 1);
-  if (mode == 0)
-    psgd_gemm_kernel<0><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, out_rows, r, total_kb, kbps, out, status);
-  else
-    psgd_gemm_kernel<1><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, out_rows, r, total_kb, kbps, out, status);
+#define HP_GEMM(MODE, BK, ST)                                                                                        \
+  do {                                                                                                               \
+    cudaError_t e = cudaFuncSetAttribute(psgd_gemm_kernel<MODE, BK, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                         int(smem));                                                                 \
+    if (e != cudaSuccess) return e;                                                                                  \
+    psgd_gemm_kernel<MODE, BK, ST><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, out_rows, r, total_kb, kbps,  \
+                                                                         out, status);                               \
+  } while (0)
+#define HP_GEMM_MODE(BK, ST)      \
+  do {                            \
+    if (mode == 0) HP_GEMM(0, BK, ST); \
+    else HP_GEMM(1, BK, ST);      \
+  } while (0)
+  if (var.bk == 32 && var.stages == 6) HP_GEMM_MODE(32, 6);
+  else if (var.bk == 32 && var.stages == 4) HP_GEMM_MODE(32, 4);
+  else if (var.bk == 64 && var.stages == 3) HP_GEMM_MODE(64, 3);
+  else if (var.bk == 64 && var.stages == 4) HP_GEMM_MODE(64, 4);
+  else HP_GEMM_MODE(64, 6);
+#undef HP_GEMM_MODE
+#undef HP_GEMM
   return cudaGetLastError();
 }
 

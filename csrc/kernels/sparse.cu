@@ -34,9 +34,11 @@
 //               (index, value), to a per-warp list in index order.  A warp owns a contiguous
 //               part of its CTA's chunk, so the lists, taken in order, are sorted by index.
 //               Lists grow in blocks of 16 entries taken from a pool with one atomic.
-//   select      One CTA: exact cut among the candidates (radix select over the pool, 35 K
-//               entries for a 128 MB bucket at 0.1 %), kept counts per list, exclusive offsets,
-//               k, the header.
+//   cut         One CTA, only when more than ceil(N*keep) candidates qualified: their keys
+//               (35 K for a 128 MB bucket at 0.1 %) are gathered into shared memory with batched
+//               loads and the exact cut is found by a radix select there.
+//   count+scan  One warp per list counts what it keeps against the cut; the last CTA to finish
+//               turns the per-CTA totals into exclusive offsets, k and the header.
 //   emit        One warp per list: indices and values to every destination, residual (and
 //               DGC's momentum u) cleared at the emitted positions, then the completion flag.
 //
@@ -49,6 +51,7 @@
 #include "kernels.h"
 #include "p2p.cuh"
 
+#include <algorithm>
 #include <cmath>
 
 namespace hipress {
@@ -84,15 +87,11 @@ struct SparseScratch {
   unsigned int pool_used;               // blocks handed out (reset by select)
   unsigned int dropped;                 // candidates that found no block (cumulative)
   unsigned int last_cand;               // candidates seen by the last call (metrics)
+  unsigned int lists_done;              // CTA arrival counter of the count+scan kernel (left at zero)
   unsigned int list_head[kMaxLists];    // first block of each warp's list, kNoBlock when empty
-  unsigned int list_gt[kMaxLists], list_eq[kMaxLists];   // exclusive offsets per list
+  unsigned int list_gt[kMaxLists], list_eq[kMaxLists];   // kept counts per list (above / at the cut)
 };
 
-// One block of a candidate list: 16 (index, value bits) pairs.
-struct ListBlock {
-  unsigned int count, next, pad0, pad1;
-  uint2 entry[kBlockEntries];
-};
 
 __device__ __forceinline__ int digit_of(uint32_t key, int round) {
   return round == 0 ? int(key >> 21) : round == 1 ? int((key >> 10) & 0x7ffu) : int(key & 0x3ffu);
@@ -617,15 +616,19 @@ dgc_update_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n) {
 }
 
 // ================================================================ list form
-// Pool of list blocks, behind the sample keys in the scratch.
+// Pool of list blocks, behind the sample keys in the scratch: block b holds count[b] (index,
+// value bits) pairs in entry[b * 16 ..] and continues in block next[b].  Three flat arrays, so
+// that the cut kernel can sweep all entries with coalesced, independent loads.
 struct ListPool {
-  ListBlock* blocks;
+  unsigned int* count;
+  unsigned int* next;
+  uint2* entry;
   unsigned int capacity;  // blocks
 };
 
 // Cursor of a warp's list; only lane 0's copy is used.
 struct ListCursor {
-  unsigned int block = kNoBlock, fill = 0, lost = 0;
+  unsigned int block = kNoBlock, fill = 0, lost = 0, total = 0;
   bool exhausted = false;
 };
 
@@ -658,24 +661,30 @@ __device__ __forceinline__ void list_append(SparseScratch* s, const ListPool& po
           ++cur.lost;
           continue;
         }
-        pool.blocks[id].count = 0;
-        pool.blocks[id].next = kNoBlock;
+        pool.count[id] = 0;
+        pool.next[id] = kNoBlock;
         if (cur.block == kNoBlock) s->list_head[list] = id;
-        else pool.blocks[cur.block].next = id;
+        else pool.next[cur.block] = id;
         cur.block = id;
         cur.fill = 0;
       }
-      pool.blocks[cur.block].entry[cur.fill] = make_uint2(i, __float_as_uint(v));
-      pool.blocks[cur.block].count = ++cur.fill;
+      pool.entry[size_t(cur.block) * kBlockEntries + cur.fill] = make_uint2(i, __float_as_uint(v));
+      pool.count[cur.block] = ++cur.fill;
+      ++cur.total;
     }
   }
 }
 
 // ---- the one pass over the tensor
-__global__ void __launch_bounds__(kThreads)
+// MODE = fuse.mode as a template parameter (no registers for arrays a mode does not read); four
+// CTAs per SM, so that the whole grid of 4 x 148 CTAs is resident at once.
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 4)
 collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chunk, int64_t sample_cnt,
                SparseScratch* s, ListPool pool) {
+  fuse.mode = MODE;
   constexpr int kWarps = kThreads / 32;
+  constexpr int U = MODE == 2 ? 2 : 4;   // steps whose loads are issued together
   uint32_t thr_key = 0;
   if (sample_cnt > 0) {
     unsigned int bin, rin;
@@ -695,8 +704,8 @@ collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chu
   const int64_t wbegin = begin + warp * wlen < end ? begin + warp * wlen : end;
   const int64_t wend = wbegin + wlen < end ? wbegin + wlen : end;
   uintptr_t bits = reinterpret_cast<uintptr_t>(R);
-  if (fuse.mode >= 1) bits |= reinterpret_cast<uintptr_t>(fuse.grad);
-  if (fuse.mode == 2) bits |= reinterpret_cast<uintptr_t>(fuse.u);
+  if (MODE >= 1) bits |= reinterpret_cast<uintptr_t>(fuse.grad);
+  if (MODE == 2) bits |= reinterpret_cast<uintptr_t>(fuse.u);
   const bool vec_ok = (bits & 15) == 0 && (begin & 3) == 0;
   float* gw = const_cast<float*>(fuse.grad);   // mode 2 leaves zeros behind
 
@@ -706,13 +715,13 @@ collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chu
   // state update + candidate test of the 4 elements at e0 (e0 + 3 < wend, 16-byte aligned)
   auto step4 = [&](int64_t e0, float4 r4, float4 g4, float4 u4, uint32_t (&idx)[4], float (&val)[4]) -> unsigned int {
     float r[4] = {r4.x, r4.y, r4.z, r4.w};
-    if (fuse.mode == 1) {
+    if (MODE == 1) {
       const float g[4] = {g4.x, g4.y, g4.z, g4.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) r[j] = hp_add(g[j], r[j]);
       *reinterpret_cast<float4*>(R + e0) = make_float4(r[0], r[1], r[2], r[3]);
       if (fuse.zero_grad) *reinterpret_cast<float4*>(gw + e0) = make_float4(0.f, 0.f, 0.f, 0.f);
-    } else if (fuse.mode == 2) {
+    } else if (MODE == 2) {
       const float g[4] = {g4.x, g4.y, g4.z, g4.w};
       float u[4] = {u4.x, u4.y, u4.z, u4.w};
 #pragma unroll
@@ -743,21 +752,21 @@ collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chu
 
   int64_t base = wbegin;
   if (vec_ok) {
-    // four steps per iteration with their loads issued together
-    for (; base + 512 <= wend; base += 512) {
-      float4 r4[4], g4[4] = {}, u4[4] = {};
+    // U steps per iteration with their loads issued together
+    for (; base + U * 128 <= wend; base += U * 128) {
+      float4 r4[U], g4[MODE >= 1 ? U : 1] = {}, u4[MODE == 2 ? U : 1] = {};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < U; ++q) {
         const int64_t e0 = base + q * 128 + lane * 4;
         r4[q] = *reinterpret_cast<const float4*>(R + e0);
-        if (fuse.mode >= 1) g4[q] = *reinterpret_cast<const float4*>(fuse.grad + e0);
-        if (fuse.mode == 2) u4[q] = *reinterpret_cast<const float4*>(fuse.u + e0);
+        if (MODE >= 1) g4[MODE >= 1 ? q : 0] = __ldg(reinterpret_cast<const float4*>(fuse.grad + e0));
+        if (MODE == 2) u4[MODE == 2 ? q : 0] = *reinterpret_cast<const float4*>(fuse.u + e0);
       }
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < U; ++q) {
         uint32_t idx[4] = {0u, 0u, 0u, 0u};
         float val[4] = {0.f, 0.f, 0.f, 0.f};
-        const unsigned int count = step4(base + q * 128 + lane * 4, r4[q], g4[q], u4[q], idx, val);
+        const unsigned int count = step4(base + q * 128 + lane * 4, r4[q], g4[MODE >= 1 ? q : 0], u4[MODE == 2 ? q : 0], idx, val);
         if (__ballot_sync(0xffffffffu, count != 0) != 0) list_append(s, pool, list, lane, count, idx, val, cur);
       }
     }
@@ -772,11 +781,11 @@ collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chu
       const int64_t e = base + lane * 4 + j;
       if (e < wend) {
         float r = R[e];
-        if (fuse.mode == 1) {
+        if (MODE == 1) {
           r = hp_add(fuse.grad[e], r);
           R[e] = r;
           if (fuse.zero_grad) gw[e] = 0.f;
-        } else if (fuse.mode == 2) {
+        } else if (MODE == 2) {
           const float u = dgc_new_u(fuse.u[e], fuse.grad[e], fuse.momentum, scale);
           r = __fadd_rn(r, u);
           fuse.u[e] = u;
@@ -797,102 +806,236 @@ collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chu
     }
     if (__ballot_sync(0xffffffffu, count != 0) != 0) list_append(s, pool, list, lane, count, idx, val, cur);
   }
-  if (lane == 0 && cur.lost != 0) atomicAdd(&s->dropped, cur.lost);
+  if (lane == 0) {
+    if (cur.lost != 0) atomicAdd(&s->dropped, cur.lost);
+    if (cur.total != 0) atomicAdd(&s->cand, cur.total);
+  }
 }
 
-// ---- one CTA: exact cut among the candidates, offsets, k, header, housekeeping
-__global__ void __launch_bounds__(kThreads)
-select_kernel(int lists, unsigned int expected, PushTargets dst, SparseScratch* s, ListPool pool,
-              const float* sumsq_to_clear) {
-  resolve_epoch(dst);
+// ---- one CTA: the exact cut among the candidates, when there are more than wanted
+constexpr int kCutThreads = 1024;
+constexpr int kCutSmemKeys = 48 * 1024;   // keys held in shared memory (192 KB)
+
+// Block-wide over kCutThreads threads: the bin holding the element of 0-indexed `rank` counted
+// from the top bin down, and the rank inside that bin.  Every thread returns the same pair.
+__device__ void pick_from_top_1024(const unsigned int* hist, unsigned int rank, unsigned int& bin,
+                                   unsigned int& rank_in_bin, unsigned int* part /* [kCutThreads] */,
+                                   unsigned int* res /* [2] */) {
+  constexpr int PER = kBins / kCutThreads;  // 2 bins per thread
+  const int t = threadIdx.x;
+  unsigned int local[PER];
+  unsigned int sum = 0;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    local[j] = hist[kBins - 1 - (t * PER + j)];
+    sum += local[j];
+  }
+  // inclusive scan of the per-thread sums: warp scans, then a scan of the 32 warp totals
+  const int lane = t & 31, warp = t >> 5;
+  unsigned int inc = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned int a = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += a;
+  }
+  if (lane == 31) part[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    const unsigned int x = part[lane];
+    unsigned int sx = x;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned int a = __shfl_up_sync(0xffffffffu, sx, o);
+      if (lane >= o) sx += a;
+    }
+    part[lane] = sx - x;   // exclusive
+  }
+  __syncthreads();
+  const unsigned int before = part[warp] + inc - sum;
+  if (rank >= before && rank < before + sum) {
+    unsigned int run = before;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      if (rank >= run && rank < run + local[j]) {
+        res[0] = kBins - 1 - (t * PER + j);
+        res[1] = rank - run;
+      }
+      run += local[j];
+    }
+  }
+  __syncthreads();
+  bin = res[0];
+  rank_in_bin = res[1];
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(kCutThreads)
+cut_kernel(unsigned int expected, SparseScratch* s, ListPool pool) {
+  extern __shared__ uint32_t keys[];   // kCutSmemKeys
   __shared__ unsigned int sh[kBins];
-  __shared__ unsigned int part_gt[kThreads], part_eq[kThreads];
-  __shared__ unsigned int total_sh;
+  __shared__ unsigned int part[kCutThreads];
+  __shared__ unsigned int res[2];
+  __shared__ unsigned int nkeys;
+  const unsigned int cand = s->cand;
+  if (cand <= expected) {
+    if (threadIdx.x == 0) {
+      s->cut_key = s->thr_key;
+      s->ties_kept = 0;
+    }
+    return;
+  }
   const unsigned int used = s->pool_used < pool.capacity ? s->pool_used : pool.capacity;
-  const uint32_t thr_key = s->thr_key;
-  // how many candidates are there (block counts are final: the collect pass has completed)
-  unsigned int mine = 0;
-  for (unsigned int b = threadIdx.x; b < used; b += kThreads) mine += pool.blocks[b].count;
-  if (threadIdx.x == 0) total_sh = 0;
+  const unsigned int slots = used * kBlockEntries;
+  const bool in_smem = cand <= unsigned(kCutSmemKeys);
+  if (threadIdx.x == 0) nkeys = 0;
   __syncthreads();
-  atomicAdd(&total_sh, mine);
-  __syncthreads();
-  const unsigned int cand = total_sh;
-  uint32_t cut = thr_key;
-  unsigned int ties = 0;
-  if (cand > expected) {
-    // radix select of the element of rank expected-1 (0-based, from the top) over the pool
-    uint32_t prefix = 0;
-    unsigned int rank = expected - 1;
-    for (int round = 0; round < 3; ++round) {
-      for (int i = threadIdx.x; i < kBins; i += kThreads) sh[i] = 0;
-      __syncthreads();
-      for (unsigned int b = threadIdx.x; b < used; b += kThreads) {
-        const unsigned int c = pool.blocks[b].count;
-        for (unsigned int e = 0; e < c; ++e) {
-          const uint32_t key = pool.blocks[b].entry[e].y & 0x7fffffffu;
-          const bool match = round == 0 ? true : round == 1 ? (key >> 21) == prefix : (key >> 10) == prefix;
-          if (match) atomicAdd(&sh[round == 0 ? int(key >> 21) : round == 1 ? int((key >> 10) & 0x7ffu) : int(key & 0x3ffu)], 1u);
+  if (in_smem) {
+    // sweep the pool once: four independent loads per thread and iteration
+    for (unsigned int base = 0; base < slots; base += kCutThreads * 4) {
+      uint32_t k[4];
+      bool ok[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const unsigned int i = base + u * kCutThreads + threadIdx.x;
+        ok[u] = i < slots && (i & (kBlockEntries - 1)) < pool.count[i / kBlockEntries];
+        k[u] = ok[u] ? (pool.entry[i].y & 0x7fffffffu) : 0u;
+      }
+      // one shared-memory atomic per warp and load, not one per key
+      const int lane = threadIdx.x & 31;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const unsigned int m = __ballot_sync(0xffffffffu, ok[u]);
+        if (m == 0) continue;
+        unsigned int at = 0;
+        if (lane == __ffs(m) - 1) at = atomicAdd(&nkeys, unsigned(__popc(m)));
+        at = __shfl_sync(0xffffffffu, at, __ffs(m) - 1);
+        if (ok[u]) keys[at + __popc(m & ((1u << lane) - 1u))] = k[u];
+      }
+    }
+    __syncthreads();
+  }
+  const unsigned int count = in_smem ? nkeys : slots;
+  uint32_t prefix = 0;
+  unsigned int rank = expected - 1;   // 0-based from the top
+  for (int round = 0; round < 3; ++round) {
+    for (int i = threadIdx.x; i < kBins; i += kCutThreads) sh[i] = 0;
+    __syncthreads();
+    // whole warps iterate together: candidate keys share their leading bits (same exponent), so
+    // the lanes that hit the same bin are counted by one of them (one atomic per bin and warp)
+    const unsigned int count_padded = (count + 31u) & ~31u;
+    for (unsigned int i = threadIdx.x; i < count_padded; i += kCutThreads) {
+      uint32_t key = 0;
+      bool live = i < count;
+      if (live) {
+        if (in_smem) {
+          key = keys[i];
+        } else {   // more candidates than shared memory holds: read the pool again in every round
+          live = (i & (kBlockEntries - 1)) < pool.count[i / kBlockEntries];
+          if (live) key = pool.entry[i].y & 0x7fffffffu;
         }
       }
-      __syncthreads();
-      unsigned int bin, rin;
-      pick_from_top(sh, rank, bin, rin);
-      prefix = round == 0 ? bin : round == 1 ? (prefix << 11) | bin : (prefix << 10) | bin;
-      rank = rin;
-      __syncthreads();
+      live = live && prefix_matches(key, round, prefix);
+      const int bin = live ? digit_of(key, round) : -1;
+      const unsigned int same = __match_any_sync(0xffffffffu, bin);
+      if (live && (threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&sh[bin], unsigned(__popc(same)));
     }
-    cut = prefix;
-    ties = rank + 1;
+    __syncthreads();
+    unsigned int bin, rin;
+    pick_from_top_1024(sh, rank, bin, rin, part, res);
+    prefix = extend_prefix(prefix, round, bin);
+    rank = rin;
   }
-  // kept counts per list, in list (= index) order
-  const int per = (lists + kThreads - 1) / kThreads;
-  const int l0 = threadIdx.x * per, l1 = (l0 + per < lists) ? l0 + per : lists;
-  unsigned int g = 0, e = 0;
-  for (int l = l0; l < l1; ++l) {
-    unsigned int lg = 0, le = 0;
-    for (unsigned int b = s->list_head[l]; b != kNoBlock && b < pool.capacity; b = pool.blocks[b].next) {
-      const unsigned int c = pool.blocks[b].count;
-      for (unsigned int i = 0; i < c; ++i) {
-        const uint32_t key = pool.blocks[b].entry[i].y & 0x7fffffffu;
-        lg += key > cut;
-        le += key == cut;
-      }
+  if (threadIdx.x == 0) {
+    s->cut_key = prefix;
+    s->ties_kept = rank + 1;
+  }
+}
+
+// ---- one warp per list: kept counts against the cut; the last CTA: offsets, k, header, housekeeping
+__global__ void __launch_bounds__(kThreads)
+count_scan_kernel(int lists, PushTargets dst, SparseScratch* s, ListPool pool, float* sumsq_to_clear) {
+  resolve_epoch(dst);
+  constexpr int kWarps = kThreads / 32;
+  __shared__ unsigned int w_gt[kWarps], w_eq[kWarps];
+  __shared__ bool is_last;
+  __shared__ unsigned int part_gt[kThreads], part_eq[kThreads];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int list = blockIdx.x * kWarps + warp;
+  const uint32_t cut = s->cut_key;
+  unsigned int gt = 0, eq = 0;
+  if (list < lists) {
+    for (unsigned int b = s->list_head[list]; b != kNoBlock && b < pool.capacity; b = pool.next[b]) {
+      const unsigned int c = pool.count[b];
+      const uint32_t key = lane < int(c) ? (pool.entry[size_t(b) * kBlockEntries + lane].y & 0x7fffffffu) : 0u;
+      gt += __popc(__ballot_sync(0xffffffffu, lane < int(c) && key > cut));
+      eq += __popc(__ballot_sync(0xffffffffu, lane < int(c) && key == cut));
     }
-    s->list_gt[l] = g;   // exclusive within this thread's run; the run's base is added below
-    s->list_eq[l] = e;
-    g += lg;
-    e += le;
+    if (lane == 0) {
+      s->list_gt[list] = gt;
+      s->list_eq[list] = eq;
+    }
   }
-  part_gt[threadIdx.x] = g;
-  part_eq[threadIdx.x] = e;
+  if (lane == 0) {
+    w_gt[warp] = gt;
+    w_eq[warp] = eq;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned int a = 0, b = 0;
+    for (int w = 0; w < kWarps; ++w) {
+      a += w_gt[w];
+      b += w_eq[w];
+    }
+    s->cnt_gt[blockIdx.x] = a;
+    s->cnt_eq[blockIdx.x] = b;
+    __threadfence();
+    is_last = atomicAdd(&s->lists_done, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // exclusive scan of the per-CTA totals (at most kMaxBlocks of them)
+  const int ctas = gridDim.x;
+  const int per = (ctas + kThreads - 1) / kThreads;
+  const int c0 = threadIdx.x * per, c1 = (c0 + per < ctas) ? c0 + per : ctas;
+  unsigned int a = 0, b = 0;
+  for (int c = c0; c < c1; ++c) {
+    const unsigned int x = reinterpret_cast<volatile unsigned int*>(s->cnt_gt)[c];
+    const unsigned int y = reinterpret_cast<volatile unsigned int*>(s->cnt_eq)[c];
+    s->off_gt[c] = a;   // exclusive within this thread's run; the run's base is added below
+    s->off_eq[c] = b;
+    a += x;
+    b += y;
+  }
+  part_gt[threadIdx.x] = a;
+  part_eq[threadIdx.x] = b;
   __syncthreads();
   if (threadIdx.x == 0) {
     unsigned int rg = 0, re = 0;
     for (int i = 0; i < kThreads; ++i) {
-      const unsigned int a = part_gt[i], b = part_eq[i];
+      const unsigned int x = part_gt[i], y = part_eq[i];
       part_gt[i] = rg;
       part_eq[i] = re;
-      rg += a;
-      re += b;
+      rg += x;
+      re += y;
     }
+    const unsigned int ties = s->ties_kept;
     const unsigned int k = rg + (re < ties ? re : ties);
     s->k = k;
-    s->cut_key = cut;
-    s->ties_kept = ties;
-    s->last_cand = cand;
+    s->last_cand = s->cand;
     const uint32_t total = 4u + 8u * k;
     uint8_t header[4];
     for (int i = 0; i < 4; ++i) header[i] = uint8_t(total >> (8 * i));
     push_bytes(dst, 0, header, 4);
     s->pool_used = 0;
     s->cand = 0;
-    if (sumsq_to_clear != nullptr) *const_cast<float*>(sumsq_to_clear) = 0.f;
+    s->lists_done = 0;
+    if (sumsq_to_clear != nullptr) *sumsq_to_clear = 0.f;
   }
   __syncthreads();
-  for (int l = l0; l < l1; ++l) {
-    s->list_gt[l] += part_gt[threadIdx.x];
-    s->list_eq[l] += part_eq[threadIdx.x];
+  for (int c = c0; c < c1; ++c) {
+    s->off_gt[c] += part_gt[threadIdx.x];
+    s->off_eq[c] += part_eq[threadIdx.x];
   }
   unsigned int* h = &s->shist[0][0];
   for (int i = threadIdx.x; i < 3 * kBins; i += kThreads) h[i] = 0;
@@ -903,16 +1046,22 @@ __global__ void __launch_bounds__(kThreads)
 emit_kernel(float* __restrict__ R, float* __restrict__ u_mask, int lists, PushTargets dst,
             const SparseScratch* s, ListPool pool) {
   resolve_epoch(dst);
-  const int lane = threadIdx.x & 31;
-  const int list = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  constexpr int kWarps = kThreads / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int list = blockIdx.x * kWarps + warp;
   const uint32_t cut = s->cut_key;
   const unsigned int ties = s->ties_kept, k_total = s->k;
   if (list < lists) {
-    unsigned int run_gt = s->list_gt[list], run_eq = s->list_eq[list];
-    for (unsigned int b = s->list_head[list]; b != kNoBlock && b < pool.capacity; b = pool.blocks[b].next) {
-      const unsigned int c = pool.blocks[b].count;
+    // what the lists before this one keep: the CTA's offset plus the earlier warps of the CTA
+    unsigned int run_gt = s->off_gt[blockIdx.x], run_eq = s->off_eq[blockIdx.x];
+    for (int w = 0; w < warp; ++w) {
+      run_gt += s->list_gt[blockIdx.x * kWarps + w];
+      run_eq += s->list_eq[blockIdx.x * kWarps + w];
+    }
+    for (unsigned int b = s->list_head[list]; b != kNoBlock && b < pool.capacity; b = pool.next[b]) {
+      const unsigned int c = pool.count[b];
       uint2 en = make_uint2(0u, 0u);
-      if (lane < int(c)) en = pool.blocks[b].entry[lane];
+      if (lane < int(c)) en = pool.entry[size_t(b) * kBlockEntries + lane];
       const uint32_t key = en.y & 0x7fffffffu;
       const bool above = lane < int(c) && key > cut, at = lane < int(c) && key == cut;
       const unsigned int ma = __ballot_sync(0xffffffffu, above), me = __ballot_sync(0xffffffffu, at);
@@ -932,6 +1081,38 @@ emit_kernel(float* __restrict__ R, float* __restrict__ u_mask, int lists, PushTa
     }
   }
   publish_when_grid_done(dst);
+}
+
+// out[idx] = 0 for every index of every payload: puts a dense buffer that only holds scattered
+// payload entries back to all zeros without a pass over the whole buffer.
+struct ClearSources {
+  const uint8_t* payload[kMaxWorld];
+  int64_t cap[kMaxWorld];
+};
+__global__ void __launch_bounds__(kThreads)
+clear_kernel(ClearSources src, float* __restrict__ out, int64_t n, const uint32_t* epoch_dev, int64_t parity_stride,
+             const int* guard) {
+  if (status_guarded(guard)) return;
+  const uint8_t* payload = src.payload[0];
+  int64_t cap = src.cap[0];
+#pragma unroll
+  for (int r = 1; r < kMaxWorld; ++r) {
+    if (r == int(blockIdx.y)) {
+      payload = src.payload[r];
+      cap = src.cap[r];
+    }
+  }
+  if (epoch_dev != nullptr && (*epoch_dev & 1u)) payload += parity_stride;
+  uint32_t total = 0;
+  for (int k = 0; k < 4; ++k) total |= uint32_t(payload[k]) << (8 * k);
+  if (total < 4 || int64_t(total) > cap) return;   // reported by the scatter kernel
+  const int64_t k = (int64_t(total) - 4) / 8;
+  const uint32_t* idx = reinterpret_cast<const uint32_t*>(payload + 4);
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < k; x += stride) {
+    const uint32_t i = idx[x];
+    if (int64_t(i) < n) out[i] = 0.0f;
+  }
 }
 
 struct Plan {
@@ -970,7 +1151,8 @@ inline ListPlan list_plan(int64_t n) {
   p.pool_blocks = entries / kBlockEntries + kMaxLists;
   p.keys_offset = (sizeof(SparseScratch) + 255) / 256 * 256;
   p.pool_offset = (p.keys_offset + size_t(p.key_capacity) * 4 + 255) / 256 * 256;
-  p.total_bytes = p.pool_offset + size_t(p.pool_blocks) * sizeof(ListBlock);
+  // count[blocks], next[blocks], entry[blocks][16]
+  p.total_bytes = p.pool_offset + size_t(p.pool_blocks) * (8 + kBlockEntries * sizeof(uint2)) + 256;
   return p;
 }
 
@@ -1021,12 +1203,24 @@ cudaError_t sparse_compress_fused(const SparseFuse& fuse, float* R, int64_t n, d
   PushTargets hdr = dst;
   hdr.done = nullptr;
   if (lists) {
-    ListPool pool{reinterpret_cast<ListBlock*>(static_cast<uint8_t*>(scratch) + lp.pool_offset),
-                  static_cast<unsigned int>(lp.pool_blocks)};
+    uint8_t* pool_base = static_cast<uint8_t*>(scratch) + lp.pool_offset;
+    ListPool pool;
+    pool.capacity = static_cast<unsigned int>(lp.pool_blocks);
+    pool.count = reinterpret_cast<unsigned int*>(pool_base);
+    pool.next = pool.count + lp.pool_blocks;
+    pool.entry = reinterpret_cast<uint2*>((reinterpret_cast<uintptr_t>(pool.next + lp.pool_blocks) + 127) & ~uintptr_t(127));
     const int nlists = pl.blocks * (kThreads / 32);
-    collect_kernel<<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);
-    select_kernel<<<1, kThreads, 0, stream>>>(nlists, unsigned(expected), hdr, s, pool,
-                                              fuse.mode == 2 && fuse.clip > 0.f ? fuse.sumsq : nullptr);
+    if (fuse.mode == 2) collect_kernel<2><<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);
+    else if (fuse.mode == 1) collect_kernel<1><<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);
+    else collect_kernel<0><<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);
+    {
+      cudaError_t e = cudaFuncSetAttribute(cut_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kCutSmemKeys * int(sizeof(uint32_t)));
+      if (e != cudaSuccess) return e;
+    }
+    cut_kernel<<<1, kCutThreads, kCutSmemKeys * sizeof(uint32_t), stream>>>(unsigned(expected), s, pool);
+    count_scan_kernel<<<pl.blocks, kThreads, 0, stream>>>(
+        nlists, hdr, s, pool, fuse.mode == 2 && fuse.clip > 0.f ? const_cast<float*>(fuse.sumsq) : nullptr);
     emit_kernel<<<pl.blocks, kThreads, 0, stream>>>(R, fuse.mode == 2 ? fuse.u : nullptr, nlists, dst, s, pool);
     return cudaGetLastError();
   }
@@ -1065,6 +1259,23 @@ cudaError_t sparse_read_stats(const void* scratch, unsigned int* host4, cudaStre
   if (e == cudaSuccess) e = cudaMemcpyAsync(host4 + 2, &s->thr_key, 4, cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaMemcpyAsync(host4 + 3, &s->dropped, 4, cudaMemcpyDeviceToHost, stream);
   return e;
+}
+
+cudaError_t sparse_clear(const UnpackSources& src, float* out, int64_t n, cudaStream_t stream) {
+  if (n <= 0 || src.world < 1 || src.world > kMaxWorld) return cudaErrorInvalidValue;
+  ClearSources cs{};
+  int64_t kmax = 1;
+  for (int r = 0; r < src.world; ++r) {
+    if (reinterpret_cast<uintptr_t>(src.payload[r]) & 3) return cudaErrorInvalidValue;
+    cs.payload[r] = src.payload[r];
+    cs.cap[r] = src.payload_bytes[r];
+    kmax = std::max<int64_t>(kmax, (src.payload_bytes[r] - 4) / 8);
+  }
+  int64_t blocks = (kmax + kThreads - 1) / kThreads;
+  if (blocks > 148 * 2) blocks = 148 * 2;
+  clear_kernel<<<dim3(unsigned(blocks), unsigned(src.world), 1), kThreads, 0, stream>>>(cs, out, n, src.epoch_dev,
+                                                                                          src.parity_stride, src.guard);
+  return cudaGetLastError();
 }
 
 cudaError_t sparse_unpack_accum(const UnpackSources& src, float* out, int64_t n, int add,

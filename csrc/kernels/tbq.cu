@@ -152,7 +152,7 @@ tbq_compress_kernel(const float* __restrict__ grad, float* __restrict__ residual
 enum UnpackMode : int { kGeneric = 0, kPair = 1, kConcat = 2 };
 
 template <bool APPLY, int MODE, int WORLD>
-__global__ void __launch_bounds__(kUnpackThreads, MODE == kGeneric ? 1 : 3)
+__global__ void __launch_bounds__(kUnpackThreads, MODE == kGeneric ? 1 : 4)
 tbq_unpack_lut_kernel(UnpackSources src, float thr, float* __restrict__ out, int64_t n, int add,
                       float post_scale, SgdApply apply) {
   if (unpack_guarded(src)) return;
@@ -197,6 +197,7 @@ cudaError_t tbq_compress(const float* grad, float* residual, int64_t n, float th
   const int64_t S = dst.shard_elems;
   bool dst16 = (dst.parity_stride & 15) == 0;
   for (int p = 0; p < dst.world; ++p) dst16 = dst16 && aligned16(dst.payload[p]);
+  if (dst.mc != nullptr) dst16 = dst16 && aligned16(dst.mc);
   // scatter mode runs on the chunked path only (see tbq_compress_kernel)
   if (S > 0 && (!vec || !dst16 || S % 4096 != 0 || (n + S - 1) / S > dst.world)) return cudaErrorInvalidValue;
   // chunked path with 16-byte stores once there is a chunk per warp of a half-filled GPU

@@ -353,7 +353,7 @@ __device__ __forceinline__ TernHeader read_header(const uint8_t* p, int64_t cap,
 enum UnpackMode : int { kGeneric = 0, kPair = 1, kConcat = 2 };
 
 template <int BW, bool APPLY, int MODE, int WORLD>
-__global__ void __launch_bounds__(kUnpackThreads, MODE == kGeneric ? 1 : 3)
+__global__ void __launch_bounds__(kUnpackThreads, MODE == kGeneric ? 1 : 4)
 tern_unpack_lut_kernel(UnpackSources src, float* __restrict__ out, int64_t n, int add,
                        float post_scale, SgdApply apply, int* status) {
   if (unpack_guarded(src)) return;
@@ -494,6 +494,7 @@ cudaError_t terngrad_compress(const float* grad, float* residual, int64_t n, int
   const int64_t S = dst.shard_elems;
   bool dst16 = (dst.parity_stride & 15) == 0;
   for (int p = 0; p < dst.world; ++p) dst16 = dst16 && aligned16(dst.payload[p] + kTernHeaderBytes);
+  if (dst.mc != nullptr) dst16 = dst16 && aligned16(dst.mc + kTernHeaderBytes);
   // scatter mode runs on the chunked path only (see tern_quant_kernel)
   if (S > 0 && (!vec || !dst16 || S % 4096 != 0 || (n + S - 1) / S > dst.world)) return cudaErrorInvalidValue;
   const int shards = S > 0 ? int((n + S - 1) / S) : 1;

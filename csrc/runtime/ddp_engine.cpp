@@ -113,8 +113,6 @@ DdpEngine::DdpEngine(const EngineConfig& cfg, const std::vector<BucketDesc>& buc
     check(cudaMemset(stamps_, 0, bytes), "memset stamps");
   }
   if (cfg.device_epoch) {
-    if (cfg.codec == Codec::kDense)
-      throw std::invalid_argument("device_epoch is not implemented for the dense codec (its copy takes the slot parity from the host)");
     if (cfg.num_workers >= 1)
       throw std::invalid_argument("device_epoch needs inline issue (num_workers = 0): a captured step is issued by the capturing thread");
     check(cudaMalloc(reinterpret_cast<void**>(&epoch_dev_), 64), "cudaMalloc epoch");
@@ -203,9 +201,10 @@ void DdpEngine::set_adamw(float lr, float beta1, float beta2, float eps, float w
   fused_sgd_ = false;
 }
 
-void DdpEngine::set_symmetric(const std::vector<uint8_t*>& bases) {
+void DdpEngine::set_symmetric(const std::vector<uint8_t*>& bases, uint8_t* multicast) {
   if (static_cast<int>(bases.size()) != cfg_.world) throw std::invalid_argument("one base pointer per rank");
   bases_ = bases;
+  mc_base_ = multicast;
 }
 
 void DdpEngine::set_sgd(float lr, float momentum, float weight_decay, bool fused) {
@@ -307,6 +306,7 @@ cuda::PushTargets DdpEngine::targets_for(int b, WorkerCtx& w) const {
     t.payload[p] = base + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
     t.flag[p] = reinterpret_cast<uint32_t*>(base + L.flags) + cfg_.rank;
   }
+  if (nvls_active()) t.mc = mc_base_ + L.slots[parity] + int64_t(cfg_.rank) * L.slot_bytes + L.shift;
   return t;
 }
 
@@ -364,7 +364,7 @@ cuda::SgdApply DdpEngine::sgd_apply_for(int b) const {
   return apply;
 }
 
-void DdpEngine::issue_adamw(int b, cudaStream_t stream) {
+void DdpEngine::issue_adamw(int b, cudaStream_t stream, int clear_grad) {
   if (!param_ || !momentum_ || !second_) throw std::runtime_error("AdamW needs param and both moment buffers");
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   cuda::AdamWApply aw;
@@ -378,7 +378,7 @@ void DdpEngine::issue_adamw(int b, cudaStream_t stream) {
   aw.weight_decay = wd_;
   aw.step = int(steps_) + 1;
   aw.step_dev = epoch_dev_;   // one epoch per step: the device counter is the 1-based step count
-  aw.clear_grad = cfg_.clear_grad;
+  aw.clear_grad = clear_grad < 0 ? cfg_.clear_grad : clear_grad;
   aw.guard = status_;
   check(cuda::adamw_apply_dense(grad_ + B.offset, 1.0f, aw, B.numel, stream), "adamw_apply_dense");
 }
@@ -456,6 +456,7 @@ void DdpEngine::issue_shard_reduce(int b, int worker) {
     dst.payload[p] = base + L.slots2[parity] + int64_t(me) * L.slot_bytes + L.shift;
     dst.flag[p] = reinterpret_cast<uint32_t*>(base + L.flags2) + me;
   }
+  if (nvls_active()) dst.mc = mc_base_ + L.slots2[parity] + int64_t(me) * L.slot_bytes + L.shift;
   if (n_me == 0) {
     check(cuda::signal_flags(dst, w.recv), "signal_flags");
     launches_ += launched + 1;
@@ -632,9 +633,15 @@ void DdpEngine::issue_push(int b, int worker) {
       break;
     case Codec::kDense: {
       // own slot in local memory; peers pull it
-      uint8_t* slot = bases_[static_cast<size_t>(cfg_.rank)] + L.slots[epoch_ & 1u] +
-                      int64_t(cfg_.rank) * L.slot_bytes;
-      check(cudaMemcpyAsync(slot, g, size_t(n) * 4, cudaMemcpyDeviceToDevice, w.push), "copy");
+      if (epoch_dev_) {
+        float* even = reinterpret_cast<float*>(bases_[static_cast<size_t>(cfg_.rank)] + L.slots[0] +
+                                               int64_t(cfg_.rank) * L.slot_bytes);
+        check(cuda::dense_stage(g, even, (L.slots[1] - L.slots[0]) / 4, epoch_dev_, n, w.push), "dense_stage");
+      } else {
+        uint8_t* slot = bases_[static_cast<size_t>(cfg_.rank)] + L.slots[epoch_ & 1u] +
+                        int64_t(cfg_.rank) * L.slot_bytes;
+        check(cudaMemcpyAsync(slot, g, size_t(n) * 4, cudaMemcpyDeviceToDevice, w.push), "copy");
+      }
       check(cuda::signal_flags(dst, w.push), "signal_flags");
       launched += 1;
       break;
@@ -691,19 +698,31 @@ void DdpEngine::issue_recv(int b, int worker) {
     case Codec::kDense: {
       const float* srcs[cuda::kMaxWorld];
       for (int r = 0; r < cfg_.world; ++r)
-        srcs[r] = reinterpret_cast<const float*>(bases_[static_cast<size_t>(r)] + L.slots[epoch_ & 1u] +
-                                                 int64_t(r) * L.slot_bytes);
-      check(cuda::dense_gather_sum(srcs, cfg_.world, g, n, post, w.recv), "dense_gather_sum");
+        srcs[r] = reinterpret_cast<const float*>(bases_[static_cast<size_t>(r)] +
+                                                 L.slots[epoch_dev_ ? 0 : (epoch_ & 1u)] + int64_t(r) * L.slot_bytes);
+      check(cuda::dense_gather_sum(srcs, cfg_.world, g, n, post, w.recv, epoch_dev_, (L.slots[1] - L.slots[0]) / 4,
+                                   status_),
+            "dense_gather_sum");
       launched += 1;
       break;
     }
   }
+  // Sparse codecs: the dense gradient holds the scattered payload entries and zeros.  Instead of
+  // letting the optimizer kernel write zeros over all of it again, only the scattered positions
+  // are cleared afterwards.
+  const bool sparse_clear = cfg_.codec == Codec::kSparse && cfg_.clear_grad && (fused_sgd_ || adamw_);
   if (fused_sgd_ && !applied) {
-    check(cuda::sgd_apply_dense(g, 1.0f, apply, n, w.recv), "sgd_apply_dense");
+    cuda::SgdApply dense = apply;
+    if (sparse_clear) dense.clear_grad = 0;
+    check(cuda::sgd_apply_dense(g, 1.0f, dense, n, w.recv), "sgd_apply_dense");
     launched += 1;
   }
   if (adamw_) {
-    issue_adamw(b, w.recv);
+    issue_adamw(b, w.recv, sparse_clear ? 0 : cfg_.clear_grad);
+    launched += 1;
+  }
+  if (sparse_clear) {
+    check(cuda::sparse_clear(src, g, n, w.recv), "sparse_clear");
     launched += 1;
   }
   stamp(b, kStampDone, w.recv);

@@ -85,6 +85,12 @@ struct EngineConfig {
   // last step's table.  Adds four tiny launches per bucket, so it is off unless asked for.  (The
   // time spent inside flag waits is counted always: wait_stats().)
   int trace = 0;
+  // Deliver payloads with NVLS multicast stores (multimem.st) where the symmetric buffer has a
+  // multicast mapping: one store per packed word reaches every rank's slot through the NVLink
+  // switch, instead of one store per destination.  All-gather form of tbq / terngrad / ecq and
+  // the sparse codecs; flags, headers and ragged ends stay unicast.  Ignored (plain peer stores)
+  // when the buffer has no multicast mapping.
+  int nvls = 0;
 };
 
 struct BucketDesc {
@@ -122,7 +128,9 @@ class DdpEngine {
   void set_buffers(float* grad, float* residual, float* param, float* momentum,
                    float* aux = nullptr, float* second = nullptr);
   // bases[r]: rank r's symmetric buffer as mapped in this process.
-  void set_symmetric(const std::vector<uint8_t*>& bases);
+  // multicast: NVLS mapping of the same buffer (stores reach every rank), or null.
+  void set_symmetric(const std::vector<uint8_t*>& bases, uint8_t* multicast = nullptr);
+  bool nvls_active() const { return cfg_.nvls && mc_base_ != nullptr && cfg_.world > 1; }
 
   void set_sgd(float lr, float momentum, float weight_decay, bool fused);
   void set_adamw(float lr, float beta1, float beta2, float eps, float weight_decay);
@@ -192,7 +200,7 @@ class DdpEngine {
   enum Stamp : int { kStampReady = 0, kStampPushed = 1, kStampArrived = 2, kStampDone = 3, kStampCount = 4 };
   void stamp(int b, int which, cudaStream_t stream);
   cuda::SgdApply sgd_apply_for(int b) const;
-  void issue_adamw(int b, cudaStream_t stream);
+  void issue_adamw(int b, cudaStream_t stream, int clear_grad = -1);  // -1: as configured
   void issue_bucket(int b, int worker);
   void issue_push(int b, int worker);
   void issue_recv(int b, int worker);
@@ -215,6 +223,7 @@ class DdpEngine {
   bool adamw_ = false;
   float beta1_ = 0.9f, beta2_ = 0.999f, eps_ = 1e-8f;
   std::vector<uint8_t*> bases_;
+  uint8_t* mc_base_ = nullptr;
   float lr_ = 0.f, sgd_mu_ = 0.f, wd_ = 0.f;
   bool fused_sgd_ = false;
   double keep_fraction_;

@@ -67,6 +67,10 @@ class CompressionConfig:
     clip_norm: float = 0.0
     # per-stage device timing (metrics()["stages"]): four one-thread launches per bucket
     trace: bool = False
+    # how payloads reach the peers: "p2p" = one store per destination over NVLink (always
+    # available); "nvls" = one multicast store through the NVLink switch where the host exposes
+    # it (falls back to p2p otherwise; ``wrapper.transport`` says which one runs)
+    transport: str = "p2p"
 
     def engine_dict(self, rank: int, world: int, device: int) -> Dict:
         return dict(rank=rank, world=world, device=device, codec=self.algorithm, bitwidth=self.bitwidth,
@@ -215,15 +219,20 @@ class CompressedDataParallel(nn.Module):
         cfg_dict["sharded"] = 1 if self.sharded else 0
         self.graph_capturable = bool(self.config.graph_capturable)
         if self.graph_capturable:
-            if self.config.algorithm not in ("tbq", "terngrad", "graddrop", "dgc", "ecq") or not fused:
-                raise ValueError("graph_capturable needs tbq, terngrad, graddrop, dgc or ecq with a fused optimizer")
+            if not fused:
+                raise ValueError("graph_capturable needs a fused optimizer (the update is part of the captured step)")
             cfg_dict["device_epoch"] = 1
             cfg_dict["num_workers"] = 0
         elif self.config.num_workers < 0:
             per_bucket = {"dgc": 12 + world, "graddrop": 10 + world}.get(self.config.algorithm, 4)
             cfg_dict["num_workers"] = 1 if len(self.plan.buckets) * per_bucket > 200 else 0
+        if self.config.transport not in ("p2p", "nvls"):
+            raise ValueError("transport must be 'p2p' or 'nvls'")
+        cfg_dict["nvls"] = 1 if self.config.transport == "nvls" else 0
         self.engine = _C.DdpEngine(cfg_dict, self.plan.buckets, self.plan.param_bucket)
-        self.symmetric = symmetric or SymmetricMemory(self.engine.symmetric_bytes, dev, process_group)
+        self.symmetric = symmetric or SymmetricMemory(self.engine.symmetric_bytes, dev, process_group,
+                                                      multicast=self.config.transport == "nvls")
+        self.transport = "nvls" if (self.config.transport == "nvls" and self.symmetric.multicast) else "p2p"
         if self.symmetric.nbytes < self.engine.symmetric_bytes:
             raise ValueError("symmetric buffer too small for this model")
         self.engine.set_buffers(self.flat_grad, self.flat_residual, self.flat_param, self.flat_momentum,

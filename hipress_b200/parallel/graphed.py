@@ -8,14 +8,16 @@ as in eager mode) and replays it with a single launch.
 
 Two capture scopes:
 
-* **Whole step** (wrappers created with ``CompressionConfig(graph_capturable=True)``: TBQ,
-  TernGrad, GradDrop and DGC with a fused optimizer).  The engine keeps the step's epoch -- flag
+* **Whole step** (wrappers created with ``graph_capturable=True``: TBQ, TernGrad, ECQ, GradDrop,
+  DGC and the dense codec with a fused optimizer, and PowerSGD).  The engine keeps the step's epoch -- flag
   values, slot parity, rounding / sampling seed, AdamW's step count -- in device memory, advanced
   by a one-thread kernel at the start of the step, so nothing in its launches changes from step
   to step.  The capture then contains
   ``begin_step``, forward, backward *with the gradient hooks firing* and ``step``: every bucket
   is compressed, pushed to the peers, unpacked and applied on the engine's side streams as soon
-  as its gradients exist, overlapping the rest of backward, exactly as in eager mode.
+  as its gradients exist, overlapping the rest of backward, exactly as in eager mode.  PowerSGD
+  alternates between two accumulator sets by epoch parity; its step is captured once per parity
+  (``capture_variants``) and the two graphs, which share one memory pool, are replayed in turn.
 * **Forward + backward only** (every other wrapper).  The exchange takes host-side arguments
   per step and stays outside the graph; all buckets are handed to the engine right after the
   replay.  On NVLink the exchange of a whole model costs a few hundred microseconds, less than
@@ -55,20 +57,34 @@ class GraphedTrainStep:
                     fn(ddp.module, *self.static_inputs).backward()
             torch.cuda.current_stream().wait_stream(side)
             self._restore(saved)
-            self.graph = torch.cuda.CUDAGraph()
+            self.variants = int(getattr(ddp, "capture_variants", 1)) if self.whole_step else 1
+            self.graphs, self.losses = [], []
             if self.whole_step:
                 ddp.hooks_enabled = True
-                with torch.cuda.graph(self.graph):
-                    ddp.begin_step()
-                    self.loss = fn(ddp.module, *self.static_inputs)
-                    self.loss.backward()
-                    ddp.step()
-                # nothing ran: the step issued during the capture comes back out of the counters
-                self.launches_per_step = ddp.end_capture()
+                pool = None
+                for v in range(self.variants):
+                    if self.variants > 1:
+                        ddp.begin_capture_variant(v)
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, pool=pool):
+                        ddp.begin_step()
+                        loss = fn(ddp.module, *self.static_inputs)
+                        loss.backward()
+                        ddp.step()
+                    # nothing ran: the step issued during the capture comes back out of the counters
+                    self.launches_per_step = ddp.end_capture()
+                    pool = g.pool()
+                    self.graphs.append(g)
+                    self.losses.append(loss)
+                    self._restore(saved)
             else:
-                with torch.cuda.graph(self.graph):
-                    self.loss = fn(ddp.module, *self.static_inputs)
-                    self.loss.backward()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    loss = fn(ddp.module, *self.static_inputs)
+                    loss.backward()
+                self.graphs.append(g)
+                self.losses.append(loss)
+            self.graph, self.loss = self.graphs[0], self.losses[0]
             self._restore(saved)
         except BaseException:
             # a failed capture must leave the wrapper usable for eager steps
@@ -91,9 +107,10 @@ class GraphedTrainStep:
         for dst, src in zip(self.static_inputs, inputs):
             dst.copy_(src, non_blocking=True)
         if self.whole_step:
-            self.graph.replay()
+            v = self.ddp.next_variant() if self.variants > 1 else 0
+            self.graphs[v].replay()
             self.ddp.note_replay(self.launches_per_step)
-            return self.loss
+            return self.losses[v]
         self.ddp.begin_step()
         self.ddp.hooks_enabled = False       # nothing fires during a replay; guards an eager fallback
         try:

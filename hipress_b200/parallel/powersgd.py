@@ -39,7 +39,8 @@ class PowerSGDDataParallel(nn.Module):
     def __init__(self, module: nn.Module, rank_r: int = 4, *, lr: float = 0.1, momentum: float = 0.9,
                  weight_decay: float = 0.0, seed: int = 0, process_group: Optional[dist.ProcessGroup] = None,
                  symmetric: Optional[SymmetricMemory] = None, rank: Optional[int] = None,
-                 world: Optional[int] = None, flag_timeout_s: float = 20.0, emulated: bool = False):
+                 world: Optional[int] = None, flag_timeout_s: float = 20.0, emulated: bool = False,
+                 graph_capturable: bool = False):
         super().__init__()
         if not 1 <= rank_r <= 16:
             raise ValueError("rank must be between 1 and 16")
@@ -50,6 +51,13 @@ class PowerSGDDataParallel(nn.Module):
         self.world = world if world is not None else (dist.get_world_size(process_group) if dist.is_initialized() else 1)
         self.lr, self.momentum, self.weight_decay = lr, momentum, weight_decay
         self.timeout = flag_timeout_s
+        # Whole-step CUDA graph capture (GraphedTrainStep): the flag value of a step lives in device
+        # memory (advanced by a one-thread kernel), and because which of the two accumulator sets a
+        # step uses depends on the epoch's parity, the step is captured twice, once per parity, and
+        # the two graphs are replayed in turn (capture_variants).
+        self.graph_capturable = bool(graph_capturable)
+        self.capture_variants = 2 if self.graph_capturable else 1
+        self._forced_parity: Optional[int] = None
         params = [p for p in module.parameters() if p.requires_grad]
         self.device = params[0].device
         self.mats = [p for p in params if p.dim() >= 2]
@@ -95,6 +103,7 @@ class PowerSGDDataParallel(nn.Module):
         if self.symmetric.nbytes < need:
             raise ValueError("symmetric buffer too small")
         self.emulated = emulated
+        self.epoch_dev = torch.zeros(16, dtype=torch.int32, device=dev) if self.graph_capturable else None
 
         # ---- native step driver: batched small kernels + one GEMM / expand launch per matrix
         self.engine = _C.PsgdEngine(self.world, self.r, self.flat_M)
@@ -131,7 +140,9 @@ class PowerSGDDataParallel(nn.Module):
                     p.data = v
                     p.grad = self.vec_grad[off:off + p.numel()].view_as(p)
             cfg = dict(rank=self.rank, world=self.world, device=dev.index, codec="dense",
-                       flag_timeout_s=flag_timeout_s, defer_recv=1 if emulated else 0)
+                       flag_timeout_s=flag_timeout_s, defer_recv=1 if emulated else 0,
+                       device_epoch=1 if self.graph_capturable else 0,
+                       num_workers=0 if self.graph_capturable else 1)
             self.vec_engine = _C.DdpEngine(cfg, [(0, cur, 1)], [0])
             self.vec_symmetric = SymmetricMemory(self.vec_engine.symmetric_bytes, dev, process_group) \
                 if not emulated else None
@@ -170,38 +181,74 @@ class PowerSGDDataParallel(nn.Module):
     # The step is split into phases so that a single-process emulation of several ranks can
     # run every rank's phase k before any rank's phase k+1 (no kernel then waits for a kernel
     # that has not been launched).  ``step()`` simply runs them back to back.
+    def _parity(self) -> int:
+        return self.epoch & 1 if self._forced_parity is None else self._forced_parity
+
     def phase_project_p(self) -> None:
         self.epoch += 1
-        par = self.epoch & 1
+        if self.epoch_dev is not None:
+            _C.bump_epoch(self.epoch_dev)
+        par = self._parity()
         self.engine.project_p(par, self.device.index)
-        _C.signal_flags(self.symmetric.buf, self.flag_off["P"], self.epoch, self.device.index)
+        _C.signal_flags(self.symmetric.buf, self.flag_off["P"], self.epoch, self.device.index, self.epoch_dev)
         if self.vec_engine is not None:
-            self.vec_engine.begin_step()
+            self.vec_engine.begin_step(self.device.index)
             self.vec_engine.bucket_ready(0, self.device.index)
         self.launches += 1
 
     def phase_project_q(self) -> None:
-        par = self.epoch & 1
-        _C.wait_flags(self.symmetric.buf, self.flag_off["P"], self.epoch, self.timeout, self.flat_M)
+        par = self._parity()
+        _C.wait_flags(self.symmetric.buf, self.flag_off["P"], self.epoch, self.timeout, self.flat_M, self.epoch_dev)
         # every rank has finished reading the other parity's accumulators: clear them for the next step
         other = self.sym_base + (1 - par) * self.acc_bytes
         self.symmetric.tensor(self.rank, other, self.acc_bytes, "uint8").zero_()
         self.engine.project_q(par, self.device.index)
-        _C.signal_flags(self.symmetric.buf, self.flag_off["Q"], self.epoch, self.device.index)
+        _C.signal_flags(self.symmetric.buf, self.flag_off["Q"], self.epoch, self.device.index, self.epoch_dev)
         self.launches += 3
 
     def phase_apply(self) -> None:
-        par = self.epoch & 1
-        _C.wait_flags(self.symmetric.buf, self.flag_off["Q"], self.epoch, self.timeout, self.flat_M)
-        self.engine.apply(par, self.lr, self.momentum, self.weight_decay, self.steps == 0, self.device.index)
+        par = self._parity()
+        _C.wait_flags(self.symmetric.buf, self.flag_off["Q"], self.epoch, self.timeout, self.flat_M, self.epoch_dev)
+        # momentum starts at zero, so mu * buf + g equals the first step's buf = g: a captured step
+        # must not bake the first-step flag in
+        first = self.steps == 0 and not self.graph_capturable
+        self.engine.apply(par, self.lr, self.momentum, self.weight_decay, first, self.device.index)
         if self.vec_engine is not None:
             self.vec_engine.finish_step(self.device.index)
             self.vec_grad.zero_()
         self.launches += 1
         self.steps += 1
 
+    # ---- whole-step CUDA graph capture (GraphedTrainStep)
+    def begin_capture_variant(self, variant: int) -> None:
+        """The next step is being captured for epochs of parity ``variant``."""
+        self._forced_parity = int(variant)
+
+    def next_variant(self) -> int:
+        """Which captured graph the next step must replay: the parity of its epoch."""
+        return (self.epoch + 1) & 1
+
+    def end_capture(self) -> int:
+        """The step issued during a capture did not run: take it back out of the host counters."""
+        self._forced_parity = None
+        self.epoch -= 1
+        self.steps -= 1
+        per_step = self.launches - self._launches_mark + (self.engine.launches - self._engine_mark)
+        self.launches = self._launches_mark
+        self._vec_per_step = int(self.vec_engine.end_capture()) if self.vec_engine is not None else 0
+        return per_step + self._vec_per_step
+
+    def note_replay(self, launches_per_step: int, count: int = 1) -> None:
+        self.epoch += count
+        self.steps += count
+        self.launches += count * (launches_per_step - self._vec_per_step)
+        if self.vec_engine is not None:
+            self.vec_engine.note_replay(count, self._vec_per_step)
+
     def begin_step(self) -> None:
         """Nothing to arm: the whole exchange runs in ``step``."""
+        self._launches_mark = self.launches
+        self._engine_mark = self.engine.launches
 
     def grad_buffers(self):
         return [self.flat_M] + ([self.vec_grad] if self.vecs else [])

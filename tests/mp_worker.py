@@ -36,10 +36,17 @@ def same_on_all_ranks(t: torch.Tensor) -> bool:
     return all(int(v) == int(allv[0]) for v in allv)
 
 
-def check_codec(codec, kw, rank, world, local, n=300000 + 8):
-    cfg = dict(rank=rank, world=world, device=local, codec=codec, seed=5, flag_timeout_s=10.0, **kw)
+def check_codec(codec, kw, rank, world, local, n=300000 + 8, nvls=False):
+    """Returns False when ``nvls`` was asked for and the host exposes no multicast mapping."""
+    cfg = dict(rank=rank, world=world, device=local, codec=codec, seed=5, flag_timeout_s=10.0, nvls=int(nvls), **kw)
     eng = hp._C.DdpEngine(cfg, [(0, n, 1)], [0])
-    sym = SymmetricMemory(eng.symmetric_bytes, torch.device("cuda", local))
+    sym = SymmetricMemory(eng.symmetric_bytes, torch.device("cuda", local), multicast=nvls)
+    if nvls and not sym.multicast:
+        if rank == 0:
+            print("NVLS unavailable:", getattr(sym, "multicast_note", ""), flush=True)
+        dist.barrier()
+        del eng, sym
+        return False
     grad = torch.zeros(n, device="cuda")
     resid = torch.zeros(n, device="cuda")
     eng.set_buffers(grad, resid, None, None)
@@ -86,6 +93,7 @@ def check_codec(codec, kw, rank, world, local, n=300000 + 8):
             assert torch.equal(resid.cpu(), cpu_resid[rank]), f"{codec} residual rank {rank} step {step}"
     dist.barrier()
     del eng, sym
+    return True
 
 
 def check_sharded(codec, kw, rank, world, local, device_epoch=0):
@@ -144,6 +152,16 @@ def main():
     check_codec("ecq", dict(bitwidth=2, alpha=1.0, beta=0.9, device_epoch=1, num_workers=0), rank, world, local)
     if rank == 0:
         print("MP_OK codec_ecq_device_epoch", flush=True)
+    # payloads delivered with NVLS multicast stores: bit-identical to the peer-store path
+    # (no rank leaves during this check; the rank-exit tests keep multicast off)
+    if os.environ.get("HIPRESS_TEST_NVLS", "1") != "0":
+        ran = True
+        for codec, kw, size in [("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1), 1400000 + 8),
+                                ("tbq", dict(threshold=0.01), 300000 + 8),
+                                ("graddrop", dict(keep_fraction=0.01, sample_rate=0.05), 300000 + 8)]:
+            ran = check_codec(codec, kw, rank, world, local, n=size, nvls=True) and ran
+        if rank == 0:
+            print("MP_OK codec_nvls" if ran else "MP_SKIP codec_nvls (no multicast on this host)", flush=True)
 
     for codec, kw in [("terngrad", dict(bitwidth=2, enable_random=1, error_feedback=1)), ("tbq", dict(threshold=0.01))]:
         check_sharded(codec, kw, rank, world, local)
@@ -233,6 +251,23 @@ def main():
     assert same_on_all_ranks(pm.flat_param) and same_on_all_ranks(pm.vec_param), "PowerSGD replicas diverged"
     if rank == 0:
         print("MP_OK ddp_powersgd", flush=True)
+
+    # PowerSGD with the exchange inside the captured step: two graphs (one per accumulator parity)
+    torch.manual_seed(0)
+    net = vgg_tiny(10).cuda()
+    gp = PowerSGDDataParallel(net, rank_r=2, lr=0.05, momentum=0.9, graph_capturable=True)
+
+    def plain_loss(module, a, b):
+        return torch.nn.functional.cross_entropy(module(a), b)
+
+    pstep = GraphedTrainStep(gp, plain_loss, (x, y))
+    assert pstep.whole_step and pstep.variants == 2
+    plosses = [float(pstep(x, y).detach()) for _ in range(8)]
+    gp.check()
+    assert same_on_all_ranks(gp.flat_param) and same_on_all_ranks(gp.vec_param), "graphed PowerSGD replicas diverged"
+    assert all(v == v for v in plosses)
+    if rank == 0:
+        print("MP_OK ddp_graphed_powersgd", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -83,7 +83,35 @@ def test_graphed_nccl_wrapper_and_bert():
     assert losses[-1] < losses[0], losses
 
 
-@pytest.mark.parametrize("algorithm", ["tbq", "terngrad"])
+def test_whole_step_capture_powersgd_matches_eager():
+    """PowerSGD with the exchange inside the graph: one captured graph per accumulator parity,
+    replayed in turn, flag values read from the device epoch."""
+    torch.manual_seed(1)
+    base = vgg_tiny(10).cuda().train()
+    data = batches(7, n=32)
+
+    def make(capturable):
+        return PowerSGDDataParallel(copy.deepcopy(base), rank_r=4, lr=0.05, momentum=0.9, graph_capturable=capturable)
+
+    eager, graphed = make(False), make(True)
+    for x, y in data:
+        image_loss(eager, x, y).backward()
+        eager.step()
+    step = GraphedTrainStep(graphed, image_loss, data[0])
+    assert step.whole_step and step.variants == 2
+    losses = [float(step(x, y).detach()) for x, y in data]
+    eager.check()
+    graphed.check()
+    assert graphed.steps == eager.steps == len(data) and graphed.epoch == eager.epoch
+    assert all(l == l for l in losses)
+    torch.testing.assert_close(graphed.flat_param, eager.flat_param, atol=2e-2, rtol=0)
+    torch.testing.assert_close(graphed.vec_param, eager.vec_param, atol=2e-2, rtol=0)
+    assert (graphed.flat_param - eager.flat_param).abs().mean().item() < 1e-3
+    # the error-feedback memory is carried across replays
+    assert graphed.flat_M.abs().sum().item() > 0
+
+
+@pytest.mark.parametrize("algorithm", ["tbq", "terngrad", "ecq", "dense"])
 def test_whole_step_capture_matches_eager(algorithm):
     """Exchange captured inside the graph (epoch kept on the device): same parameters as the
     eager engine after every step, stochastic rounding included (same seed schedule)."""
@@ -106,7 +134,8 @@ def test_whole_step_capture_matches_eager(algorithm):
     eager.check()
     graphed.check()
     assert graphed.engine.steps == eager.engine.steps == len(data)
-    assert graphed.metrics()["kernel_launches"] == len(data) * step.launches_per_step
+    if algorithm in ("tbq", "terngrad"):
+        assert graphed.metrics()["kernel_launches"] == len(data) * step.launches_per_step
     # identical kernels on identical data; cuDNN may pick different algorithms for the two module
     # copies, and a last-bit difference can flip a stochastic rounding (one quantisation step of
     # one element): parameters agree to a few such steps.  (Bit-exactness of the device-epoch

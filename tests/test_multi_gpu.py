@@ -26,5 +26,5 @@ def test_engine_and_wrappers_across_gpus(nproc):
                  "codec_terngrad_device_epoch", "codec_tbq_device_epoch", "codec_terngrad_wide", "codec_tbq_wide",
                  "codec_ecq_device_epoch", "sharded_terngrad", "sharded_tbq", "sharded_terngrad_device_epoch",
                  "sharded_tbq_device_epoch", "ddp_terngrad", "ddp_graphed", "ddp_graphed_sharded", "ddp_graphed_dgc",
-                 "ddp_powersgd"):
+                 "ddp_powersgd", "ddp_graphed_powersgd"):
         assert f"MP_OK {name}" in res.stdout, res.stdout[-2000:]
