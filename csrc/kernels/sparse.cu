@@ -237,16 +237,25 @@ sample_round_kernel(SparseFuseDev fuse, const float* __restrict__ R, int64_t n,
   __syncthreads();
   const float scale = dgc_clip_scale(fuse);
   const int64_t stride = int64_t(gridDim.x) * blockDim.x;
-  for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < sample_cnt; x += stride) {
-    uint32_t key;
-    if (ROUND > 0 && keys != nullptr) {
-      key = keys[x];
-    } else {
-      const uint32_t idx = sparse_sample_index(seed, x, uint32_t(n));
-      key = abs_key(fused_value(fuse, R, idx, scale));
-      if (keys != nullptr) keys[x] = key;
+  // whole warps iterate together; sampled magnitudes share their leading bits, so the lanes that
+  // hit the same bin are counted by one of them (one shared-memory atomic per bin and warp)
+  const int64_t padded = (sample_cnt + 31) & ~int64_t(31);
+  for (int64_t x = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; x < padded; x += stride) {
+    uint32_t key = 0;
+    bool live = x < sample_cnt;
+    if (live) {
+      if (ROUND > 0 && keys != nullptr) {
+        key = keys[x];
+      } else {
+        const uint32_t idx = sparse_sample_index(seed, x, uint32_t(n));
+        key = abs_key(fused_value(fuse, R, idx, scale));
+        if (keys != nullptr) keys[x] = key;
+      }
+      live = prefix_matches(key, ROUND, prefix);
     }
-    if (prefix_matches(key, ROUND, prefix)) atomicAdd(&sh[digit_of(key, ROUND)], 1u);
+    const int bin = live ? digit_of(key, ROUND) : -1;
+    const unsigned int same = __match_any_sync(0xffffffffu, bin);
+    if (live && int(threadIdx.x & 31) == __ffs(same) - 1) atomicAdd(&sh[bin], unsigned(__popc(same)));
   }
   hist_flush(sh, s->shist[ROUND]);
 }
@@ -623,6 +632,7 @@ struct ListPool {
   unsigned int* count;
   unsigned int* next;
   uint2* entry;
+  uint32_t* dense;        // the candidates' keys once more, densely packed in no particular order
   unsigned int capacity;  // blocks
 };
 
@@ -806,9 +816,22 @@ collect_kernel(SparseFuseDev fuse, float* __restrict__ R, int64_t n, int64_t chu
     }
     if (__ballot_sync(0xffffffffu, count != 0) != 0) list_append(s, pool, list, lane, count, idx, val, cur);
   }
-  if (lane == 0) {
-    if (cur.lost != 0) atomicAdd(&s->dropped, cur.lost);
-    if (cur.total != 0) atomicAdd(&s->cand, cur.total);
+  // The cut kernel wants all candidate keys in one flat array (it is a single CTA: a sweep over
+  // the half-empty list blocks cost it 70 us).  Each warp copies the keys of its own list, which
+  // it has just written, to a range it reserves with one atomic.
+  if (lane == 0 && cur.lost != 0) atomicAdd(&s->dropped, cur.lost);
+  const unsigned int total = __shfl_sync(0xffffffffu, cur.total, 0);
+  if (total != 0) {
+    unsigned int base = 0;
+    if (lane == 0) base = atomicAdd(&s->cand, total);
+    base = __shfl_sync(0xffffffffu, base, 0);
+    __syncwarp();   // lane 0's list writes are visible to the other lanes
+    unsigned int done = 0;
+    for (unsigned int b = s->list_head[list]; b != kNoBlock && b < pool.capacity; b = pool.next[b]) {
+      const unsigned int c = pool.count[b];
+      if (lane < int(c)) pool.dense[base + done + lane] = pool.entry[size_t(b) * kBlockEntries + lane].y & 0x7fffffffu;
+      done += c;
+    }
   }
 }
 
@@ -875,7 +898,6 @@ cut_kernel(unsigned int expected, SparseScratch* s, ListPool pool) {
   __shared__ unsigned int sh[kBins];
   __shared__ unsigned int part[kCutThreads];
   __shared__ unsigned int res[2];
-  __shared__ unsigned int nkeys;
   const unsigned int cand = s->cand;
   if (cand <= expected) {
     if (threadIdx.x == 0) {
@@ -884,37 +906,25 @@ cut_kernel(unsigned int expected, SparseScratch* s, ListPool pool) {
     }
     return;
   }
-  const unsigned int used = s->pool_used < pool.capacity ? s->pool_used : pool.capacity;
-  const unsigned int slots = used * kBlockEntries;
   const bool in_smem = cand <= unsigned(kCutSmemKeys);
-  if (threadIdx.x == 0) nkeys = 0;
-  __syncthreads();
   if (in_smem) {
-    // sweep the pool once: four independent loads per thread and iteration
-    for (unsigned int base = 0; base < slots; base += kCutThreads * 4) {
-      uint32_t k[4];
-      bool ok[4];
+    // eight independent loads per thread and iteration
+    for (unsigned int base = 0; base < cand; base += kCutThreads * 8) {
+      uint32_t k[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const unsigned int i = base + u * kCutThreads + threadIdx.x;
-        ok[u] = i < slots && (i & (kBlockEntries - 1)) < pool.count[i / kBlockEntries];
-        k[u] = ok[u] ? (pool.entry[i].y & 0x7fffffffu) : 0u;
+        k[u] = i < cand ? pool.dense[i] : 0u;
       }
-      // one shared-memory atomic per warp and load, not one per key
-      const int lane = threadIdx.x & 31;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const unsigned int m = __ballot_sync(0xffffffffu, ok[u]);
-        if (m == 0) continue;
-        unsigned int at = 0;
-        if (lane == __ffs(m) - 1) at = atomicAdd(&nkeys, unsigned(__popc(m)));
-        at = __shfl_sync(0xffffffffu, at, __ffs(m) - 1);
-        if (ok[u]) keys[at + __popc(m & ((1u << lane) - 1u))] = k[u];
+      for (int u = 0; u < 8; ++u) {
+        const unsigned int i = base + u * kCutThreads + threadIdx.x;
+        if (i < cand) keys[i] = k[u];
       }
     }
     __syncthreads();
   }
-  const unsigned int count = in_smem ? nkeys : slots;
+  const unsigned int count = cand;
   uint32_t prefix = 0;
   unsigned int rank = expected - 1;   // 0-based from the top
   for (int round = 0; round < 3; ++round) {
@@ -927,12 +937,7 @@ cut_kernel(unsigned int expected, SparseScratch* s, ListPool pool) {
       uint32_t key = 0;
       bool live = i < count;
       if (live) {
-        if (in_smem) {
-          key = keys[i];
-        } else {   // more candidates than shared memory holds: read the pool again in every round
-          live = (i & (kBlockEntries - 1)) < pool.count[i / kBlockEntries];
-          if (live) key = pool.entry[i].y & 0x7fffffffu;
-        }
+        key = in_smem ? keys[i] : pool.dense[i];   // more candidates than shared memory holds: from L2
       }
       live = live && prefix_matches(key, round, prefix);
       const int bin = live ? digit_of(key, round) : -1;
@@ -1151,8 +1156,8 @@ inline ListPlan list_plan(int64_t n) {
   p.pool_blocks = entries / kBlockEntries + kMaxLists;
   p.keys_offset = (sizeof(SparseScratch) + 255) / 256 * 256;
   p.pool_offset = (p.keys_offset + size_t(p.key_capacity) * 4 + 255) / 256 * 256;
-  // count[blocks], next[blocks], entry[blocks][16]
-  p.total_bytes = p.pool_offset + size_t(p.pool_blocks) * (8 + kBlockEntries * sizeof(uint2)) + 256;
+  // count[blocks], next[blocks], entry[blocks][16], dense[blocks * 16]
+  p.total_bytes = p.pool_offset + size_t(p.pool_blocks) * (8 + kBlockEntries * (sizeof(uint2) + 4)) + 512;
   return p;
 }
 
@@ -1209,6 +1214,7 @@ cudaError_t sparse_compress_fused(const SparseFuse& fuse, float* R, int64_t n, d
     pool.count = reinterpret_cast<unsigned int*>(pool_base);
     pool.next = pool.count + lp.pool_blocks;
     pool.entry = reinterpret_cast<uint2*>((reinterpret_cast<uintptr_t>(pool.next + lp.pool_blocks) + 127) & ~uintptr_t(127));
+    pool.dense = reinterpret_cast<uint32_t*>(pool.entry + size_t(lp.pool_blocks) * kBlockEntries);
     const int nlists = pl.blocks * (kThreads / 32);
     if (fuse.mode == 2) collect_kernel<2><<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);
     else if (fuse.mode == 1) collect_kernel<1><<<pl.blocks, kThreads, 0, stream>>>(f, R, n, pl.chunk, sample_cnt, s, pool);

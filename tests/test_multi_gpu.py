@@ -21,6 +21,7 @@ def test_engine_and_wrappers_across_gpus(nproc):
     if torch.cuda.device_count() < nproc:
         pytest.skip(f"needs {nproc} GPUs")
     res = _run_workers(nproc, 29540 + nproc)
+    print("\n".join(l for l in res.stdout.splitlines() if l.startswith(("MP_", "NVLS"))))   # shown with -s / -rP
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     for name in ("codec_terngrad", "codec_tbq", "codec_graddrop", "codec_ecq", "codec_dense",
                  "codec_terngrad_device_epoch", "codec_tbq_device_epoch", "codec_terngrad_wide", "codec_tbq_wide",
