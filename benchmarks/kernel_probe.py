@@ -46,13 +46,18 @@ def timed(fn, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="terngrad",
-                    choices=["terngrad", "terngrad_words", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q",
+                    choices=["terngrad", "terngrad_words", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q", "psgd_group_p", "psgd_group_q", "psgd_loop_p", "psgd_loop_q",
                              "psgd_expand", "sgd", "adamw", "terngrad_unpack_apply", "bn_fwd", "bn_bwd",
                              "bias_relu_pool_fwd", "bias_relu_pool_bwd", "add_ln_fwd", "add_ln_bwd", "maxpool_fwd",
                              "maxpool_bwd"])
     ap.add_argument("--mb", type=float, default=64.0)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--world", type=int, default=8, help="payload count for the unpack kernels")
+    ap.add_argument("--graph", type=int, default=0,
+                    help="1: time the op as a CUDA-graph replay (no host work between its launches, as a captured "
+                         "training step runs it)")
+    ap.add_argument("--rows", type=int, default=4096, help="matrix rows for the psgd kernels (columns follow from --mb)")
+    ap.add_argument("--cols", type=int, default=0, help="matrix columns for the psgd kernels (0: from --mb and --rows)")
     args = ap.parse_args()
     n = int(args.mb * (1 << 20) / 4)
     dev = torch.device("cuda", 0)
@@ -102,8 +107,9 @@ def main():
         fn = lambda: ops.ecq_compress(g, r, 1.0, 0.9, 2, 1, out=out)
         traffic = n * (8 + 8 + 4 + 0.25)
     elif k in ("psgd_p", "psgd_q", "psgd_expand"):
-        rows = 4096
-        cols = n // rows
+        rows = args.rows
+        cols = args.cols if args.cols > 0 else n // rows
+        n = rows * cols
         M = torch.randn(rows, cols, device=dev)
         Q = torch.randn(cols, 4, device=dev)
         P = torch.randn(rows, 4, device=dev)
@@ -119,6 +125,24 @@ def main():
             out = torch.zeros(rows * cols, device=dev)
             fn = lambda: ops.psgd_expand_feedback(P, Q, M, out)
             traffic = rows * cols * 12
+    elif k in ("psgd_group_p", "psgd_group_q", "psgd_loop_p", "psgd_loop_q"):
+        # the 19 weight matrices of VGG-19 (16 convolutions as [out, in*9], 3 classifier layers): one grouped
+        # launch ("group") against one launch per matrix ("loop"); --mb is ignored
+        mode = 0 if k.endswith("_p") else 1
+        chans = [(64, 3), (64, 64), (128, 64), (128, 128), (256, 128), (256, 256), (256, 256), (256, 256),
+                 (512, 256), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512)]
+        shapes = [(o, i * 9) for o, i in chans] + [(4096, 25088), (4096, 4096), (1000, 4096)]
+        Ms = [torch.randn(a, b, device=dev) for a, b in shapes]
+        Xs = [torch.randn(b if mode == 0 else a, 4, device=dev) for a, b in shapes]
+        outs = [torch.zeros(a if mode == 0 else b, 4, device=dev) for a, b in shapes]
+        if k.startswith("psgd_group"):
+            fn = lambda: ops.psgd_project_grouped(mode, Ms, Xs, outs)
+        else:
+            def fn():
+                for M, X, o in zip(Ms, Xs, outs):
+                    ops.psgd_project(mode, M, X, [o])
+        traffic = sum(a * b for a, b in shapes) * 4
+        n = traffic // 4
     elif k == "terngrad_unpack_apply":
         # what a training step runs per bucket: decode `world` payloads, average, fused SGD step,
         # zeros left in the gradient bucket
@@ -214,9 +238,19 @@ def main():
         traffic = n * 24
     fn()
     torch.cuda.synchronize()
+    if args.graph:
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            fn()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                fn()
+        torch.cuda.synchronize()
+        fn = graph.replay
     ms = timed(fn, args.iters)
     gbs = traffic / (ms * 1e-3) / 1e9
-    print(json.dumps({"kernel": k, "mb": args.mb, "n": n, "ms": round(ms, 4), "algorithmic_gbs": round(gbs, 1),
+    print(json.dumps({"kernel": k, "mb": round(n * 4 / (1 << 20), 1) if k.startswith("psgd") else args.mb, "n": n,
+                      "graph": args.graph, "ms": round(ms, 4), "algorithmic_gbs": round(gbs, 1),
                       "fraction_of_measured_hbm": round(gbs / hbm, 3), "hbm_gbs_measured_peak": hbm}))
 
 

@@ -160,6 +160,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("powersgd_encode1", &ops::powersgd_encode1);
   m.def("powersgd_encode2", &ops::powersgd_encode2);
   m.def("powersgd_decode", &ops::powersgd_decode);
+  m.def("psgd_project_grouped", &ops::psgd_project_grouped, py::arg("mode"), py::arg("Ms"), py::arg("Xs"), py::arg("outs"));
   m.def("psgd_project", &ops::psgd_project, py::arg("mode"), py::arg("M"), py::arg("X"),
         py::arg("owners"), py::arg("simt") = false);
   m.def("bn_supported", &ops::bn_supported, py::arg("x"));

@@ -320,6 +320,17 @@ cudaError_t psgd_transpose_pad(const float* X, int64_t rows, int r, float* Xt, i
 cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const float* X,
                       const float* Xt, int r, const ReduceTargets& red, int force_simt, int* status,
                       cudaStream_t stream);
+// The same projection for a list of matrices in as few launches as possible (one per 24
+// tensor-core-eligible matrices; the others fall back to psgd_gemm one by one).
+struct PsgdGemmItem {
+  const float* Mat = nullptr;
+  int64_t n = 0, m = 0;
+  const float* X = nullptr;    // [K x r]
+  const float* Xt = nullptr;   // [16 x psgd_kpad(K)], or null: SIMT fallback
+  ReduceTargets red;
+};
+cudaError_t psgd_gemm_grouped(int mode, const PsgdGemmItem* items, int count, int r, int* status,
+                              int* launches, cudaStream_t stream);
 // In-place modified Gram-Schmidt of the n x r matrix P (r <= 16).
 cudaError_t gram_schmidt(float* P, int64_t n, int r, float eps, cudaStream_t stream);
 // approx = P Q^T.  mode 0 (API parity): Mat = approx; residual = grad - Mat[:N]; grad = Mat[:N].

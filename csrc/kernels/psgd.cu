@@ -23,6 +23,9 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <cstring>
+#include <vector>
+#include <algorithm>
 
 #include "kernels.h"
 #include "p2p.cuh"
@@ -38,6 +41,7 @@ constexpr int kBN = 16;      // padded rank (UMMA N)
 constexpr int kBoxK = 32;    // fp32 elements along K of one TMA box = 128 bytes, the swizzle width
 constexpr int kKPad = 64;    // the K extent of the operands is padded to a multiple of this
 constexpr int kGemmThreads = 192;       // warp0 TMA, warp1 MMA, warps 2-5 epilogue
+constexpr int kGemmGroup = 24;          // matrices per grouped launch (descriptors travel as kernel parameters)
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // every barrier wait gives up after 2 s
 constexpr int kTmemCols = 32;
 
@@ -139,24 +143,16 @@ struct OwnerTargets {
 // MODE 1: out[m x r] += Mat^T * X, A tile MN-major (columns of Mat x K along n)
 // Xt is X transposed and zero-padded to [16][k_pad] (K-major B operand).
 template <int MODE, int BK, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 int64_t out_rows, int r, int total_kb, int kb_per_split, OwnerTargets out,
-                 int* status) {
+__device__ __forceinline__ void psgd_gemm_body(const CUtensorMap* map_a_p, const CUtensorMap* map_b_p,
+                                               const float* __restrict__ Mat, int64_t n, int64_t m,
+                                               int64_t out_rows, int r, int tile, int kb_begin, int nkb,
+                                               const OwnerTargets& out, int* status) {
   using Smem = GemmSmem<BK, STAGES>;
   constexpr int kBK = BK, kStages = STAGES, kStageA = Smem::kStageA, kStageB = Smem::kStageB;
   constexpr int kBoxes = BK / kBoxK;   // 128-byte boxes along K per stage
   extern __shared__ uint8_t smem_raw[];
   Smem& s = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
-  // Split-K with a contiguous K range per CTA.  (Dealing the K blocks round-robin, so that the
-  // CTAs sharing a row tile would read neighbouring 128-byte pieces of the same rows at about
-  // the same time, was measured and is slower: 0.52 instead of 0.58 of the copy bandwidth for
-  // M Q at 256 MB, unchanged for M^T P.)
-  const int kb_begin = blockIdx.y * kb_per_split;
-  const int kb_end = min(kb_begin + kb_per_split, total_kb);
-  const int nkb = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -193,15 +189,15 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           // K-major A: one box of 128 rows x 128 bytes per 32 K elements, side by side in K
 #pragma unroll
           for (int j = 0; j < kBoxes; ++j)
-            tma_load_2d(s.a[st] + j * (kBM * 128), &map_a, k0 + j * kBoxK, tile * kBM, &s.full[st]);
+            tma_load_2d(s.a[st] + j * (kBM * 128), map_a_p, k0 + j * kBoxK, tile * kBM, &s.full[st]);
         } else {
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            tma_load_2d(s.a[st] + j * (kBK * 128), &map_a, tile * kBM + j * 32, k0, &s.full[st]);
+            tma_load_2d(s.a[st] + j * (kBK * 128), map_a_p, tile * kBM + j * 32, k0, &s.full[st]);
         }
 #pragma unroll
         for (int j = 0; j < kBoxes; ++j)
-          tma_load_2d(s.b[st] + j * (kBN * 128), &map_b, k0 + j * kBoxK, 0, &s.full[st]);
+          tma_load_2d(s.b[st] + j * (kBN * 128), map_b_p, k0 + j * kBoxK, 0, &s.full[st]);
       }
     } else if (warp == 1 && lane == 0) {
       // ---------------- MMA issuer
@@ -287,6 +283,52 @@ psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols)
                  : "memory");
   }
+}
+
+// One matrix per launch: grid = (row tiles, K splits), a contiguous K range per CTA.  (Dealing
+// the K blocks round-robin, so that the CTAs sharing a row tile would read neighbouring 128-byte
+// pieces of the same rows at about the same time, was measured and is slower.)
+template <int MODE, int BK, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+psgd_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const float* __restrict__ Mat, int64_t n, int64_t m,
+                 int64_t out_rows, int r, int total_kb, int kb_per_split, const __grid_constant__ OwnerTargets out,
+                 int* status) {
+  const int kb_begin = blockIdx.y * kb_per_split;
+  const int kb_end = min(kb_begin + kb_per_split, total_kb);
+  psgd_gemm_body<MODE, BK, STAGES>(&map_a, &map_b, Mat, n, m, out_rows, r, int(blockIdx.x), kb_begin,
+                                          kb_end - kb_begin, out, status);
+}
+
+// All matrices of a step in one launch.  A kernel of this kind spends 7-8 us ramping up and
+// draining whatever its size (a 9 MB convolution matrix streams in 1.5 us), so a model's tens of
+// matrices are projected by ONE grid: CTA u works on unit u of a list that runs through the
+// matrices (largest units first), a unit being one row tile x one K range of one matrix.
+struct GroupedMat {
+  alignas(64) CUtensorMap map_a;
+  alignas(64) CUtensorMap map_b;
+  const float* Mat;
+  int64_t n, m, out_rows;
+  OwnerTargets out;
+  int unit_begin, tiles, kbps, total_kb;
+};
+struct GroupedGemm {
+  int count;
+  int r;
+  GroupedMat mat[kGemmGroup];
+};
+template <int MODE, int BK, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+psgd_gemm_grouped_kernel(const __grid_constant__ GroupedGemm g, int* status) {
+  int u = int(blockIdx.x), i = 0;
+  while (i + 1 < g.count && u >= g.mat[i + 1].unit_begin) ++i;
+  const GroupedMat& M = g.mat[i];
+  u -= M.unit_begin;
+  const int tile = u % M.tiles, split = u / M.tiles;
+  const int kb_begin = split * M.kbps;
+  const int kb_end = min(kb_begin + M.kbps, M.total_kb);
+  psgd_gemm_body<MODE, BK, STAGES>(&M.map_a, &M.map_b, M.Mat, M.n, M.m, M.out_rows, g.r, tile, kb_begin,
+                                          kb_end - kb_begin, M.out, status);
 }
 
 // X[rows x r] row-major -> Xt[16][rows_pad], zero padded.
@@ -560,8 +602,10 @@ struct GemmVariant {
   int bk, stages;
   size_t smem_bytes;
 };
+// Read on every call (two getenv look-ups per launch) so that a test or a probe can switch
+// variants inside one process.
 GemmVariant gemm_variant() {
-  static const GemmVariant v = [] {
+  {
     int bk = 32, stages = 6;
     if (const char* e = std::getenv("HIPRESS_PSGD_BK")) bk = std::atoi(e);
     if (const char* e = std::getenv("HIPRESS_PSGD_STAGES")) stages = std::atoi(e);
@@ -570,8 +614,7 @@ GemmVariant gemm_variant() {
     if (bk == 64 && stages == 3) return GemmVariant{64, 3, sizeof(GemmSmem<64, 3>)};
     if (bk == 64 && stages == 4) return GemmVariant{64, 4, sizeof(GemmSmem<64, 4>)};
     return GemmVariant{64, 6, sizeof(GemmSmem<64, 6>)};
-  }();
-  return v;
+  }
 }
 
 OwnerTargets owners_of(const ReduceTargets& red, int64_t rows) {
@@ -653,13 +696,13 @@ cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const fl
     cudaError_t e = cudaFuncSetAttribute(psgd_gemm_kernel<MODE, BK, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                          int(smem));                                                                 \
     if (e != cudaSuccess) return e;                                                                                  \
-    psgd_gemm_kernel<MODE, BK, ST><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, out_rows, r, total_kb, kbps,  \
-                                                                         out, status);                               \
+    psgd_gemm_kernel<MODE, BK, ST><<<grid, kGemmThreads, smem, stream>>>(map_a, map_b, Mat, n, m, out_rows, r,        \
+                                                                         total_kb, kbps, out, status);               \
   } while (0)
-#define HP_GEMM_MODE(BK, ST)      \
-  do {                            \
+#define HP_GEMM_MODE(BK, ST)           \
+  do {                                 \
     if (mode == 0) HP_GEMM(0, BK, ST); \
-    else HP_GEMM(1, BK, ST);      \
+    else HP_GEMM(1, BK, ST);           \
   } while (0)
   if (var.bk == 32 && var.stages == 6) HP_GEMM_MODE(32, 6);
   else if (var.bk == 32 && var.stages == 4) HP_GEMM_MODE(32, 4);
@@ -669,6 +712,110 @@ cudaError_t psgd_gemm(int mode, const float* Mat, int64_t n, int64_t m, const fl
 #undef HP_GEMM_MODE
 #undef HP_GEMM
   return cudaGetLastError();
+}
+
+cudaError_t psgd_gemm_grouped(int mode, const PsgdGemmItem* items, int count, int r, int* status,
+                              int* launches, cudaStream_t stream) {
+  if (r < 1 || r > kBN || count < 0) return cudaErrorInvalidValue;
+  const GemmVariant var = gemm_variant();
+  const size_t smem = var.smem_bytes + 1024;
+  int per_sm = int((227 * 1024) / smem);
+  per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+  const int resident = 148 * per_sm;
+
+  struct Plan {
+    int item;
+    int tiles, total_kb, kbps, splits;
+    double unit_bytes;
+  };
+  std::vector<Plan> plans;
+  double total_bytes = 0;
+  for (int i = 0; i < count; ++i) {
+    const PsgdGemmItem& it = items[i];
+    if (it.red.world < 1 || it.red.world > kMaxWorld || it.n < 1 || it.m < 1) return cudaErrorInvalidValue;
+    if (it.Xt == nullptr || !psgd_tensor_core_eligible(it.Mat, it.n, it.m)) {
+      const cudaError_t e = psgd_gemm(mode, it.Mat, it.n, it.m, it.X, it.Xt, r, it.red, 1, status, stream);
+      if (e != cudaSuccess) return e;
+      if (launches) ++*launches;
+      continue;
+    }
+    const int64_t out_rows = mode == 0 ? it.n : it.m;
+    const int64_t K = mode == 0 ? it.m : it.n;
+    Plan pl{};
+    pl.item = i;
+    pl.tiles = int((out_rows + kBM - 1) / kBM);
+    pl.total_kb = int(psgd_kpad(K) / var.bk);
+    plans.push_back(pl);
+    total_bytes += double(it.n) * double(it.m) * 4.0;
+  }
+  if (plans.empty()) return cudaSuccess;
+  // Units of about equal size, one wave of resident CTAs in total where the row tiles allow it.
+  const double target = total_bytes / double(resident);
+  for (Plan& pl : plans) {
+    const PsgdGemmItem& it = items[pl.item];
+    const double bytes = double(it.n) * double(it.m) * 4.0;
+    int64_t units = int64_t(bytes / target + 0.5);
+    int splits = int(units / pl.tiles);
+    const int max_splits = pl.total_kb / 4 > 0 ? pl.total_kb / 4 : 1;
+    splits = splits < 1 ? 1 : (splits > max_splits ? max_splits : splits);
+    pl.kbps = (pl.total_kb + splits - 1) / splits;
+    pl.splits = (pl.total_kb + pl.kbps - 1) / pl.kbps;
+    pl.unit_bytes = bytes / double(pl.tiles) / double(pl.splits);
+  }
+  // largest units first: the small ones fill the tail of the grid
+  std::stable_sort(plans.begin(), plans.end(), [](const Plan& a, const Plan& b) { return a.unit_bytes > b.unit_bytes; });
+
+  for (size_t base = 0; base < plans.size(); base += kGemmGroup) {
+    GroupedGemm g{};
+    g.count = int(std::min<size_t>(kGemmGroup, plans.size() - base));
+    g.r = r;
+    int units = 0;
+    for (int j = 0; j < g.count; ++j) {
+      const Plan& pl = plans[base + size_t(j)];
+      const PsgdGemmItem& it = items[pl.item];
+      GroupedMat& gm = g.mat[j];
+      const int64_t out_rows = mode == 0 ? it.n : it.m;
+      const int64_t K = mode == 0 ? it.m : it.n;
+      const bool ok_a = mode == 0 ? make_map(&gm.map_a, it.Mat, it.m, it.n, kBoxK, kBM, CU_TENSOR_MAP_SWIZZLE_128B)
+                                  : make_map(&gm.map_a, it.Mat, it.m, it.n, 32, var.bk,
+                                             CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B);
+      const bool ok_b = make_map(&gm.map_b, it.Xt, psgd_kpad(K), kBN, kBoxK, kBN, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (!ok_a || !ok_b) return cudaErrorInvalidValue;
+      gm.Mat = it.Mat;
+      gm.n = it.n;
+      gm.m = it.m;
+      gm.out_rows = out_rows;
+      gm.out = owners_of(it.red, out_rows);
+      gm.unit_begin = units;
+      gm.tiles = pl.tiles;
+      gm.kbps = pl.kbps;
+      gm.total_kb = pl.total_kb;
+      units += pl.tiles * pl.splits;
+    }
+#define HP_GROUPED(MODE, BK, ST)                                                                        \
+  do {                                                                                                  \
+    cudaError_t e = cudaFuncSetAttribute(psgd_gemm_grouped_kernel<MODE, BK, ST>,                        \
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));      \
+    if (e != cudaSuccess) return e;                                                                     \
+    psgd_gemm_grouped_kernel<MODE, BK, ST><<<unsigned(units), kGemmThreads, smem, stream>>>(g, status); \
+  } while (0)
+#define HP_GROUPED_MODE(BK, ST)           \
+  do {                                    \
+    if (mode == 0) HP_GROUPED(0, BK, ST); \
+    else HP_GROUPED(1, BK, ST);           \
+  } while (0)
+    if (var.bk == 32 && var.stages == 6) HP_GROUPED_MODE(32, 6);
+    else if (var.bk == 32 && var.stages == 4) HP_GROUPED_MODE(32, 4);
+    else if (var.bk == 64 && var.stages == 3) HP_GROUPED_MODE(64, 3);
+    else if (var.bk == 64 && var.stages == 4) HP_GROUPED_MODE(64, 4);
+    else HP_GROUPED_MODE(64, 6);
+#undef HP_GROUPED_MODE
+#undef HP_GROUPED
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+  }
+  return cudaSuccess;
 }
 
 // ---------------------------------------------------------------- batched small kernels

@@ -454,6 +454,47 @@ void psgd_project(int64_t mode, const torch::Tensor& M, const torch::Tensor& X,
   }
 }
 
+void psgd_project_grouped(int64_t mode, const std::vector<torch::Tensor>& Ms, const std::vector<torch::Tensor>& Xs,
+                          const std::vector<torch::Tensor>& outs) {
+  TORCH_CHECK(mode == 0 || mode == 1, "mode must be 0 or 1");
+  TORCH_CHECK(!Ms.empty() && Ms.size() == Xs.size() && Ms.size() == outs.size(), "one X and one output per matrix");
+  TORCH_CHECK(Ms[0].is_cuda(), "CUDA tensors expected");
+  c10::cuda::CUDAGuard guard(Ms[0].device());
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int64_t r = Xs[0].size(1);
+  TORCH_CHECK(r >= 1 && r <= 16, "rank must be between 1 and 16");
+  std::vector<cuda::PsgdGemmItem> items(Ms.size());
+  std::vector<cuda::PsgdTransposeItem> transposes;
+  std::vector<torch::Tensor> keep;
+  for (size_t i = 0; i < Ms.size(); ++i) {
+    const torch::Tensor& M = Ms[i];
+    check_f32(M, "M");
+    check_f32(Xs[i], "X");
+    check_f32(outs[i], "out");
+    TORCH_CHECK(M.dim() == 2 && Xs[i].dim() == 2 && Xs[i].size(1) == r, "matrices of one rank expected");
+    const int64_t n = M.size(0), m = M.size(1);
+    const int64_t k = mode == 0 ? m : n, out_rows = mode == 0 ? n : m;
+    TORCH_CHECK(Xs[i].size(0) == k && outs[i].numel() == out_rows * r, "shape mismatch at matrix ", i);
+    cuda::PsgdGemmItem& it = items[i];
+    it.Mat = M.data_ptr<float>();
+    it.n = n;
+    it.m = m;
+    it.X = Xs[i].data_ptr<float>();
+    it.red.world = 1;
+    it.red.dst[0] = outs[i].data_ptr<float>();
+    if (cuda::psgd_tensor_core_eligible(it.Mat, n, m)) {
+      const int64_t kp = cuda::psgd_kpad(k);
+      keep.push_back(torch::empty({16, kp}, M.options()));
+      it.Xt = keep.back().data_ptr<float>();
+      transposes.push_back(cuda::PsgdTransposeItem{it.X, keep.back().data_ptr<float>(), k, kp, int(r)});
+    }
+  }
+  if (!transposes.empty())
+    HP_CHECK_CUDA(cuda::psgd_transpose_pad_batched(transposes.data(), int(transposes.size()), stream));
+  HP_CHECK_CUDA(cuda::psgd_gemm_grouped(int(mode), items.data(), int(items.size()), int(r), status_word_for(Ms[0]),
+                                        nullptr, stream));
+}
+
 void gram_schmidt(torch::Tensor P, double eps) {
   check_f32(P, "P");
   TORCH_CHECK(P.dim() == 2 && P.size(1) >= 1 && P.size(1) <= 16, "P must be n x r with r <= 16");

@@ -69,6 +69,10 @@ void powersgd_decode(const torch::Tensor& P, const torch::Tensor& Q, torch::Tens
 // local tensor before accumulating.  simt forces the non-tensor-core kernel.
 void psgd_project(int64_t mode, const torch::Tensor& M, const torch::Tensor& X,
                   const std::vector<torch::Tensor>& owners, bool simt);
+// outs[i] += Ms[i] Xs[i] (mode 0) or Ms[i]^T Xs[i] (mode 1) for a list of CUDA matrices, all tensor-core
+// eligible ones in one grid.
+void psgd_project_grouped(int64_t mode, const std::vector<torch::Tensor>& Ms, const std::vector<torch::Tensor>& Xs,
+                          const std::vector<torch::Tensor>& outs);
 void gram_schmidt(torch::Tensor P, double eps);
 // grad_out[:N] = post_scale * P Q^T ; M -= P Q^T   (error feedback stays in M)
 void psgd_expand_feedback(const torch::Tensor& P, const torch::Tensor& Q, torch::Tensor M,

@@ -1,8 +1,11 @@
 #include "ddp_engine.h"
 
 #include <algorithm>
+#include <cstdio>
 #include <cstring>
 #include <stdexcept>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include "../common/codec_math.h"
 
@@ -18,6 +21,22 @@ void check(cudaError_t e, const char* what) {
 int64_t round_up(int64_t v, int64_t a) { return (v + a - 1) / a * a; }
 
 constexpr size_t kScratchBytes = 256 * 1024;
+
+// Named range on the calling thread's timeline for an attached tool; a no-op test when tracing is off.
+struct TraceRange {
+  bool on;
+  TraceRange(bool enabled, const char* what, int bucket) : on(enabled) {
+    if (!on) return;
+    char name[48];
+    snprintf(name, sizeof(name), "hipress %s b%d", what, bucket);
+    nvtxRangePushA(name);
+  }
+  ~TraceRange() {
+    if (on) nvtxRangePop();
+  }
+  TraceRange(const TraceRange&) = delete;
+  TraceRange& operator=(const TraceRange&) = delete;
+};
 
 }  // namespace
 
@@ -387,6 +406,7 @@ void DdpEngine::issue_adamw(int b, cudaStream_t stream, int clear_grad) {
 // slot [rank] of the shard's owner -- one launch (two for TernGrad) over the whole bucket, the
 // kernels switching destination from shard to shard (PushTargets::shard_elems).
 void DdpEngine::issue_shard_push(int b, int worker) {
+  TraceRange range(cfg_.trace != 0, "shard push", b);
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
@@ -427,6 +447,7 @@ void DdpEngine::issue_shard_push(int b, int worker) {
 // Phase 2: the owner decodes the `world` payloads of its shard in one pass, averages, and
 // re-compresses the average with its own residual into slot [rank] of every rank's phase-2 area.
 void DdpEngine::issue_shard_reduce(int b, int worker) {
+  TraceRange range(cfg_.trace != 0, "shard reduce", b);
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
@@ -496,6 +517,7 @@ void DdpEngine::issue_shard_reduce(int b, int worker) {
 // Phase 3: one pass over the whole bucket that decodes every shard from its owner's payload
 // (UnpackSources::shard_elems) and applies the update.
 void DdpEngine::issue_shard_final(int b, int worker) {
+  TraceRange range(cfg_.trace != 0, "shard final", b);
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
@@ -565,6 +587,7 @@ void DdpEngine::reduce_step() {
 }
 
 void DdpEngine::issue_push(int b, int worker) {
+  TraceRange range(cfg_.trace != 0, "push", b);
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];
@@ -654,6 +677,7 @@ void DdpEngine::issue_push(int b, int worker) {
 }
 
 void DdpEngine::issue_recv(int b, int worker) {
+  TraceRange range(cfg_.trace != 0, "recv", b);
   WorkerCtx& w = workers_[static_cast<size_t>(worker)];
   const BucketDesc& B = buckets_[static_cast<size_t>(b)];
   const BucketLayout& L = layouts_[static_cast<size_t>(b)];

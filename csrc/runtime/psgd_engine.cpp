@@ -58,13 +58,23 @@ cudaError_t PsgdEngine::project_p(int parity, cudaStream_t stream) {
     PSGD_TRY(cuda::psgd_transpose_pad_batched(tq_.data(), int(tq_.size()), stream));
     launches_ += batches(tq_.size());
   }
-  for (const PsgdMatrix& mat : mats_) {
-    cuda::ReduceTargets red;
-    red.world = world_;
-    for (int p = 0; p < world_; ++p) red.dst[p] = mat.accP[parity][p];
-    PSGD_TRY(cuda::psgd_gemm(0, mat.M, mat.n, mat.m, mat.Q, mat.Qt, r_, red, mat.Qt ? 0 : 1, status_, stream));
-    ++launches_;
+  // every matrix's P += M Q in one grid (a launch per matrix costs more in ramp-up and drain
+  // than the small matrices take to stream)
+  std::vector<cuda::PsgdGemmItem> items(mats_.size());
+  for (size_t i = 0; i < mats_.size(); ++i) {
+    const PsgdMatrix& mat = mats_[i];
+    cuda::PsgdGemmItem& it = items[i];
+    it.Mat = mat.M;
+    it.n = mat.n;
+    it.m = mat.m;
+    it.X = mat.Q;
+    it.Xt = mat.Qt;
+    it.red.world = world_;
+    for (int p = 0; p < world_; ++p) it.red.dst[p] = mat.accP[parity][p];
   }
+  int launched = 0;
+  PSGD_TRY(cuda::psgd_gemm_grouped(0, items.data(), int(items.size()), r_, status_, &launched, stream));
+  launches_ += launched;
   return cudaSuccess;
 }
 
@@ -79,13 +89,21 @@ cudaError_t PsgdEngine::project_q(int parity, cudaStream_t stream) {
     PSGD_TRY(cuda::psgd_transpose_pad_batched(tp_.data(), int(tp_.size()), stream));
     launches_ += batches(tp_.size());
   }
-  for (const PsgdMatrix& mat : mats_) {
-    cuda::ReduceTargets red;
-    red.world = world_;
-    for (int p = 0; p < world_; ++p) red.dst[p] = mat.accQ[parity][p];
-    PSGD_TRY(cuda::psgd_gemm(1, mat.M, mat.n, mat.m, mat.P, mat.Pt, r_, red, mat.Pt ? 0 : 1, status_, stream));
-    ++launches_;
+  std::vector<cuda::PsgdGemmItem> items(mats_.size());
+  for (size_t i = 0; i < mats_.size(); ++i) {
+    const PsgdMatrix& mat = mats_[i];
+    cuda::PsgdGemmItem& it = items[i];
+    it.Mat = mat.M;
+    it.n = mat.n;
+    it.m = mat.m;
+    it.X = mat.P;
+    it.Xt = mat.Pt;
+    it.red.world = world_;
+    for (int p = 0; p < world_; ++p) it.red.dst[p] = mat.accQ[parity][p];
   }
+  int launched = 0;
+  PSGD_TRY(cuda::psgd_gemm_grouped(1, items.data(), int(items.size()), r_, status_, &launched, stream));
+  launches_ += launched;
   return cudaSuccess;
 }
 

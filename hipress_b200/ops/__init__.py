@@ -31,7 +31,7 @@ __all__ = [
     "graddrop_compress", "dgc_compress", "sparse_decompress", "sparse_payload_k",
     "ecq_compress", "ecq_decompress",
     "powersgd_encode1", "powersgd_encode2", "powersgd_decode",
-    "psgd_project", "gram_schmidt", "psgd_expand_feedback", "read_status",
+    "psgd_project", "psgd_project_grouped", "gram_schmidt", "psgd_expand_feedback", "read_status",
     "hp_cuda_tbq", "hp_cuda_tbqr", "hp_cuda_terngrad", "hp_cuda_terngradr", "hp_cuda_gd",
     "hp_cuda_gdr", "hp_cuda_powersgd_encode1", "hp_cuda_powersgd_encode2", "hp_cuda_powersgd_decode",
 ]
@@ -191,6 +191,14 @@ def powersgd_encode2(P, M, Q):
 def powersgd_decode(P, Q, M, residual, grad):
     """``M = P Q^T; residual = grad - M[:N]; grad = M[:N]`` (ref powersgd_body.h:54-78)."""
     _C.powersgd_decode(P, Q, M, residual.view(-1), grad.view(-1))
+
+
+def psgd_project_grouped(mode: int, Ms: Sequence[torch.Tensor], Xs: Sequence[torch.Tensor],
+                         outs: Sequence[torch.Tensor]) -> None:
+    """outs[i] += Ms[i] @ Xs[i] (mode 0) or Ms[i].T @ Xs[i] (mode 1) for a list of CUDA matrices of one rank:
+    every tensor-core-eligible matrix of the list is projected by the same grid (what the PowerSGD step
+    driver launches per phase).  Reference: one `mm` per matrix, powersgd_body.h:28, 49."""
+    _C.psgd_project_grouped(int(mode), list(Ms), list(Xs), list(outs))
 
 
 def psgd_project(mode: int, M: torch.Tensor, X: torch.Tensor, owners: Sequence[torch.Tensor],

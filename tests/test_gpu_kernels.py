@@ -265,6 +265,51 @@ def test_psgd_project_matches_fp64(n, m, r, simt):
     assert ops.read_status(M) == 0
 
 
+@pytest.mark.parametrize("bk,stages", [(32, 4), (64, 3), (64, 4)])
+@pytest.mark.parametrize("n,m,r", [(128, 128, 4), (300, 1000, 4), (1000, 4096, 4), (130, 36, 4), (512, 4608, 2)])
+def test_psgd_project_variants_match_fp64(monkeypatch, bk, stages, n, m, r):
+    """Every pipeline shape of the tensor-core projection (one or two 128-byte boxes per row and stage, ring
+    depth) gives the same TF32-level result."""
+    monkeypatch.setenv("HIPRESS_PSGD_BK", str(bk))
+    monkeypatch.setenv("HIPRESS_PSGD_STAGES", str(stages))
+    torch.manual_seed(n + m + r)
+    M = torch.randn(n, m, device="cuda")
+    Q = torch.randn(m, r, device="cuda")
+    P = torch.zeros(n, r, device="cuda")
+    ops.psgd_project(0, M, Q, [P])
+    ref = M.double() @ Q.double()
+    assert (P.double() - ref).abs().max().item() <= 5e-3 * (m ** 0.5)
+    Pn = torch.randn(n, r, device="cuda")
+    Qo = torch.zeros(m, r, device="cuda")
+    ops.psgd_project(1, M, Pn, [Qo])
+    ref = M.double().T @ Pn.double()
+    assert (Qo.double() - ref).abs().max().item() <= 5e-3 * (n ** 0.5)
+    assert ops.read_status(M) == 0
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("count", [1, 5, 30])
+def test_psgd_project_grouped_matches_fp64(mode, count):
+    """One grid over a list of matrices (mixed sizes, ragged tiles, one SIMT-only shape, more matrices than a
+    launch holds) equals the per-matrix products."""
+    torch.manual_seed(count + mode)
+    shapes = [(64, 576), (512, 4608), (300, 1000), (128, 1152), (77, 61), (1000, 4096), (256, 2304), (130, 36)]
+    Ms, Xs, outs, refs = [], [], [], []
+    for i in range(count):
+        n, m = shapes[i % len(shapes)]
+        M = torch.randn(n, m, device="cuda")
+        X = torch.randn(m if mode == 0 else n, 4, device="cuda")
+        Ms.append(M)
+        Xs.append(X)
+        outs.append(torch.zeros(n if mode == 0 else m, 4, device="cuda"))
+        refs.append(M.double() @ X.double() if mode == 0 else M.double().T @ X.double())
+    ops.psgd_project_grouped(mode, Ms, Xs, outs)
+    for M, o, ref in zip(Ms, outs, refs):
+        k = M.shape[1] if mode == 0 else M.shape[0]
+        assert (o.double() - ref).abs().max().item() <= 5e-3 * (k ** 0.5), tuple(M.shape)
+    assert ops.read_status(Ms[0]) == 0
+
+
 def test_psgd_project_relative_error_tf32():
     torch.manual_seed(0)
     n, m, r = 1024, 4096, 4
