@@ -152,20 +152,26 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
     all_objs = cu_objs + plain_objs + torch_objs
     newest_obj = max(Path(o).stat().st_mtime for o in all_objs)
     if not ext.exists() or ext.stat().st_mtime < newest_obj:
-        cmd = ["g++", "-shared", "-o", str(ext), *all_objs]
+        # link under a temporary name and rename: a reader (an import in another process, a copy
+        # of the tree) never sees a half-written library
+        tmp = ext.with_name(ext.name + ".tmp")
+        cmd = ["g++", "-shared", "-o", str(tmp), *all_objs]
         for l in lib:
             cmd += ["-L", l, f"-Wl,-rpath,{l}"]
         cmd += ["-L", f"{cuda_home}/lib64", f"-Wl,-rpath,{cuda_home}/lib64",
                 "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
                 "-lcudart", "-ldl", "-lpthread"]
         _run(cmd)
+        os.replace(tmp, ext)
 
     # torch-free C ABI library (kernels + CPU codecs + c_api)
     clib = PKG / "libhipress_kernels.so"
     c_objs = cu_objs + plain_objs
     if c_objs and (not clib.exists() or clib.stat().st_mtime < max(Path(o).stat().st_mtime for o in c_objs)):
-        _run(["g++", "-shared", "-o", str(clib), *c_objs, "-L", f"{cuda_home}/lib64",
+        tmp = clib.with_name(clib.name + ".tmp")
+        _run(["g++", "-shared", "-o", str(tmp), *c_objs, "-L", f"{cuda_home}/lib64",
               f"-Wl,-rpath,{cuda_home}/lib64", "-lcudart", "-ldl", "-lpthread"])
+        os.replace(tmp, clib)
     return ext
 
 
