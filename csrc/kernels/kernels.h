@@ -339,6 +339,20 @@ cudaError_t psgd_expand_residual(const float* P, const float* Q, int64_t n, int6
                                  float* Mat, float* residual, float* grad, int64_t N, int mode,
                                  float post_scale, cudaStream_t stream);
 
+// psgd_expand_sgd for a list of matrices in as few launches as possible (one grid per 32 matrices
+// that take the vectorised form; the others one by one).  `common` carries lr / momentum / weight
+// decay / first_step; param and momentum come from the items.
+struct PsgdExpandItem {
+  const float* P = nullptr;
+  const float* Q = nullptr;
+  int64_t n = 0, m = 0, N = 0;
+  float* Mat = nullptr;
+  float* param = nullptr;
+  float* momentum = nullptr;
+};
+cudaError_t psgd_expand_sgd_grouped(const PsgdExpandItem* items, int count, int r, float post_scale,
+                                    const SgdApply& common, int* launches, cudaStream_t stream);
+
 // Batched forms of the small per-matrix kernels: one launch per kPsgdBatch matrices.
 constexpr int kPsgdBatch = 32;
 struct PsgdTransposeItem {

@@ -475,18 +475,19 @@ expand_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t 
 // columns in registers, reads P rows as broadcasts, and touches Mat / grad / param / momentum
 // with 16-byte accesses only (no per-element division).
 template <int MODE, int R>
-__global__ void __launch_bounds__(256)
-expand_rows_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t n, int64_t m,
-                   float* __restrict__ Mat, float* __restrict__ residual, float* __restrict__ grad,
-                   int64_t N, float scale, SgdApply apply, int rows_per_cta) {
-  const int64_t col = (int64_t(blockIdx.x) * 256 + threadIdx.x) * 4;
+__device__ __forceinline__ void expand_rows_body(const float* __restrict__ P, const float* __restrict__ Q, int64_t n,
+                                                 int64_t m, float* __restrict__ Mat, float* __restrict__ residual,
+                                                 float* __restrict__ grad, int64_t N, float scale,
+                                                 const SgdApply& apply, int rows_per_cta, int col_block,
+                                                 int row_block) {
+  const int64_t col = (int64_t(col_block) * 256 + threadIdx.x) * 4;
   if (col >= m) return;
   float q[4][R];
 #pragma unroll
   for (int j = 0; j < 4; ++j)
 #pragma unroll
     for (int c = 0; c < R; ++c) q[j][c] = Q[(col + j) * R + c];
-  const int64_t r0 = int64_t(blockIdx.y) * rows_per_cta;
+  const int64_t r0 = int64_t(row_block) * rows_per_cta;
   const int64_t r1 = min(r0 + rows_per_cta, n);
   for (int64_t i = r0; i < r1; ++i) {
     float p[R];
@@ -536,6 +537,47 @@ expand_rows_kernel(const float* __restrict__ P, const float* __restrict__ Q, int
       }
     }
   }
+}
+
+template <int MODE, int R>
+__global__ void __launch_bounds__(256)
+expand_rows_kernel(const float* __restrict__ P, const float* __restrict__ Q, int64_t n, int64_t m,
+                   float* __restrict__ Mat, float* __restrict__ residual, float* __restrict__ grad,
+                   int64_t N, float scale, SgdApply apply, int rows_per_cta) {
+  expand_rows_body<MODE, R>(P, Q, n, m, Mat, residual, grad, N, scale, apply, rows_per_cta, int(blockIdx.x),
+                            int(blockIdx.y));
+}
+
+// The expand + SGD pass (mode 2) of every matrix of a step in one grid, for the same reason as the
+// grouped projections: CTA u works on unit u (a 1024-column strip x a band of rows of one matrix).
+constexpr int kExpandGroup = 32;
+struct ExpandMat {
+  const float* P;
+  const float* Q;
+  int64_t n, m, N;
+  float* Mat;
+  float* param;
+  float* momentum;
+  int unit_begin, col_blocks, rows_per;
+};
+struct GroupedExpand {
+  int count;
+  float scale;
+  SgdApply apply;   // lr / momentum / weight decay / first_step shared; param and momentum per matrix
+  ExpandMat mat[kExpandGroup];
+};
+template <int R>
+__global__ void __launch_bounds__(256)
+expand_rows_grouped_kernel(const __grid_constant__ GroupedExpand g) {
+  int u = int(blockIdx.x), i = 0;
+  while (i + 1 < g.count && u >= g.mat[i + 1].unit_begin) ++i;
+  const ExpandMat& M = g.mat[i];
+  u -= M.unit_begin;
+  SgdApply apply = g.apply;
+  apply.param = M.param;
+  apply.momentum = M.momentum;
+  expand_rows_body<2, R>(M.P, M.Q, M.n, M.m, M.Mat, nullptr, nullptr, M.N, g.scale, apply, M.rows_per,
+                         u % M.col_blocks, u / M.col_blocks);
 }
 
 template <int MODE>
@@ -977,6 +1019,86 @@ cudaError_t psgd_expand_sgd(const float* P, const float* Q, int64_t n, int64_t m
   if (blocks > 148 * 8) blocks = 148 * 8;
   expand_kernel<2><<<int(blocks), 256, 0, stream>>>(P, Q, n, m, r, Mat, nullptr, nullptr, N, post_scale, apply);
   return cudaGetLastError();
+}
+
+cudaError_t psgd_expand_sgd_grouped(const PsgdExpandItem* items, int count, int r, float post_scale,
+                                    const SgdApply& common, int* launches, cudaStream_t stream) {
+  if (count < 0 || r < 1 || r > kBN) return cudaErrorInvalidValue;
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  struct Plan {
+    int item, col_blocks, rows_per, row_blocks;
+    double unit_elems;
+  };
+  std::vector<Plan> plans;
+  double total = 0;
+  for (int i = 0; i < count; ++i) {
+    const PsgdExpandItem& it = items[i];
+    if (it.n < 1 || it.m < 1 || it.N > it.n * it.m || it.param == nullptr || it.momentum == nullptr)
+      return cudaErrorInvalidValue;
+    const bool rows_form = (it.m & 3) == 0 && al(it.Mat) && al(it.param) && al(it.momentum) &&
+                           (r == 1 || r == 2 || r == 4 || r == 8);
+    if (!rows_form) {
+      SgdApply a = common;
+      a.param = it.param;
+      a.momentum = it.momentum;
+      const cudaError_t e = psgd_expand_sgd(it.P, it.Q, it.n, it.m, r, it.Mat, it.N, post_scale, a, stream);
+      if (e != cudaSuccess) return e;
+      if (launches) ++*launches;
+      continue;
+    }
+    Plan pl{};
+    pl.item = i;
+    pl.col_blocks = int((it.m / 4 + 255) / 256);
+    plans.push_back(pl);
+    total += double(it.n) * double(it.m);
+  }
+  if (plans.empty()) return cudaSuccess;
+  const double target_ctas = 148.0 * 8.0;
+  for (Plan& pl : plans) {
+    const PsgdExpandItem& it = items[pl.item];
+    const double share = double(it.n) * double(it.m) / total * target_ctas;
+    int64_t row_blocks = int64_t(share / double(pl.col_blocks) + 0.5);
+    const int64_t most = (it.n + 7) / 8;
+    row_blocks = row_blocks < 1 ? 1 : (row_blocks > most ? most : row_blocks);
+    pl.rows_per = int((it.n + row_blocks - 1) / row_blocks);
+    pl.row_blocks = int((it.n + pl.rows_per - 1) / pl.rows_per);
+    pl.unit_elems = double(pl.rows_per) * double(it.m < 1024 ? it.m : 1024);
+  }
+  std::stable_sort(plans.begin(), plans.end(), [](const Plan& a, const Plan& b) { return a.unit_elems > b.unit_elems; });
+  for (size_t base = 0; base < plans.size(); base += kExpandGroup) {
+    GroupedExpand g{};
+    g.count = int(std::min<size_t>(kExpandGroup, plans.size() - base));
+    g.scale = post_scale;
+    g.apply = common;
+    int units = 0;
+    for (int j = 0; j < g.count; ++j) {
+      const Plan& pl = plans[base + size_t(j)];
+      const PsgdExpandItem& it = items[pl.item];
+      ExpandMat& em = g.mat[j];
+      em.P = it.P;
+      em.Q = it.Q;
+      em.n = it.n;
+      em.m = it.m;
+      em.N = it.N;
+      em.Mat = it.Mat;
+      em.param = it.param;
+      em.momentum = it.momentum;
+      em.unit_begin = units;
+      em.col_blocks = pl.col_blocks;
+      em.rows_per = pl.rows_per;
+      units += pl.col_blocks * pl.row_blocks;
+    }
+    switch (r) {
+      case 1: expand_rows_grouped_kernel<1><<<unsigned(units), 256, 0, stream>>>(g); break;
+      case 2: expand_rows_grouped_kernel<2><<<unsigned(units), 256, 0, stream>>>(g); break;
+      case 4: expand_rows_grouped_kernel<4><<<unsigned(units), 256, 0, stream>>>(g); break;
+      default: expand_rows_grouped_kernel<8><<<unsigned(units), 256, 0, stream>>>(g); break;
+    }
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    if (launches) ++*launches;
+  }
+  return cudaSuccess;
 }
 
 namespace {

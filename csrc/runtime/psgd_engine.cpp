@@ -114,17 +114,27 @@ cudaError_t PsgdEngine::apply(int parity, float lr, float mu, float weight_decay
   PSGD_TRY(cuda::psgd_owner_gather_batched(gq_[parity].data(), int(gq_[parity].size()), world_,
                                            1.0f / float(world_), stream));
   launches_ += batches(gq_[parity].size());
-  for (const PsgdMatrix& mat : mats_) {
-    cuda::SgdApply a;
-    a.param = mat.param;
-    a.momentum = mat.momentum;
-    a.lr = lr;
-    a.mu = mu;
-    a.weight_decay = weight_decay;
-    a.first_step = first_step ? 1 : 0;
-    PSGD_TRY(cuda::psgd_expand_sgd(mat.P, mat.Q, mat.n, mat.m, r_, mat.M, mat.numel, 1.0f, a, stream));
-    ++launches_;
+  cuda::SgdApply common;
+  common.lr = lr;
+  common.mu = mu;
+  common.weight_decay = weight_decay;
+  common.first_step = first_step ? 1 : 0;
+  std::vector<cuda::PsgdExpandItem> items(mats_.size());
+  for (size_t i = 0; i < mats_.size(); ++i) {
+    const PsgdMatrix& mat = mats_[i];
+    cuda::PsgdExpandItem& it = items[i];
+    it.P = mat.P;
+    it.Q = mat.Q;
+    it.n = mat.n;
+    it.m = mat.m;
+    it.N = mat.numel;
+    it.Mat = mat.M;
+    it.param = mat.param;
+    it.momentum = mat.momentum;
   }
+  int launched = 0;
+  PSGD_TRY(cuda::psgd_expand_sgd_grouped(items.data(), int(items.size()), r_, 1.0f, common, &launched, stream));
+  launches_ += launched;
   return cudaSuccess;
 }
 
