@@ -181,6 +181,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_ln_forward", &ops::add_ln_forward, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("bias"),
         py::arg("eps"));
   m.def("add_ln_backward", &ops::add_ln_backward, py::arg("dy"), py::arg("z"), py::arg("stats"), py::arg("weight"));
+  m.def("linear_wgrad_bgrad", &ops::linear_wgrad_bgrad, py::arg("dy"), py::arg("x"));
   m.def("colsum_supported", &ops::colsum_supported, py::arg("dy"));
   m.def("colsum", &ops::colsum, py::arg("dy"));
   m.def("psgd_kpad", &cuda::psgd_kpad, py::arg("k"));

@@ -121,6 +121,10 @@ std::vector<torch::Tensor> bias_relu_backward(const torch::Tensor& dy, const tor
                                               const c10::optional<torch::Tensor>& idx, bool pool);
 
 // Sum over all leading dimensions of a contiguous bf16 tensor -> fp32 [last dim] (bias gradients).
+// {dW [out, in] fp32, db [out] fp32} of a linear layer from dy [tokens, out] and x [tokens, in] (bf16), the
+// bias gradient taken by the GEMM's epilogue; an empty list when the library has no such algorithm for the
+// shape (the caller then uses its separate GEMM and column sum).
+std::vector<torch::Tensor> linear_wgrad_bgrad(const torch::Tensor& dy, const torch::Tensor& x);
 bool colsum_supported(const torch::Tensor& dy);
 torch::Tensor colsum(const torch::Tensor& dy);
 

@@ -160,7 +160,7 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
             cmd += ["-L", l, f"-Wl,-rpath,{l}"]
         cmd += ["-L", f"{cuda_home}/lib64", f"-Wl,-rpath,{cuda_home}/lib64",
                 "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
-                "-lcudart", "-ldl", "-lpthread"]
+                "-lcublasLt", "-lcudart", "-ldl", "-lpthread"]
         _run(cmd)
         os.replace(tmp, ext)
 

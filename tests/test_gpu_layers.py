@@ -270,3 +270,24 @@ def test_fused_linear_matches_autocast_linear(shape, out):
     ref_w = dy.reshape(-1, out).float().t() @ x.reshape(-1, shape[-1]).float()
     torch.testing.assert_close(fused.weight.grad, ref_w, atol=2e-2 * ref_w.abs().max().item(), rtol=2e-2)
     torch.testing.assert_close(fused.bias.grad, dy.reshape(-1, out).float().sum(0), atol=1e-2, rtol=1e-3)
+
+
+@pytest.mark.parametrize("tokens,in_f,out_f", [(4096, 1024, 1024), (4096, 1024, 4096), (4096, 4096, 1024), (21, 64, 256)])
+def test_linear_wgrad_bgrad_matches_fp32(tokens, in_f, out_f):
+    """Weight gradient and bias gradient from one GEMM (bias-gradient epilogue) against fp32 products of the
+    same bf16 operands; shapes of BERT-large's attention and feed-forward layers plus a small ragged one."""
+    import hipress_b200 as hp
+    torch.manual_seed(tokens + in_f + out_f)
+    dy = torch.randn(tokens, out_f, device="cuda").to(torch.bfloat16)
+    x = torch.randn(tokens, in_f, device="cuda").to(torch.bfloat16)
+    both = hp._C.linear_wgrad_bgrad(dy, x)
+    if not both:
+        pytest.skip("the GEMM library offers no bias-gradient epilogue for this shape; the two-kernel path runs")
+    dw, db = both
+    assert dw.dtype == torch.float32 and db.dtype == torch.float32 and dw.shape == (out_f, in_f) and db.shape == (out_f,)
+    ref_w = dy.float().t() @ x.float()
+    torch.testing.assert_close(dw, ref_w, atol=1e-3 * ref_w.abs().max().item(), rtol=1e-3)
+    torch.testing.assert_close(db, dy.float().sum(0), atol=1e-3 * (tokens ** 0.5), rtol=1e-3)
+    # a second call of the same shape reuses the cached plan and gives the same bits
+    dw2, db2 = hp._C.linear_wgrad_bgrad(dy, x)
+    assert torch.equal(dw, dw2) and torch.equal(db, db2)
