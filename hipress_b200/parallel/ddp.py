@@ -90,19 +90,25 @@ class CompressionConfig:
 
 
 def prefer_sharded(bucket_bytes: float, world: int) -> bool:
-    """Size rule for the form of the tbq / terngrad exchange.
+    """Size rule for the form of the tbq / terngrad exchange (used when ``sharded=None``).
 
     All-gather form: every rank stores its payload into all ``world`` slots and decodes
     ``world`` payloads per element -- two phases, the fewest launches.  Sharded form: compressed
     reduce-scatter to shard owners, then compressed all-gather of the re-quantised averages --
     2 (world-1)/world of one payload on the wire and two table look-ups per element instead of
-    ``world``, for a third phase, a second flag wait and a second quantisation.  The sharded form
-    pays once a rank's outgoing payloads and its ``world``-fold decode dominate: large buckets on
-    many GPUs."""
-    return world >= 4 and bucket_bytes >= SHARDED_MIN_BYTES
+    ``world``, for a third phase, a second flag wait and a second quantisation.
+
+    Measured on NVSwitch at 2 and 4 GPUs the all-gather form wins at every size from 256 KB to
+    512 MB (512 MB at 4 GPUs: TBQ 0.43 ms against 0.51 ms sharded, TernGrad 0.61 against 0.75):
+    the switch delivers the extra copies of a payload for the cost of one read of the gradient.
+    The rule therefore picks the sharded form only where a rank's outgoing payloads and its
+    ``world``-fold decode grow further, at 8 ranks and buckets of ``SHARDED_MIN_BYTES`` or
+    more; that corner is not calibrated by a measurement on the current kernels."""
+    return world >= SHARDED_MIN_WORLD and bucket_bytes >= SHARDED_MIN_BYTES
 
 
 SHARDED_MIN_BYTES = 48 * (1 << 20)
+SHARDED_MIN_WORLD = 8
 
 
 @dataclass
