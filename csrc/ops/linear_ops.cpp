@@ -10,6 +10,8 @@
 // A[in, T] * B[out, T]^T with A = X and B = dY as cuBLAS sees row-major buffers; the epilogue
 // reduces B over T, one value per column of D.
 //
+// The reference has no model code; this belongs to the model zoo built around its codecs.
+//
 // Not every (shape, type) combination has an algorithm with this epilogue; `linear_wgrad_bgrad`
 // reports that by returning an empty list and the caller keeps its two-kernel path.
 #include <ATen/cuda/CUDAContext.h>
