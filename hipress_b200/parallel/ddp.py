@@ -98,16 +98,16 @@ def prefer_sharded(bucket_bytes: float, world: int) -> bool:
     2 (world-1)/world of one payload on the wire and two table look-ups per element instead of
     ``world``, for a third phase, a second flag wait and a second quantisation.
 
-    Measured on NVSwitch at 2 and 4 GPUs the all-gather form wins at every size from 256 KB to
-    512 MB (512 MB at 4 GPUs: TBQ 0.43 ms against 0.51 ms sharded, TernGrad 0.61 against 0.75):
-    the switch delivers the extra copies of a payload for the cost of one read of the gradient.
-    The rule therefore picks the sharded form only where a rank's outgoing payloads and its
-    ``world``-fold decode grow further, at 8 ranks and buckets of ``SHARDED_MIN_BYTES`` or
-    more; that corner is not calibrated by a measurement on the current kernels."""
+    Measured on NVSwitch: at 2 and 4 GPUs the all-gather form wins at every size from 256 KB to
+    512 MB (512 MB at 4 GPUs: TBQ 0.43 ms against 0.51 ms sharded) -- the switch delivers the
+    extra copies of a payload for the cost of one read of the gradient.  At 8 GPUs the sharded
+    form wins at 512 MB (TBQ 0.50 against 0.59 ms, TernGrad 0.76 against 0.89 ms), ties at 64 MB
+    and loses below.  The rule picks it at 8 ranks from ``SHARDED_MIN_BYTES`` (128 MB, between
+    the tie and the win; 25 MB training buckets stay on the all-gather form)."""
     return world >= SHARDED_MIN_WORLD and bucket_bytes >= SHARDED_MIN_BYTES
 
 
-SHARDED_MIN_BYTES = 48 * (1 << 20)
+SHARDED_MIN_BYTES = 128 * (1 << 20)
 SHARDED_MIN_WORLD = 8
 
 

@@ -63,11 +63,12 @@ def test_clock_sampler_windows_samples_with_a_fake_nvidia_smi(tmp_path, monkeypa
 
 def test_prefer_sharded_rule():
     """The exchange-form rule: all-gather form wherever it was measured faster (2 and 4 ranks, any size),
-    sharded only for large buckets at 8 ranks."""
+    sharded only where it was measured faster: large buckets at 8 ranks."""
     from hipress_b200.parallel import prefer_sharded
     mb = 1 << 20
     for world in (1, 2, 4):
         for size in (256 * 1024, 25 * mb, 512 * mb):
             assert not prefer_sharded(size, world)
     assert not prefer_sharded(25 * mb, 8)
-    assert prefer_sharded(64 * mb, 8)
+    assert not prefer_sharded(64 * mb, 8)
+    assert prefer_sharded(512 * mb, 8)
