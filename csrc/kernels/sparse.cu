@@ -380,6 +380,9 @@ recount_kernel(const float* __restrict__ R, int64_t n, int64_t chunk, unsigned i
 }
 
 // ---- one CTA: offsets, k, header, housekeeping
+// thread t scans the totals of CTA t: the count / write kernels may not have more CTAs than this
+// kernel has threads
+static_assert(kMaxBlocks <= 1024, "scan_kernel scans one per-CTA total per thread");
 __global__ void __launch_bounds__(1024)
 scan_kernel(int blocks, PushTargets dst, SparseScratch* s) {
   resolve_epoch(dst);
