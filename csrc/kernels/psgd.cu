@@ -11,8 +11,12 @@
 // those rows with red.global.add.f32 -- the owner may be a peer GPU (NVLink
 // peer memory), which makes the kernel a fused GEMM + reduce-scatter.  Mode 1
 // consumes Mat through the MN-major operand form, so Mat is never transposed
-// in memory.  The reference computes these with torch::mm (cuBLAS) and leaves
-// the all-reduce to its caller (ref powersgd_body.h:28, 49).
+// in memory.  A step's projections run as ONE grid over all matrices of the
+// model (psgd_gemm_grouped: units of row tile x K range, largest first), because
+// a launch per matrix costs more in ramp-up and drain than the small matrices
+// take to stream.  The reference computes these with torch::mm (cuBLAS), one
+// call per matrix, and leaves the all-reduce to its caller
+// (ref powersgd_body.h:28, 49).
 //
 // Shapes TMA cannot describe (row pitch not a multiple of 16 bytes, unaligned
 // base) take a plain SIMT kernel with the same interface.

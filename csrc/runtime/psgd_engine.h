@@ -1,8 +1,9 @@
 // PowerSGD step driver: owns the per-matrix launch plan of a model and issues each phase of a
 // step as a handful of launches -- one batched kernel per kind of small work (operand
-// transposes, factor gathers, orthonormalisation) and one tcgen05 GEMM / fused expand per
-// matrix -- from a single native call, so that a model with tens of matrices does not pay a
-// Python round trip and a tiny launch per matrix and stage.
+// transposes, factor gathers, orthonormalisation), one grouped tcgen05 grid for the projections
+// of all matrices and one grouped grid for their expand + SGD pass -- from a single native
+// call, so that a model with tens of matrices pays neither a Python round trip nor a kernel's
+// ramp-up and drain per matrix and stage.
 //
 // The reference exposes PowerSGD as three tasks per tensor (encode1 / encode2 / decode:
 // ref hp_cuda.cpp:640-772, powersgd_body.h:10-78) that its five worker threads pick up one

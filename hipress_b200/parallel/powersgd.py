@@ -105,7 +105,7 @@ class PowerSGDDataParallel(nn.Module):
         self.emulated = emulated
         self.epoch_dev = torch.zeros(16, dtype=torch.int32, device=dev) if self.graph_capturable else None
 
-        # ---- native step driver: batched small kernels + one GEMM / expand launch per matrix
+        # ---- native step driver: batched small kernels + one grouped GEMM / expand grid per phase
         self.engine = _C.PsgdEngine(self.world, self.r, self.flat_M)
         tsize = sum(16 * (_C.psgd_kpad(n) + _C.psgd_kpad(m)) for n, m in self.shapes)
         self.operand_scratch = torch.zeros(max(tsize, 16), device=dev)
