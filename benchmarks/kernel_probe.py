@@ -46,7 +46,7 @@ def timed(fn, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="terngrad",
-                    choices=["terngrad", "terngrad_words", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q", "psgd_group_p", "psgd_group_q", "psgd_loop_p", "psgd_loop_q",
+                    choices=["terngrad", "terngrad_words", "terngrad_unpack", "tbq", "tbq_unpack", "sparse", "ecq", "psgd_p", "psgd_q", "psgd_group_p", "psgd_group_q", "psgd_loop_p", "psgd_loop_q", "psgd_group_expand", "psgd_loop_expand",
                              "psgd_expand", "sgd", "adamw", "terngrad_unpack_apply", "bn_fwd", "bn_bwd",
                              "bias_relu_pool_fwd", "bias_relu_pool_bwd", "add_ln_fwd", "add_ln_bwd", "maxpool_fwd",
                              "maxpool_bwd"])
@@ -143,6 +143,26 @@ def main():
                     ops.psgd_project(mode, M, X, [o])
         traffic = sum(a * b for a, b in shapes) * 4
         n = traffic // 4
+    elif k in ("psgd_group_expand", "psgd_loop_expand"):
+        # M -= P Q^T and the SGD-momentum step from P Q^T for the 19 weight matrices of VGG-19: one grid over all
+        # of them against one launch per matrix; --mb is ignored
+        import hipress_b200 as hp
+        chans = [(64, 3), (64, 64), (128, 64), (128, 128), (256, 128), (256, 256), (256, 256), (256, 256),
+                 (512, 256), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512)]
+        shapes = [(o, i * 9) for o, i in chans] + [(4096, 25088), (4096, 4096), (1000, 4096)]
+        Ms = [torch.randn(a, b, device=dev) for a, b in shapes]
+        Ps = [torch.randn(a, 4, device=dev) * 0.01 for a, b in shapes]
+        Qs = [torch.randn(b, 4, device=dev) * 0.01 for a, b in shapes]
+        params = [torch.randn(a * b, device=dev) for a, b in shapes]
+        moms = [torch.zeros(a * b, device=dev) for a, b in shapes]
+        if k == "psgd_group_expand":
+            fn = lambda: hp._C.psgd_expand_sgd_grouped(Ps, Qs, Ms, params, moms, 1.0, 0.01, 0.9, 0.0, False)
+        else:
+            def fn():
+                for P_, Q_, M_, p_, m_ in zip(Ps, Qs, Ms, params, moms):
+                    hp._C.psgd_expand_sgd(P_, Q_, M_, p_, m_, 1.0, 0.01, 0.9, 0.0, False)
+        n = sum(a * b for a, b in shapes)
+        traffic = n * 24          # read and write the matrix, the parameters and the momentum
     elif k == "terngrad_unpack_apply":
         # what a training step runs per bucket: decode `world` payloads, average, fused SGD step,
         # zeros left in the gradient bucket

@@ -193,6 +193,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("psgd_expand_sgd", &ops::psgd_expand_sgd, py::arg("P"), py::arg("Q"), py::arg("M"),
         py::arg("param"), py::arg("momentum"), py::arg("post_scale"), py::arg("lr"), py::arg("mu"),
         py::arg("weight_decay"), py::arg("first_step"));
+  m.def("psgd_expand_sgd_grouped", &ops::psgd_expand_sgd_grouped, py::arg("Ps"), py::arg("Qs"), py::arg("Ms"),
+        py::arg("params"), py::arg("momenta"), py::arg("post_scale"), py::arg("lr"), py::arg("mu"),
+        py::arg("weight_decay"), py::arg("first_step"));
   m.def("read_status", &ops::read_status, py::arg("like"), py::arg("reset") = true);
 
   // fused SGD-momentum over flat fp32 buffers

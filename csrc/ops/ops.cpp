@@ -565,6 +565,45 @@ void psgd_expand_sgd(const torch::Tensor& P, const torch::Tensor& Q, torch::Tens
                                       at::cuda::getCurrentCUDAStream()));
 }
 
+void psgd_expand_sgd_grouped(const std::vector<torch::Tensor>& Ps, const std::vector<torch::Tensor>& Qs,
+                             const std::vector<torch::Tensor>& Ms, const std::vector<torch::Tensor>& params,
+                             const std::vector<torch::Tensor>& momenta, double post_scale, double lr, double mu,
+                             double weight_decay, bool first_step) {
+  const size_t count = Ms.size();
+  TORCH_CHECK(count > 0 && Ps.size() == count && Qs.size() == count && params.size() == count &&
+                  momenta.size() == count,
+              "one P, Q, param and momentum per matrix");
+  TORCH_CHECK(Ms[0].is_cuda(), "CUDA tensors expected");
+  std::vector<cuda::PsgdExpandItem> items(count);
+  int64_t r = -1;
+  for (size_t i = 0; i < count; ++i) {
+    const PsgdShape s = psgd_shape(Ms[i], Ps[i], Qs[i]);
+    TORCH_CHECK(r < 0 || r == s.r, "matrices of one rank expected");
+    r = s.r;
+    TORCH_CHECK(params[i].scalar_type() == torch::kFloat32 && momenta[i].scalar_type() == torch::kFloat32,
+                "param and momentum must be float32");
+    const int64_t N = params[i].numel();
+    TORCH_CHECK(momenta[i].numel() == N && N <= s.n * s.m, "param/momentum must fit in M");
+    cuda::PsgdExpandItem& it = items[i];
+    it.P = Ps[i].data_ptr<float>();
+    it.Q = Qs[i].data_ptr<float>();
+    it.n = s.n;
+    it.m = s.m;
+    it.N = N;
+    it.Mat = Ms[i].data_ptr<float>();
+    it.param = params[i].data_ptr<float>();
+    it.momentum = momenta[i].data_ptr<float>();
+  }
+  cuda::SgdApply common;
+  common.lr = float(lr);
+  common.mu = float(mu);
+  common.weight_decay = float(weight_decay);
+  common.first_step = first_step ? 1 : 0;
+  c10::cuda::CUDAGuard guard(Ms[0].device());
+  HP_CHECK_CUDA(cuda::psgd_expand_sgd_grouped(items.data(), int(count), int(r), float(post_scale), common, nullptr,
+                                              at::cuda::getCurrentCUDAStream()));
+}
+
 void powersgd_encode1(const torch::Tensor& grad, const torch::Tensor& residual,
                       const torch::Tensor& Q, torch::Tensor M, torch::Tensor P) {
   const PsgdShape s = psgd_shape(M, P, Q);

@@ -85,6 +85,12 @@ void psgd_expand_sgd(const torch::Tensor& P, const torch::Tensor& Q, torch::Tens
                      torch::Tensor param, torch::Tensor momentum, double post_scale, double lr,
                      double mu, double weight_decay, bool first_step);
 
+// The same for a list of matrices of one rank, all matrices that take the vectorised form in one grid.
+void psgd_expand_sgd_grouped(const std::vector<torch::Tensor>& Ps, const std::vector<torch::Tensor>& Qs,
+                             const std::vector<torch::Tensor>& Ms, const std::vector<torch::Tensor>& params,
+                             const std::vector<torch::Tensor>& momenta, double post_scale, double lr, double mu,
+                             double weight_decay, bool first_step);
+
 // Device status word of the last bounds / header failure seen by kernels
 // launched through these ops on the tensor's device (0 = none); reading it
 // synchronises the current stream.

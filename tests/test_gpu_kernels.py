@@ -310,6 +310,27 @@ def test_psgd_project_grouped_matches_fp64(mode, count):
     assert ops.read_status(Ms[0]) == 0
 
 
+def test_psgd_expand_sgd_grouped_matches_per_matrix():
+    """One grid over a list of matrices (vectorised and ragged shapes mixed) leaves the same bits in the error
+    feedback, the parameters and the momentum as one launch per matrix."""
+    torch.manual_seed(5)
+    shapes = [(64, 576), (512, 4608), (300, 1000), (77, 61), (1000, 4096), (130, 36)] * 7   # more than one launch holds
+    def make():
+        torch.manual_seed(6)
+        return ([torch.randn(a, b, device="cuda") for a, b in shapes],
+                [torch.randn(a, 4, device="cuda") * 0.1 for a, b in shapes],
+                [torch.randn(b, 4, device="cuda") * 0.1 for a, b in shapes],
+                [torch.randn(a * b, device="cuda") for a, b in shapes],
+                [torch.randn(a * b, device="cuda") * 0.01 for a, b in shapes])
+    Ms, Ps, Qs, params, moms = make()
+    hp._C.psgd_expand_sgd_grouped(Ps, Qs, Ms, params, moms, 0.5, 0.01, 0.9, 1e-4, False)
+    Mr, Pr, Qr, pr, mr = make()
+    for P_, Q_, M_, p_, m_ in zip(Pr, Qr, Mr, pr, mr):
+        hp._C.psgd_expand_sgd(P_, Q_, M_, p_, m_, 0.5, 0.01, 0.9, 1e-4, False)
+    for a, b in zip(Ms + params + moms, Mr + pr + mr):
+        assert torch.equal(a, b)
+
+
 def test_psgd_project_relative_error_tf32():
     torch.manual_seed(0)
     n, m, r = 1024, 4096, 4
