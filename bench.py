@@ -128,7 +128,8 @@ class OurTrainer:
             # measured in the steady state: the 400-step sparsity warm-up is skipped, not shortened
             self.model = DGCDataParallel(net, keep_fraction=0.001, warmup_steps=400, lr=1e-4, bucket_mb=self.bucket_mb,
                                          start_step=args.dgc_start_step,
-                                         graph_capturable=bool(args.cuda_graph and args.dgc_whole_step))
+                                         graph_capturable=bool(args.cuda_graph and args.dgc_whole_step),
+                                         trace=bool(args.trace))
         elif self.algorithm == "nccl":
             from hipress_b200.parallel.baseline import NcclDataParallel
             self.error_feedback = False

@@ -36,7 +36,7 @@ class DGCDataParallel(CompressedDataParallel):
                  warmup_steps: int = 400, momentum_correction: float = 0.9, clip_norm: float = 1.0,
                  lr: float = 1e-4, weight_decay: float = 0.01, optimizer: str = "adamw",
                  bucket_mb: float = 25.0, seed: int = 1, start_step: int = 0,
-                 graph_capturable: bool = False, **kw):
+                 graph_capturable: bool = False, trace: bool = False, transport: str = "p2p", **kw):
         # start_step: position in the warm-up schedule of the first step (resuming a run, or
         # measuring the steady state without running the warm-up first)
         self.start_step = int(start_step)
@@ -45,7 +45,7 @@ class DGCDataParallel(CompressedDataParallel):
         cfg = CompressionConfig("dgc", keep_fraction=max_keep, sample_rate=sample_rate, bucket_mb=bucket_mb,
                                 seed=seed, momentum_correction=momentum_correction > 0,
                                 dgc_momentum=momentum_correction, clip_norm=clip_norm,
-                                graph_capturable=graph_capturable)
+                                graph_capturable=graph_capturable, trace=trace, transport=transport)
         super().__init__(module, cfg, lr=lr, momentum=0.0, weight_decay=weight_decay, fused_sgd=True,
                          optimizer=optimizer, **kw)
         self.target_keep = keep_fraction
