@@ -28,9 +28,12 @@ def main():
     ap.add_argument("--reference-dir", default=os.environ.get("HIPRESS_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference")))
     ap.add_argument("--n", type=int, default=1 << 22)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--threads", type=int, default=1,
+                    help="threads this framework's CPU codec may use (the reference's host path has one)")
     args = ap.parse_args()
     torch.manual_seed(0)
     torch.set_num_threads(1)
+    ops.set_cpu_threads(args.threads)
     n = args.n
     g = torch.randn(n) * 0.01
     resid, dense = torch.zeros(n), torch.empty(n)
@@ -45,7 +48,7 @@ def main():
         ops.terngrad_compress(g, 2, True, 1, out=p2)
         ops.terngrad_decompress(p2, dense)
     t2 = time.perf_counter()
-    out = {"n": n, "iters": args.iters, "threads": 1,
+    out = {"n": n, "iters": args.iters, "threads": ops.get_cpu_threads(),
            "ours": {"tbq_ms_per_iter": round((t1 - t0) * 1e3 / args.iters, 3),
                     "terngrad_ms_per_iter": round((t2 - t1) * 1e3 / args.iters, 3)}}
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"

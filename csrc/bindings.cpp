@@ -11,6 +11,7 @@
 
 #include <cstring>
 
+#include "codec_cpu/codec_cpu.h"
 #include "comm/symm_mem.h"
 #include "common/codec_math.h"
 #include "common/host_utils.h"
@@ -181,6 +182,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_ln_forward", &ops::add_ln_forward, py::arg("x"), py::arg("delta"), py::arg("weight"), py::arg("bias"),
         py::arg("eps"));
   m.def("add_ln_backward", &ops::add_ln_backward, py::arg("dy"), py::arg("z"), py::arg("stats"), py::arg("weight"));
+  m.def("set_cpu_threads", &cpu::set_threads, py::arg("threads"));
+  m.def("get_cpu_threads", &cpu::get_threads);
   m.def("linear_wgrad_bgrad", &ops::linear_wgrad_bgrad, py::arg("dy"), py::arg("x"));
   m.def("colsum_supported", &ops::colsum_supported, py::arg("dy"));
   m.def("colsum", &ops::colsum, py::arg("dy"));

@@ -1,15 +1,47 @@
 #include "codec_cpu.h"
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstring>
 #include <functional>
+#include <thread>
 #include <vector>
 
 #include "../common/codec_math.h"
 
 namespace hipress {
 namespace cpu {
+
+namespace {
+std::atomic<int> g_threads{1};
+constexpr int64_t kGrainElems = int64_t(1) << 16;   // smallest piece worth a thread
+
+// body(begin, end) over [0, items) in contiguous pieces, one per thread (the caller runs the
+// first piece).  `elems_per_item` scales the grain from elements to items (payload bytes).
+template <class F>
+void parallel_items(int64_t items, int64_t elems_per_item, const F& body) {
+  const int want = g_threads.load(std::memory_order_relaxed);
+  const int64_t grain = std::max<int64_t>(1, kGrainElems / std::max<int64_t>(1, elems_per_item));
+  int64_t pieces = std::min<int64_t>(want, items / grain);
+  if (pieces <= 1) {
+    if (items > 0) body(int64_t(0), items);
+    return;
+  }
+  const int64_t per = (items + pieces - 1) / pieces;
+  std::vector<std::thread> pool;
+  pool.reserve(size_t(pieces - 1));
+  for (int64_t p = 1; p < pieces; ++p) {
+    const int64_t b = p * per, e = std::min(items, b + per);
+    if (b < e) pool.emplace_back([&body, b, e] { body(b, e); });
+  }
+  body(int64_t(0), std::min(items, per));
+  for (auto& t : pool) t.join();
+}
+}  // namespace
+
+void set_threads(int threads) { g_threads.store(threads < 1 ? 1 : (threads > 256 ? 256 : threads)); }
+int get_threads() { return g_threads.load(); }
 
 // ------------------------------------------------------------------ TBQ
 namespace {
@@ -32,14 +64,16 @@ inline uint32_t tbq_quant_select(float& r, float g, float t) {
 
 void tbq_compress(const float* grad, float* residual, int64_t n, float threshold, uint8_t* out) {
   const int64_t full = n >> 2;
-  for (int64_t b = 0; b < full; ++b) {  // whole bytes: no bounds checks inside
-    const int64_t base = b << 2;
-    const uint32_t q = tbq_quant_select(residual[base], grad[base], threshold) |
-                       (tbq_quant_select(residual[base + 1], grad[base + 1], threshold) << 2) |
-                       (tbq_quant_select(residual[base + 2], grad[base + 2], threshold) << 4) |
-                       (tbq_quant_select(residual[base + 3], grad[base + 3], threshold) << 6);
-    out[b] = static_cast<uint8_t>(q);
-  }
+  parallel_items(full, 4, [=](int64_t b0, int64_t b1) {
+    for (int64_t b = b0; b < b1; ++b) {  // whole bytes: no bounds checks inside
+      const int64_t base = b << 2;
+      const uint32_t q = tbq_quant_select(residual[base], grad[base], threshold) |
+                         (tbq_quant_select(residual[base + 1], grad[base + 1], threshold) << 2) |
+                         (tbq_quant_select(residual[base + 2], grad[base + 2], threshold) << 4) |
+                         (tbq_quant_select(residual[base + 3], grad[base + 3], threshold) << 6);
+      out[b] = static_cast<uint8_t>(q);
+    }
+  });
   if (n & 3) {
     uint32_t q = 0;
     for (int k = 0; k < 4; ++k) {
@@ -58,18 +92,21 @@ void tbq_decompress(const uint8_t* in, int64_t n, float threshold, float* out, i
   for (int v = 0; v < 256; ++v)
     for (int k = 0; k < 4; ++k) lut[v][k] = tbq_dequant((static_cast<uint32_t>(v) >> (2 * k)) & 3u, threshold);
   const int64_t full = n >> 2;
-  if (add) {
-    for (int64_t b = 0; b < full; ++b) {
-      const float* e = lut[in[b]];
-      float* o = out + (b << 2);
-      o[0] = hp_add(e[0], o[0]);
-      o[1] = hp_add(e[1], o[1]);
-      o[2] = hp_add(e[2], o[2]);
-      o[3] = hp_add(e[3], o[3]);
+  const float (*table)[4] = lut;
+  parallel_items(full, 4, [=](int64_t b0, int64_t b1) {
+    if (add) {
+      for (int64_t b = b0; b < b1; ++b) {
+        const float* e = table[in[b]];
+        float* o = out + (b << 2);
+        o[0] = hp_add(e[0], o[0]);
+        o[1] = hp_add(e[1], o[1]);
+        o[2] = hp_add(e[2], o[2]);
+        o[3] = hp_add(e[3], o[3]);
+      }
+    } else {
+      for (int64_t b = b0; b < b1; ++b) std::memcpy(out + (b << 2), table[in[b]], 16);
     }
-  } else {
-    for (int64_t b = 0; b < full; ++b) std::memcpy(out + (b << 2), lut[in[b]], 16);
-  }
+  });
   for (int64_t i = full << 2; i < n; ++i) {
     const float v = lut[in[i >> 2]][i & 3];
     out[i] = add ? hp_add(v, out[i]) : v;
@@ -85,21 +122,23 @@ void tern_compress_impl(const float* grad, const float* res_in, float* res_out, 
   constexpr int DPB = 8 / BW;
   const int64_t full = n / DPB;
   const int rem = static_cast<int>(n % DPB);
-  float x[DPB];
-  float ef[DPB];
-  for (int64_t b = 0; b < full + (rem ? 1 : 0); ++b) {
-    const int count = b < full ? DPB : rem;
-    for (int j = 0; j < count; ++j) {
-      const int64_t e = b * DPB + j;
-      x[j] = res_in ? hp_add(grad[e], res_in[e]) : grad[e];
+  parallel_items(full + (rem ? 1 : 0), DPB, [=](int64_t b0, int64_t b1) {
+    float x[DPB] = {};
+    float ef[DPB] = {};
+    for (int64_t b = b0; b < b1; ++b) {
+      const int count = b < full ? DPB : rem;
+      for (int j = 0; j < count; ++j) {
+        const int64_t e = b * DPB + j;
+        x[j] = res_in ? hp_add(grad[e], res_in[e]) : grad[e];
+      }
+      // the tail byte is never stochastic
+      const bool rnd = random && b < full;
+      data[b] = tern_pack_byte<BW>(x, count, mn, inv, rnd, tern_byte_seed(seed, b), gap,
+                                   res_out ? ef : nullptr);
+      if (res_out)
+        for (int j = 0; j < count; ++j) res_out[b * DPB + j] = ef[j];
     }
-    // the tail byte is never stochastic
-    const bool rnd = random && b < full;
-    data[b] = tern_pack_byte<BW>(x, count, mn, inv, rnd, tern_byte_seed(seed, b), gap,
-                                 res_out ? ef : nullptr);
-    if (res_out)
-      for (int j = 0; j < count; ++j) res_out[b * DPB + j] = ef[j];
-  }
+  });
 }
 
 template <int BW>
@@ -112,15 +151,18 @@ void tern_decompress_impl(const uint8_t* data, int64_t count, float gap, float m
   for (int v = 0; v < 256; ++v)
     for (int k = 0; k < DPB; ++k) lut[v][k] = tern_dequant((static_cast<uint32_t>(v) >> (k * BW)) & MASK, gap, mn);
   const int64_t full = count / DPB;
-  if (add) {
-    for (int64_t b = 0; b < full; ++b) {
-      const float* e = lut[data[b]];
-      float* o = out + b * DPB;
-      for (int k = 0; k < DPB; ++k) o[k] = hp_add(e[k], o[k]);
+  const float (*table)[DPB] = lut;
+  parallel_items(full, DPB, [=](int64_t b0, int64_t b1) {
+    if (add) {
+      for (int64_t b = b0; b < b1; ++b) {
+        const float* e = table[data[b]];
+        float* o = out + b * DPB;
+        for (int k = 0; k < DPB; ++k) o[k] = hp_add(e[k], o[k]);
+      }
+    } else {
+      for (int64_t b = b0; b < b1; ++b) std::memcpy(out + b * DPB, table[data[b]], sizeof(float) * DPB);
     }
-  } else {
-    for (int64_t b = 0; b < full; ++b) std::memcpy(out + b * DPB, lut[data[b]], sizeof(float) * DPB);
-  }
+  });
   for (int64_t i = full * DPB; i < count; ++i) {
     const float v = lut[data[i / DPB]][i % DPB];
     out[i] = add ? hp_add(v, out[i]) : v;
@@ -135,12 +177,54 @@ int terngrad_compress(const float* grad, int64_t n, int bitwidth, int enable_ran
   if (n <= 0 || out_size != tern_payload_bytes(n, bitwidth)) return -1;
   // first minimum / last maximum, like thrust::minmax_element; the distinction
   // is only visible for +-0.0 extremes
-  float mn = residual ? hp_add(grad[0], residual[0]) : grad[0];
-  float mx = mn;
-  for (int64_t i = 1; i < n; ++i) {
-    const float v = residual ? hp_add(grad[i], residual[i]) : grad[i];
-    if (v < mn) mn = v;
-    if (!(v < mx)) mx = v;
+  float mn = 0.f, mx = 0.f;
+  auto scan = [&](int64_t b, int64_t e, float& lo, float& hi, bool& nan) {
+    lo = residual ? hp_add(grad[b], residual[b]) : grad[b];
+    hi = lo;
+    nan = lo != lo;
+    for (int64_t i = b + 1; i < e; ++i) {
+      const float v = residual ? hp_add(grad[i], residual[i]) : grad[i];
+      nan = nan || v != v;
+      if (v < lo) lo = v;
+      if (!(v < hi)) hi = v;
+    }
+  };
+  bool done = false;
+  const int pieces = int(std::min<int64_t>(get_threads(), n / kGrainElems));
+  if (pieces > 1) {
+    // per-piece extremes merged in element order with the same comparisons: the first minimum
+    // and the last maximum, exactly as the one-thread scan finds them -- for NaN-free input.
+    // A NaN makes the running extremes depend on everything before it, so any piece that
+    // saw one sends the whole tensor through the one-thread scan below.
+    std::vector<float> lo(size_t(pieces), 0.f), hi(size_t(pieces), 0.f);
+    std::vector<char> nan(size_t(pieces), 0);
+    const int64_t per = (n + pieces - 1) / pieces;
+    std::vector<std::thread> pool;
+    auto piece = [&](int p) {
+      const int64_t b = int64_t(p) * per, e = std::min(n, b + per);
+      bool saw = false;
+      if (b < e) scan(b, e, lo[size_t(p)], hi[size_t(p)], saw);
+      else saw = true;   // empty piece: take the safe path
+      nan[size_t(p)] = saw ? 1 : 0;
+    };
+    for (int p = 1; p < pieces; ++p) pool.emplace_back(piece, p);
+    piece(0);
+    for (auto& t : pool) t.join();
+    bool any_nan = false;
+    for (int p = 0; p < pieces; ++p) any_nan = any_nan || nan[size_t(p)] != 0;
+    if (!any_nan) {
+      mn = lo[0];
+      mx = hi[0];
+      for (int p = 1; p < pieces; ++p) {
+        if (lo[size_t(p)] < mn) mn = lo[size_t(p)];
+        if (!(hi[size_t(p)] < mx)) mx = hi[size_t(p)];
+      }
+      done = true;
+    }
+  }
+  if (!done) {
+    bool nan = false;
+    scan(0, n, mn, mx, nan);
   }
   const float gap = tern_gap(mn, mx, bitwidth);
   const float inv = tern_gap_inverse(gap);

@@ -12,6 +12,15 @@
 namespace hipress {
 namespace cpu {
 
+// Worker threads the TBQ and TernGrad codecs may split a tensor over (default 1: the plain
+// loops).  Every payload byte depends on its own 4 (or 8 / bitwidth) elements only -- the
+// stochastic rounding is seeded per byte -- so the split changes no bit of payload, residual or
+// decode.  The min/max pass of the TernGrad compressor stays sequential (its first-minimum /
+// last-maximum rule is defined by element order).  Tensors below 2^16 elements per thread are
+// not split.  The reference's host path is single-threaded.
+void set_threads(int threads);
+int get_threads();
+
 // ---- TBQ (ref tbq_body.h:90-158 compress, :160-200 decompress)
 // out must hold ceil(n/4) bytes.  residual is updated in place; grad is not.
 void tbq_compress(const float* grad, float* residual, int64_t n, float threshold, uint8_t* out);

@@ -34,9 +34,23 @@ __all__ = [
     "psgd_project", "psgd_project_grouped", "gram_schmidt", "psgd_expand_feedback", "read_status",
     "hp_cuda_tbq", "hp_cuda_tbqr", "hp_cuda_terngrad", "hp_cuda_terngradr", "hp_cuda_gd",
     "hp_cuda_gdr", "hp_cuda_powersgd_encode1", "hp_cuda_powersgd_encode2", "hp_cuda_powersgd_decode",
+    "set_cpu_threads", "get_cpu_threads",
 ]
 
 tbq_payload_bytes = _C.tbq_payload_bytes
+
+
+def set_cpu_threads(threads: int) -> None:
+    """Threads the TBQ / TernGrad codecs may use on CPU tensors (default 1).  Payloads, residuals and decodes
+    are bit-identical for every setting: each payload byte depends on its own elements only and stochastic
+    rounding is seeded per byte.  (The reference's host path is single-threaded.)"""
+    _C.set_cpu_threads(int(threads))
+
+
+def get_cpu_threads() -> int:
+    return int(_C.get_cpu_threads())
+
+
 terngrad_payload_bytes = _C.terngrad_payload_bytes
 sparse_payload_bytes = _C.sparse_payload_bytes
 ecq_payload_bytes = _C.ecq_payload_bytes

@@ -294,3 +294,63 @@ def test_powersgd_cpu_matches_fp64():
     approx = (P.double() @ Q.double().T).view(-1)[:N]
     torch.testing.assert_close(g2.double(), approx, atol=1e-4, rtol=1e-4)
     torch.testing.assert_close(r2.double(), grad.double() - approx, atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("n", [1 << 18, (1 << 20) + 3, 3 * (1 << 18) + 5])
+def test_threaded_cpu_codecs_are_bit_identical(n):
+    """TBQ and TernGrad (every bitwidth, stochastic and deterministic, with and without error feedback) on several
+    threads give the bytes, residuals and decodes of the one-thread loops."""
+    g = torch.randn(n, generator=torch.Generator().manual_seed(n)) * 0.01
+    def run():
+        out = []
+        r = torch.zeros(n)
+        p = ops.tbq_compress(g, r, 0.004)
+        d = torch.full((n,), 0.5)
+        ops.tbq_decompress([p, p], d, 0.004, add=True)
+        out += [p, r, d]
+        for bw in (1, 2, 4, 8):
+            for rnd in (False, True):
+                r = torch.zeros(n)
+                p = ops.terngrad_compress(g, bw, rnd, seed=7, residual=r)
+                d = torch.empty(n)
+                ops.terngrad_decompress([p], d)
+                out += [p, r, d]
+        return out
+    try:
+        ops.set_cpu_threads(1)
+        ref = run()
+        ops.set_cpu_threads(5)
+        assert ops.get_cpu_threads() == 5
+        got = run()
+    finally:
+        ops.set_cpu_threads(1)
+    assert len(ref) == len(got)
+    for a, b in zip(ref, got):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("case", ["signed_zeros", "nan_in_the_middle", "infinities", "nan_first"])
+def test_threaded_minmax_follows_element_order(case):
+    """The threaded min/max scan reports the first minimum and the last maximum of the one-thread scan (visible
+    for +-0.0 extremes) and takes the one-thread path whenever the tensor holds a NaN."""
+    n = 1 << 19
+    g = torch.zeros(n)
+    if case == "signed_zeros":
+        g[::3] = -0.0
+        g[5::7] = 0.0
+    else:
+        g = torch.randn(n, generator=torch.Generator().manual_seed(3)) * 0.01
+        if case == "nan_in_the_middle":
+            g[n // 2 + 17] = float("nan")
+        elif case == "nan_first":
+            g[0] = float("nan")
+        else:
+            g[1000], g[n - 5] = float("inf"), float("-inf")
+    try:
+        ops.set_cpu_threads(1)
+        ref = ops.terngrad_compress(g, 2, False, seed=1)
+        ops.set_cpu_threads(6)
+        got = ops.terngrad_compress(g, 2, False, seed=1)
+    finally:
+        ops.set_cpu_threads(1)
+    assert torch.equal(ref, got)
