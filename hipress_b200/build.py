@@ -178,7 +178,7 @@ def build(verbose: bool = False, jobs: int | None = None) -> Path:
 SANITIZERS = {"thread": ["-fsanitize=thread"], "address": ["-fsanitize=address,undefined", "-fno-omit-frame-pointer"]}
 
 
-def build_sanitized(kind: str) -> Path:
+def build_sanitized(kind: str, target: str = "runtime") -> Path:
     """Build the host runtime's stress test (tests/cpp/runtime_stress.cpp: WorkerPool,
     FinishQueue, AgeWatchdog -- the plain-C++ parts, which need neither torch nor a GPU) with
     ThreadSanitizer (``thread``) or AddressSanitizer + UBSan (``address``) and return the
@@ -189,12 +189,23 @@ def build_sanitized(kind: str) -> Path:
         raise ValueError(f"sanitizer must be one of {sorted(SANITIZERS)}")
     out_dir = ROOT / "build" / "sanitize"
     out_dir.mkdir(parents=True, exist_ok=True)
-    exe = out_dir / f"runtime_stress_{kind}"
-    src = ROOT / "tests" / "cpp" / "runtime_stress.cpp"
-    newest = max([src.stat().st_mtime] + [p.stat().st_mtime for p in (CSRC / "runtime").glob("*.h")])
+    if target == "codec":
+        # ``target="codec"``: the threaded CPU codecs (tests/cpp/codec_threads.cpp + codec_cpu.cpp)
+        exe = out_dir / f"codec_threads_{kind}"
+        srcs = [ROOT / "tests" / "cpp" / "codec_threads.cpp", CSRC / "codec_cpu" / "codec_cpu.cpp"]
+        deps = srcs + list((CSRC / "common").glob("*.h")) + [CSRC / "codec_cpu" / "codec_cpu.h"]
+        extra = ["-ffp-contract=off"]
+    elif target == "runtime":
+        exe = out_dir / f"runtime_stress_{kind}"
+        srcs = [ROOT / "tests" / "cpp" / "runtime_stress.cpp"]
+        deps = srcs + list((CSRC / "runtime").glob("*.h"))
+        extra = []
+    else:
+        raise ValueError("target must be 'runtime' or 'codec'")
+    newest = max(p.stat().st_mtime for p in deps)
     if not exe.exists() or exe.stat().st_mtime < newest:
-        _run(["g++", "-std=c++17", "-O1", "-g", *SANITIZERS[kind], "-I", str(CSRC), str(src), "-o", str(exe),
-              "-lpthread"])
+        _run(["g++", "-std=c++17", "-O1", "-g", *extra, *SANITIZERS[kind], "-I", str(CSRC), *map(str, srcs),
+              "-o", str(exe), "-lpthread"])
     return exe
 
 
@@ -209,6 +220,6 @@ def ptxas_report() -> str:
 
 if __name__ == "__main__":
     if len(sys.argv) >= 3 and sys.argv[1] == "--sanitize":
-        print(build_sanitized(sys.argv[2]))
+        print(build_sanitized(sys.argv[2], *(sys.argv[3:4])))   # optional third word: runtime | codec
     else:
         print(build(verbose=True))

@@ -24,3 +24,21 @@ def test_runtime_stress_under_sanitizer(kind):
     assert proc.returncode == 0, proc.stdout + proc.stderr
     assert "runtime_stress: ok" in proc.stdout
     assert "Sanitizer" not in proc.stderr, proc.stderr
+
+
+@pytest.mark.parametrize("kind", ["thread", "address"])
+def test_threaded_cpu_codecs_under_sanitizer(kind):
+    """TBQ / TernGrad split over several threads, and two callers at once, with the results compared to the
+    one-thread run inside the executable."""
+    try:
+        exe = build_sanitized(kind, target="codec")
+    except RuntimeError as exc:
+        if "sanitize" in str(exc) or "cannot find" in str(exc):
+            pytest.skip(f"-fsanitize={kind} is not available here")
+        raise
+    env = {"TSAN_OPTIONS": "halt_on_error=1 exitcode=66", "ASAN_OPTIONS": "detect_leaks=1 exitcode=66",
+           "UBSAN_OPTIONS": "halt_on_error=1 exitcode=66", "PATH": "/usr/bin:/bin"}
+    proc = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
+    assert proc.returncode == 0, proc.stdout + proc.stderr
+    assert "codec_threads: ok" in proc.stdout
+    assert "Sanitizer" not in proc.stderr, proc.stderr
