@@ -188,7 +188,7 @@ class OurTrainer:
         wrapper's ``metrics()``: it reads and resets the device-side wait counters."""
         m = self.model.metrics()
         keep = ("wait_us_total", "wait_us_max", "waits", "step_us", "exposed_tail_us", "stages", "selected_k",
-                "candidates", "wire_bytes_last_step", "thresholds", "dropped_candidates")
+                "candidates", "wire_bytes_last_step", "thresholds", "dropped_candidates", "residual_norm")
         return int(m.get("kernel_launches", 0)), {k: m[k] for k in keep if k in m}
 
     def finish(self):

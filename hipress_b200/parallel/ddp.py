@@ -384,7 +384,8 @@ class CompressedDataParallel(nn.Module):
         the time between the last bucket's gradients being ready (the end of backward) and the
         last update being applied; with a sparse codec also what the last step selected:
         ``selected_k`` elements out of ``candidates`` over the sampled ``thresholds`` (one per
-        bucket) and the bytes that put on the wire.  Synchronises the device."""
+        bucket) and the bytes that put on the wire.  ``residual_norm`` is the L2 norm of the error
+        feedback carried into the next step (codecs that keep one).  Synchronises the device."""
         dense = self.engine.dense_bytes_per_step
         wire = self.engine.wire_bytes_per_step
         total_ns, max_ns, waits = self.engine.wait_stats()
@@ -393,6 +394,10 @@ class CompressedDataParallel(nn.Module):
                "compression_ratio": dense * max(1, self.world - 1) / wire if wire else float("inf"),
                "kernel_launches": self.engine.launches, "steps": self.engine.steps,
                "wait_us_total": total_ns / 1e3, "wait_us_max": max_ns / 1e3, "waits": waits}
+        if self.flat_residual is not None:
+            # error feedback carried into the next step (for the sparse codecs: the velocity / residual
+            # the selection draws from)
+            out["residual_norm"] = float(torch.linalg.vector_norm(self.flat_residual))
         times = self.engine.stage_times()
         if times:
             nb = len(self.plan.buckets)

@@ -182,6 +182,8 @@ def test_ddp_wrapper_world1_trains(algorithm):
     assert min(losses[-4:]) < losses[0], losses
     m = model.metrics()
     assert m["kernel_launches"] > 0 and m["steps"] == 12
+    if cfg.needs_residual:
+        assert m["residual_norm"] >= 0 and m["residual_norm"] == m["residual_norm"]
 
 
 def test_ddp_dense_world1_equals_torch_sgd():
